@@ -1,0 +1,57 @@
+"""Compile the CUDA sources of this package for sm_100a, in-tree.
+
+``python -m cuda_llm_b200.build`` (or ``build()``) writes ``lib/libb2ops.so``: the
+kernels plus the C ABI declared in include/b2ops.h.  nvcc cross-compiles without a
+GPU.  The flags follow the reference's build where they are observable behaviour:
+C++17 and per-thread default streams (reference CMakeLists.txt:5-9).
+"""
+from __future__ import annotations
+
+import glob
+import os
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+LIB_DIR = os.path.join(PKG, "lib")
+LIB = os.path.join(LIB_DIR, "libb2ops.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--default-stream", "per-thread", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
+]
+
+
+def _newer(target: str, sources) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def sources():
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Build lib/libb2ops.so when it is missing or older than a source; returns its path."""
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
+        [os.path.join(ROOT, "include", "b2ops.h")]
+    if not force and _newer(LIB, deps):
+        return LIB
+    os.makedirs(LIB_DIR, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+        ["-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB] + sources()
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose:
+        sys.stderr.write(proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

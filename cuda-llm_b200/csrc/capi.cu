@@ -1,0 +1,311 @@
+// The C ABI (include/b2ops.h): argument validation, error reporting and dispatch to
+// the kernel launchers.  Nothing here allocates, synchronises or copies to the host,
+// except b2_alloc / b2_free.
+#include "b2ops.h"
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <unordered_map>
+
+namespace b2 {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+}
+
+int launch_status(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return B2_OK;
+  set_error("%s: CUDA error: %s", what, cudaGetErrorString(e));
+  return B2_ERR_CUDA;
+}
+
+int sm_count() {
+  static thread_local int cached_device = -1, cached = kSmCount;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return kSmCount; }
+  if (device != cached_device) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && n > 0) cached = n;
+    else { cudaGetLastError(); cached = kSmCount; }
+    cached_device = device;
+  }
+  return cached;
+}
+
+namespace {
+
+int invalid(const char* op, const char* why) {
+  set_error("%s: %s", op, why);
+  return B2_ERR_INVALID;
+}
+bool dtype_ok(int dtype) { return dtype == B2_F32 || dtype == B2_F16; }
+bool mode_ok(int mode) { return mode == B2_FAST || mode == B2_DETERMINISTIC; }
+cudaStream_t as_stream(b2_stream s) { return static_cast<cudaStream_t>(s); }
+// products of validated, non-negative sizes must stay addressable
+bool fits(int64_t a, int64_t b) { return a == 0 || b <= (int64_t(1) << 46) / a; }
+
+#define B2_REQUIRE(cond, op, why) do { if (!(cond)) return invalid(op, why); } while (0)
+
+std::mutex g_alloc_mutex;
+b2_alloc_stats g_alloc_stats = {0, 0, 0, 0, 0, 0};
+std::unordered_map<void*, size_t> g_alloc_sizes;
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int b2_version(void) { return 100; }
+const char* b2_last_error(void) { return g_error; }
+const char* b2_status_string(int status) {
+  switch (status) {
+    case B2_OK: return "ok";
+    case B2_ERR_INVALID: return "invalid argument";
+    case B2_ERR_CUDA: return "CUDA error";
+    case B2_ERR_UNSUPPORTED: return "unsupported";
+    case B2_ERR_TOO_LARGE: return "beyond a fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+int b2_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int64_t hidden, float eps, int dtype,
+                int mode, b2_stream stream) {
+  const char* op = "b2_rms_norm";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(rows >= 0 && hidden > 0 && fits(rows, hidden), op, "rows must be >= 0 and hidden > 0");
+  B2_REQUIRE(eps > 0.0f, op, "eps must be positive");
+  B2_REQUIRE(rows == 0 || (x && weight && out), op, "null pointer");
+  return launch_rms_norm(x, weight, out, rows, hidden, eps, dtype, mode, as_stream(stream));
+}
+
+int b2_add_rms_norm(const void* lhs, const void* rhs, const void* weight, void* residual, void* normalized,
+                    int64_t rows, int64_t hidden, float eps, int dtype, int mode, b2_stream stream) {
+  const char* op = "b2_add_rms_norm";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(rows >= 0 && hidden > 0 && fits(rows, hidden), op, "rows must be >= 0 and hidden > 0");
+  B2_REQUIRE(eps > 0.0f, op, "eps must be positive");
+  B2_REQUIRE(rows == 0 || (lhs && rhs && weight && residual && normalized), op, "null pointer");
+  B2_REQUIRE(rows == 0 || residual != normalized, op, "residual and normalized must be distinct buffers");
+  return launch_add_rms_norm(lhs, rhs, weight, residual, normalized, rows, hidden, eps, dtype, mode,
+                             as_stream(stream));
+}
+
+int b2_add(const void* a, const void* b, void* out, int64_t count, int dtype, b2_stream stream) {
+  const char* op = "b2_add";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(count >= 0 && count <= (int64_t(1) << 46), op, "count out of range");
+  B2_REQUIRE(count == 0 || (a && b && out), op, "null pointer");
+  return launch_add(a, b, out, count, dtype, as_stream(stream));
+}
+
+int b2_swiglu(const void* gate, const void* up, void* out, int64_t count, int dtype, int mode, b2_stream stream) {
+  const char* op = "b2_swiglu";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(count >= 0 && count <= (int64_t(1) << 46), op, "count out of range");
+  B2_REQUIRE(count == 0 || (gate && up && out), op, "null pointer");
+  return launch_swiglu(gate, up, out, count, dtype, mode, as_stream(stream));
+}
+
+int b2_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads, int64_t head_dim,
+            float theta, int dtype, int mode, b2_stream stream) {
+  const char* op = "b2_rope";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(tokens >= 0 && heads > 0 && head_dim > 0 && fits(tokens, heads * head_dim) && heads * head_dim < (1 << 30),
+             op, "tokens must be >= 0, heads and head_dim > 0");
+  B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
+  B2_REQUIRE(theta > 0.0f, op, "theta must be positive");
+  B2_REQUIRE(tokens == 0 || (x && positions && out), op, "null pointer");
+  return launch_rope(x, positions, out, tokens, heads, head_dim, 0, theta, dtype, mode, as_stream(stream));
+}
+
+int b2_rope_batched(const void* x, const int32_t* positions, void* out, int64_t batch, int64_t seq, int64_t heads,
+                    int64_t head_dim, float theta, int dtype, int mode, b2_stream stream) {
+  const char* op = "b2_rope_batched";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(batch >= 0 && seq > 0 && heads > 0 && head_dim > 0 && fits(batch, seq) &&
+                 fits(batch * seq, heads * head_dim) && heads * head_dim < (1 << 30),
+             op, "batch must be >= 0, seq, heads and head_dim > 0");
+  B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
+  B2_REQUIRE(theta > 0.0f, op, "theta must be positive");
+  B2_REQUIRE(batch == 0 || (x && positions && out), op, "null pointer");
+  return launch_rope(x, positions, out, batch * seq, heads, head_dim, seq, theta, dtype, mode, as_stream(stream));
+}
+
+int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                    const int32_t* positions, void* q_out, void* k_out, int64_t tokens, int64_t q_heads,
+                    int64_t k_heads, int64_t head_dim, float eps, float theta, int dtype, b2_stream stream) {
+  const char* op = "b2_qk_norm_rope";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(tokens >= 0 && q_heads > 0 && k_heads >= 0 && head_dim > 0 &&
+                 fits(tokens, (q_heads + k_heads) * head_dim) && (q_heads + k_heads) * head_dim < (1 << 30),
+             op, "tokens and k_heads must be >= 0, q_heads and head_dim > 0");
+  B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
+  B2_REQUIRE(eps > 0.0f, op, "eps must be positive");
+  B2_REQUIRE(theta > 0.0f, op, "theta must be positive");
+  B2_REQUIRE(tokens == 0 || (q && q_weight && q_out && positions), op, "null pointer");
+  B2_REQUIRE(tokens == 0 || k_heads == 0 || (k && k_weight && k_out), op, "null key pointer with k_heads > 0");
+  return launch_qk_norm_rope(q, k, q_weight, k_weight, positions, q_out, k_out, tokens, q_heads, k_heads, head_dim,
+                             eps, theta, dtype, as_stream(stream));
+}
+
+int b2_embedding_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden,
+                        int64_t vocab, int dtype, int32_t* status, b2_stream stream) {
+  const char* op = "b2_embedding_gather";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(count >= 0 && hidden > 0 && vocab > 0 && fits(count, hidden) && fits(vocab, hidden), op,
+             "count must be >= 0, hidden and vocab > 0");
+  B2_REQUIRE(count == 0 || (table && ids && out), op, "null pointer");
+  return launch_gather(table, ids, out, count, hidden, vocab, dtype, status, as_stream(stream));
+}
+
+size_t b2_argmax_workspace_bytes(int64_t rows) { return rows > 0 ? argmax_workspace_bytes(rows) : 0; }
+
+int b2_argmax_workspace_init(void* workspace, int64_t rows, b2_stream stream) {
+  const char* op = "b2_argmax_workspace_init";
+  B2_REQUIRE(rows >= 0, op, "rows must be >= 0");
+  if (rows == 0) return B2_OK;
+  B2_REQUIRE(workspace != nullptr, op, "null pointer");
+  if (cudaMemsetAsync(workspace, 0, argmax_workspace_bytes(rows), as_stream(stream)) != cudaSuccess)
+    return launch_status(op);
+  return B2_OK;
+}
+
+static int argmax_checks(const char* op, const void* logits, int64_t rows, int64_t width, int64_t row_stride,
+                         int dtype, int64_t index_base, const void* out, const void* workspace) {
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(rows >= 0 && width > 0 && row_stride >= width && fits(rows, row_stride) && rows < (1 << 24), op,
+             "rows must be >= 0, width > 0 and row_stride >= width");
+  B2_REQUIRE(index_base >= 0 && index_base + width <= 0xffffffffll, op, "global indices must fit 32 bits");
+  B2_REQUIRE(rows == 0 || (logits && out && workspace), op, "null pointer");
+  return B2_OK;
+}
+
+int b2_argmax_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, int32_t* out_ids,
+                   void* workspace, b2_stream stream) {
+  const int rc = argmax_checks("b2_argmax_rows", logits, rows, width, row_stride, dtype, 0, out_ids, workspace);
+  if (rc != B2_OK) return rc;
+  B2_REQUIRE(width <= 0x7fffffffll, "b2_argmax_rows", "width must fit int32");
+  return launch_argmax(logits, rows, width, row_stride, dtype, 0, out_ids, nullptr, workspace, as_stream(stream));
+}
+
+int b2_argmax_keys(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, int64_t index_base,
+                   int64_t* keys, void* workspace, b2_stream stream) {
+  const int rc = argmax_checks("b2_argmax_keys", logits, rows, width, row_stride, dtype, index_base, keys, workspace);
+  if (rc != B2_OK) return rc;
+  B2_REQUIRE(width <= 0x7fffffffll, "b2_argmax_keys", "width must fit int32");
+  return launch_argmax(logits, rows, width, row_stride, dtype, index_base, nullptr, keys, workspace, as_stream(stream));
+}
+
+int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out_ids, b2_stream stream) {
+  const char* op = "b2_argmax_decode_keys";
+  B2_REQUIRE(rows >= 0, op, "rows must be >= 0");
+  B2_REQUIRE(rows == 0 || (keys && out_ids), op, "null pointer");
+  return launch_argmax_decode(keys, rows, out_ids, as_stream(stream));
+}
+
+size_t b2_softmax_workspace_bytes(int64_t rows) { return rows > 0 ? softmax_workspace_bytes(rows) : 0; }
+
+int b2_softmax_rows(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode, void* workspace,
+                    b2_stream stream) {
+  const char* op = "b2_softmax_rows";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width) && rows < (1 << 24), op, "rows must be >= 0 and width > 0");
+  B2_REQUIRE(rows == 0 || (x && out && workspace), op, "null pointer");
+  return launch_softmax(x, out, rows, width, dtype, mode, workspace, as_stream(stream));
+}
+
+int b2_softmax_stats(const void* x, int64_t rows, int64_t width, int dtype, float* row_max, float* row_sum,
+                     b2_stream stream) {
+  const char* op = "b2_softmax_stats";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width), op, "rows must be >= 0 and width > 0");
+  B2_REQUIRE(rows == 0 || (x && row_max && row_sum), op, "null pointer");
+  return launch_softmax_stats(x, rows, width, dtype, row_max, row_sum, as_stream(stream));
+}
+
+int b2_softmax_rebase(const float* row_max, const float* global_max, float* row_sum, int64_t rows, b2_stream stream) {
+  const char* op = "b2_softmax_rebase";
+  B2_REQUIRE(rows >= 0, op, "rows must be >= 0");
+  B2_REQUIRE(rows == 0 || (row_max && global_max && row_sum), op, "null pointer");
+  return launch_softmax_rebase(row_max, global_max, row_sum, rows, as_stream(stream));
+}
+
+int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
+                     const float* row_sum, b2_stream stream) {
+  const char* op = "b2_softmax_apply";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width), op, "rows must be >= 0 and width > 0");
+  B2_REQUIRE(rows == 0 || (x && out && row_max && row_sum), op, "null pointer");
+  return launch_softmax_apply(x, out, rows, width, dtype, row_max, row_sum, as_stream(stream));
+}
+
+void* b2_alloc(size_t bytes) {
+  void* p = nullptr;
+  const cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    set_error("b2_alloc: CUDA error: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  g_alloc_sizes[p] = bytes;
+  ++g_alloc_stats.malloc_calls;
+  g_alloc_stats.allocated_bytes_total += bytes;
+  g_alloc_stats.live_bytes += bytes;
+  if (g_alloc_stats.live_bytes > g_alloc_stats.peak_live_bytes) g_alloc_stats.peak_live_bytes = g_alloc_stats.live_bytes;
+  return p;
+}
+
+int b2_free(void* ptr) {
+  if (ptr == nullptr) return B2_OK;
+  const cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) {
+    set_error("b2_free: CUDA error: %s", cudaGetErrorString(e));
+    return B2_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  const auto it = g_alloc_sizes.find(ptr);
+  if (it != g_alloc_sizes.end()) {
+    ++g_alloc_stats.free_calls;
+    g_alloc_stats.freed_bytes_total += it->second;
+    g_alloc_stats.live_bytes -= it->second;
+    g_alloc_sizes.erase(it);
+  }
+  return B2_OK;
+}
+
+void b2_get_alloc_stats(b2_alloc_stats* out) {
+  if (out == nullptr) return;
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  *out = g_alloc_stats;
+}
+
+// Allocations that are live at the reset are the baseline of the new measurement
+// window: the peak restarts from the current live bytes (reference src/tensor_cuda.cu:16-25).
+void b2_reset_alloc_stats(void) {
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  g_alloc_stats.malloc_calls = g_alloc_stats.free_calls = 0;
+  g_alloc_stats.allocated_bytes_total = g_alloc_stats.freed_bytes_total = 0;
+  g_alloc_stats.peak_live_bytes = g_alloc_stats.live_bytes;
+}
+
+}  // extern "C"

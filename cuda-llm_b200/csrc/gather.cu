@@ -1,0 +1,75 @@
+// Embedding-row gather for sm_100a: out[t,:] = table[ids[t],:], bit-exact.
+// One warp copies one row at a time in 16-byte vectors, four loads in flight per
+// lane; the id is read once per row instead of once per element, and there is no
+// per-element integer division.  An id outside [0, vocab) is never dereferenced:
+// its row is zero-filled and a status bit is raised.
+//
+// Replaces reference kernel embeddingk<T> (src/ops_cuda.cu:564), which moves one
+// element per thread, divides per element and has no device-side bounds check.
+#include "common.cuh"
+#include "kernels.h"
+#include "b2ops.h"
+
+namespace b2 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+// Rows are `row_bytes` long; kVec selects 16-byte or 4/2-byte units (`unit_t`).
+template <typename unit_t>
+__device__ __forceinline__ unit_t zero_unit();
+template <> __device__ __forceinline__ uint4 zero_unit<uint4>() { return make_uint4(0, 0, 0, 0); }
+template <> __device__ __forceinline__ uint32_t zero_unit<uint32_t>() { return 0u; }
+template <> __device__ __forceinline__ uint16_t zero_unit<uint16_t>() { return 0; }
+
+template <typename unit_t>
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const unit_t* __restrict__ table, const int32_t* __restrict__ ids, unit_t* __restrict__ out,
+                   int64_t count, int64_t units_per_row, int64_t vocab, int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = int64_t(gridDim.x) * (kThreads / kWarpSize);
+  for (int64_t t = int64_t(blockIdx.x) * (kThreads / kWarpSize) + (threadIdx.x >> 5); t < count; t += warps) {
+    const int64_t id = ids[t];
+    unit_t* dst = out + t * units_per_row;
+    if (id < 0 || id >= vocab) {
+      for (int64_t u = lane; u < units_per_row; u += kWarpSize) dst[u] = zero_unit<unit_t>();
+      if (lane == 0 && status != nullptr) atomicOr(status, 1);
+      continue;
+    }
+    const unit_t* src = table + id * units_per_row;
+    int64_t u = lane;
+    for (; u + int64_t(kUnroll - 1) * kWarpSize < units_per_row; u += int64_t(kUnroll) * kWarpSize) {
+      unit_t r[kUnroll];
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k) r[k] = __ldg(src + u + k * kWarpSize);
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k) __stcs(dst + u + k * kWarpSize, r[k]);
+    }
+    for (; u < units_per_row; u += kWarpSize) __stcs(dst + u, __ldg(src + u));
+  }
+}
+
+template <typename unit_t>
+int launch_units(const void* table, const int32_t* ids, void* out, int64_t count, int64_t units_per_row,
+                 int64_t vocab, int32_t* status, cudaStream_t s) {
+  const int warps_per_cta = kThreads / kWarpSize;
+  const int64_t blocks = (count + warps_per_cta - 1) / warps_per_cta, cap = int64_t(sm_count()) * 8;
+  gather_rows_kernel<unit_t><<<unsigned(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+      static_cast<const unit_t*>(table), ids, static_cast<unit_t*>(out), count, units_per_row, vocab, status);
+  return launch_status("embedding_gather");
+}
+
+}  // namespace
+
+int launch_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden, int64_t vocab,
+                  int dtype, int32_t* status, cudaStream_t s) {
+  if (count == 0 || hidden == 0) return B2_OK;
+  const int64_t elem = dtype == B2_F32 ? 4 : 2, row_bytes = hidden * elem;
+  if (row_bytes % 16 == 0 && aligned16(table) && aligned16(out))
+    return launch_units<uint4>(table, ids, out, count, row_bytes / 16, vocab, status, s);
+  if (dtype == B2_F32) return launch_units<uint32_t>(table, ids, out, count, hidden, vocab, status, s);
+  return launch_units<uint16_t>(table, ids, out, count, hidden, vocab, status, s);
+}
+
+}  // namespace b2

@@ -1,0 +1,42 @@
+// Host-side launchers of the sm_100a kernels.  Arguments are already validated by
+// the C ABI layer (capi.cu); each returns B2_OK or B2_ERR_CUDA.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2 {
+
+// norm.cu
+int launch_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t hidden, float eps,
+                    int dtype, int mode, cudaStream_t s);
+int launch_add_rms_norm(const void* lhs, const void* rhs, const void* w, void* residual, void* normalized,
+                        int64_t rows, int64_t hidden, float eps, int dtype, int mode, cudaStream_t s);
+// elementwise.cu
+int launch_add(const void* a, const void* b, void* out, int64_t n, int dtype, cudaStream_t s);
+int launch_swiglu(const void* g, const void* u, void* out, int64_t n, int dtype, int mode, cudaStream_t s);
+// rope.cu: x is [tokens, heads, head_dim]; position of token t is positions[pos_period ? t % pos_period : t]
+int launch_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
+                int64_t head_dim, int64_t pos_period, float theta, int dtype, int mode, cudaStream_t s);
+int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
+                        void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads,
+                        int64_t head_dim, float eps, float theta, int dtype, cudaStream_t s);
+// gather.cu
+int launch_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden,
+                  int64_t vocab, int dtype, int32_t* status, cudaStream_t s);
+// vocab.cu
+size_t argmax_workspace_bytes(int64_t rows);
+int launch_argmax(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                  int64_t index_base, int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s);
+int launch_argmax_decode(const int64_t* keys, int64_t rows, int32_t* out_ids, cudaStream_t s);
+size_t softmax_workspace_bytes(int64_t rows);
+int launch_softmax(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode, void* workspace,
+                   cudaStream_t s);
+int launch_softmax_stats(const void* x, int64_t rows, int64_t width, int dtype, float* row_max, float* row_sum,
+                         cudaStream_t s);
+int launch_softmax_rebase(const float* row_max, const float* global_max, float* row_sum, int64_t rows,
+                          cudaStream_t s);
+int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
+                         const float* row_sum, cudaStream_t s);
+
+}  // namespace b2

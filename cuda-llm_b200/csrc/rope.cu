@@ -1,0 +1,318 @@
+// Rotary embedding (NeoX rotate-half) for sm_100a, alone or fused behind the
+// per-head QK RMSNorm.  A CTA takes a tile of tokens: it first builds the tile's
+// cos/sin table in shared memory, once per (token, frequency) instead of once per
+// (token, head, frequency) as the reference does, then streams every head of those
+// tokens through 16-byte loads and stores.
+//
+// Replaces reference kernels ropek<T>, rope_batched_kernel<T> and
+// rope_decode_batched_kernel<T> (src/ops_cuda.cu:133-135) and, in the fused form,
+// the rmsk<T> launches in front of them (src/qwen3_layer_cuda.cu:289-292).
+#include "common.cuh"
+#include "kernels.h"
+#include "b2ops.h"
+
+#include <cmath>
+
+namespace b2 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxTableHalf = 128;   // inverse-frequency table passed by value: head_dim <= 256
+constexpr int kMaxTileTokens = 8;
+
+struct InvFreq { double v[kMaxTableHalf]; };
+
+// cos/sin of positions[t] * theta^(-2j/D).
+// Fast mode: the angle is formed in fp64 from a host-built table of
+// pow(double(theta), -2j/D) (the same expression as the CPU operator,
+// src/ops_cpu.cpp:11), reduced to [-pi, pi] in fp64 with a two-term 2*pi, and only
+// then handed to the fp32 sincosf: about 1 ulp of fp32 at any position.
+// Deterministic mode: the reference kernel's all-fp32 expression.
+template <bool kOrdered>
+__device__ __forceinline__ float2 rope_cos_sin(int32_t position, int j, int head_dim, float theta,
+                                               const InvFreq& freq, int half) {
+  if (kOrdered) {
+    const float ang = float(position) * powf(theta, -2.f * float(j) / float(head_dim));
+    return make_float2(cosf(ang), sinf(ang));
+  }
+  const double inv = half <= kMaxTableHalf ? freq.v[j]
+                                           : pow(double(theta), -2.0 * double(j) / double(head_dim));
+  const double angle = double(position) * inv;
+  const double two_pi_hi = 6.283185307179586232e+00, two_pi_lo = 2.449293598294706414e-16;
+  const double turns = rint(angle * 1.591549430918953456e-01);
+  double r = fma(-turns, two_pi_hi, angle);
+  r = fma(-turns, two_pi_lo, r);
+  float s, c;
+  sincosf(float(r), &s, &c);
+  return make_float2(c, s);
+}
+
+// rotate one (low, high) pair
+template <bool kOrdered>
+__device__ __forceinline__ void rotate(float a, float b, float2 cs, float& lo, float& hi) {
+  if (kOrdered) {
+    // written as in the reference kernel, contraction left to the compiler as it is there
+    lo = a * cs.x - b * cs.y;
+    hi = b * cs.x + a * cs.y;
+  } else {
+    // individually rounded products, like the CPU operator built without FMA
+    lo = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+    hi = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+  }
+}
+
+struct HeadSet {           // one [tokens, heads, head_dim] tensor with its optional norm weight
+  const void* x; const void* w; void* out; int heads;
+};
+
+// ---------------------------------------------------------------------------
+// Vector kernel.  Work item = one 16-byte vector of the low half of a head plus
+// its partner in the high half.  hv = (head_dim/2)/kPerVec items make one head and
+// are consecutive lanes of one warp (hv is a power of two <= 32), so the fused
+// norm reduces over them with xor-shuffles.  Two tensors (q and k) are served by
+// one launch: items [0, q.heads*hv) of a token belong to q, the rest to k.
+// ---------------------------------------------------------------------------
+template <typename T, bool kNorm, bool kOrdered>
+__global__ void __launch_bounds__(kThreads)
+rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int tile_tokens,
+                   int head_dim, int hv, int64_t pos_period, float eps, float theta,
+                   const __grid_constant__ InvFreq freq) {
+  constexpr int N = Elem<T>::kPerVec;
+  extern __shared__ float2 table[];   // [tile_tokens][half]
+  const int half = head_dim >> 1;
+  const int items_q = q.heads * hv, items_per_token = (q.heads + k.heads) * hv;
+  const int64_t tiles = (tokens + tile_tokens - 1) / tile_tokens;
+  const int vecs_per_head = 2 * hv;
+
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int64_t token0 = tile * tile_tokens;
+    const int here = int(tokens - token0 < tile_tokens ? tokens - token0 : tile_tokens);
+
+    for (int e = threadIdx.x; e < here * half; e += kThreads) {
+      const int tl = e / half, j = e - tl * half;
+      const int64_t t = token0 + tl;
+      const int32_t p = positions[pos_period ? t % pos_period : t];
+      table[e] = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+    }
+    __syncthreads();
+
+    const int work = here * items_per_token;
+    // every lane of a warp runs the same number of steps so the shuffles below are converged
+    for (int base = 0; base < work; base += kThreads) {
+      const int item = base + threadIdx.x;
+      const bool ok = item < work;
+      const int tl = ok ? item / items_per_token : 0;
+      const int in_token = ok ? item - tl * items_per_token : 0;
+      const bool is_k = in_token >= items_q;
+      const HeadSet& set = is_k ? k : q;
+      const int local = is_k ? in_token - items_q : in_token;
+      const int head = local / hv, v = local - head * hv;
+      const size_t head_vec0 = (size_t(token0 + tl) * set.heads + head) * size_t(vecs_per_head);
+      const uint4* src = reinterpret_cast<const uint4*>(set.x) + head_vec0;
+
+      float lo[N], hi[N];
+      if (ok) {
+        const uint4 raw_lo = ld_stream(src + v), raw_hi = ld_stream(src + hv + v);
+        Elem<T>::unpack(raw_lo, lo);
+        Elem<T>::unpack(raw_hi, hi);
+      } else {
+#pragma unroll
+        for (int e = 0; e < N; ++e) lo[e] = hi[e] = 0.0f;
+      }
+
+      if (kNorm) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < N; ++e) ss = fmaf(lo[e], lo[e], ss);
+#pragma unroll
+        for (int e = 0; e < N; ++e) ss = fmaf(hi[e], hi[e], ss);
+        ss = group_sum(ss, hv);
+        const float inv = 1.0f / sqrtf(ss / float(head_dim) + eps);
+        if (ok) {
+          float wl[N], wh[N];
+          const uint4* wv = reinterpret_cast<const uint4*>(set.w);
+          Elem<T>::unpack(ld_reuse(wv + v), wl);
+          Elem<T>::unpack(ld_reuse(wv + hv + v), wh);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            lo[e] = __fmul_rn(__fmul_rn(lo[e], inv), wl[e]);
+            hi[e] = __fmul_rn(__fmul_rn(hi[e], inv), wh[e]);
+          }
+        }
+      }
+
+      if (ok) {
+        const float2* cs = table + tl * half + v * N;
+        float out_lo[N], out_hi[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) rotate<kOrdered>(lo[e], hi[e], cs[e], out_lo[e], out_hi[e]);
+        uint4* dst = reinterpret_cast<uint4*>(set.out) + head_vec0;
+        st_stream(dst + v, Elem<T>::pack(out_lo));
+        st_stream(dst + hv + v, Elem<T>::pack(out_hi));
+      }
+    }
+    __syncthreads();  // the table is rebuilt for the next tile
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Scalar kernel for shapes the vector kernel cannot take (tiny or odd head_dim,
+// unaligned views): one (low, high) pair per thread per step.  With kNorm one warp
+// owns a head and reduces it with shuffles.
+// ---------------------------------------------------------------------------
+template <typename T, bool kOrdered>
+__global__ void __launch_bounds__(kThreads)
+rope_scalar_kernel(const T* x, const int32_t* __restrict__ positions, T* out, int64_t tokens, int64_t heads,
+                   int head_dim, int64_t pos_period, float theta, const __grid_constant__ InvFreq freq) {
+  const int half = head_dim >> 1;
+  const int64_t total = tokens * heads * half;
+  for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < total; i += int64_t(gridDim.x) * kThreads) {
+    const int j = int(i % half);
+    const int64_t th = i / half, t = th / heads;
+    const int32_t p = positions[pos_period ? t % pos_period : t];
+    const float2 cs = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+    const int64_t base = th * head_dim;
+    const float a = Elem<T>::load(x + base + j), b = Elem<T>::load(x + base + half + j);
+    float lo, hi;
+    rotate<kOrdered>(a, b, cs, lo, hi);
+    Elem<T>::store(out + base + j, lo);
+    Elem<T>::store(out + base + half + j, hi);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+norm_rope_scalar_kernel(const T* x, const T* __restrict__ w, const int32_t* __restrict__ positions, T* out,
+                        int64_t tokens, int64_t heads, int head_dim, float eps, float theta,
+                        const __grid_constant__ InvFreq freq) {
+  const int half = head_dim >> 1, lane = threadIdx.x & 31;
+  const int64_t warps = int64_t(gridDim.x) * (kThreads / kWarpSize);
+  for (int64_t th = int64_t(blockIdx.x) * (kThreads / kWarpSize) + (threadIdx.x >> 5); th < tokens * heads;
+       th += warps) {
+    const int64_t base = th * head_dim;
+    const int32_t p = positions[th / heads];
+    float ss = 0.0f;
+    for (int j = lane; j < head_dim; j += kWarpSize) { const float v = Elem<T>::load(x + base + j); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / float(head_dim) + eps);
+    for (int j = lane; j < half; j += kWarpSize) {
+      const float a = __fmul_rn(__fmul_rn(Elem<T>::load(x + base + j), inv), Elem<T>::load(w + j));
+      const float b = __fmul_rn(__fmul_rn(Elem<T>::load(x + base + half + j), inv), Elem<T>::load(w + half + j));
+      const float2 cs = rope_cos_sin<false>(p, j, head_dim, theta, freq, half);
+      float lo, hi;
+      rotate<false>(a, b, cs, lo, hi);
+      // a lane reads both of its elements before it writes either: in-place use is safe
+      Elem<T>::store(out + base + j, lo);
+      Elem<T>::store(out + base + half + j, hi);
+    }
+  }
+}
+
+InvFreq make_table(int64_t head_dim, float theta) {
+  InvFreq f;
+  const int64_t half = head_dim / 2;
+  for (int64_t j = 0; j < kMaxTableHalf; ++j)
+    f.v[j] = j < half ? std::pow(double(theta), -2.0 * double(j) / double(head_dim)) : 0.0;
+  return f;
+}
+
+template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t half = head_dim / 2;
+  if (half % N != 0) return false;
+  const int64_t hv = half / N;
+  if (hv > 32 || (hv & (hv - 1)) != 0) return false;
+  *hv_out = int(hv);
+  return true;
+}
+
+template <typename T, bool kNorm, bool kOrdered>
+int launch_vector(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv,
+                  int64_t pos_period, float eps, float theta, cudaStream_t s, const char* what) {
+  const int items_per_token = (q.heads + k.heads) * hv;
+  // enough tokens per tile to occupy the CTA once, but a small table
+  int tile_tokens = (kThreads + items_per_token - 1) / items_per_token;
+  if (tile_tokens < 1) tile_tokens = 1;
+  if (tile_tokens > kMaxTileTokens) tile_tokens = kMaxTileTokens;
+  const int64_t tiles = (tokens + tile_tokens - 1) / tile_tokens;
+  const int64_t cap = int64_t(sm_count()) * 8;
+  const unsigned grid = unsigned(tiles < cap ? tiles : cap);
+  const size_t smem = size_t(tile_tokens) * size_t(head_dim / 2) * sizeof(float2);
+  rope_tokens_kernel<T, kNorm, kOrdered><<<grid, kThreads, smem, s>>>(
+      q, k, positions, tokens, tile_tokens, int(head_dim), hv, pos_period, eps, theta, make_table(head_dim, theta));
+  return launch_status(what);
+}
+
+template <typename T>
+int launch_rope_typed(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
+                      int64_t head_dim, int64_t pos_period, float theta, int mode, cudaStream_t s) {
+  if (tokens == 0 || heads == 0 || head_dim == 0) return B2_OK;
+  int hv = 0;
+  const bool vec = vector_shape_ok<T>(head_dim, &hv) && aligned16(x) && aligned16(out) && heads <= (1 << 20);
+  if (vec) {
+    HeadSet q{x, nullptr, out, int(heads)}, none{nullptr, nullptr, nullptr, 0};
+    return mode == B2_DETERMINISTIC
+               ? launch_vector<T, false, true>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, s,
+                                               "rope (deterministic)")
+               : launch_vector<T, false, false>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, s,
+                                                "rope");
+  }
+  const int64_t total = tokens * heads * (head_dim / 2);
+  const int64_t blocks = (total + kThreads - 1) / kThreads, cap = int64_t(sm_count()) * 8;
+  const unsigned grid = unsigned(blocks < cap ? blocks : cap);
+  const InvFreq table = make_table(head_dim, theta);
+  if (mode == B2_DETERMINISTIC)
+    rope_scalar_kernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), positions, static_cast<T*>(out),
+                                                          tokens, heads, int(head_dim), pos_period, theta, table);
+  else
+    rope_scalar_kernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), positions, static_cast<T*>(out),
+                                                           tokens, heads, int(head_dim), pos_period, theta, table);
+  return launch_status("rope (scalar)");
+}
+
+template <typename T>
+int launch_qk_typed(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
+                    void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads, int64_t head_dim,
+                    float eps, float theta, cudaStream_t s) {
+  if (tokens == 0 || head_dim == 0 || q_heads + k_heads == 0) return B2_OK;
+  int hv = 0;
+  const bool vec = vector_shape_ok<T>(head_dim, &hv) && aligned16(q) && aligned16(q_out) && aligned16(qw) &&
+                   (k_heads == 0 || (aligned16(k) && aligned16(k_out) && aligned16(kw))) &&
+                   q_heads + k_heads <= (1 << 20);
+  if (vec) {
+    HeadSet qs{q, qw, q_out, int(q_heads)}, ks{k, kw, k_out, int(k_heads)};
+    return launch_vector<T, true, false>(qs, ks, positions, tokens, head_dim, hv, 0, eps, theta, s, "qk_norm_rope");
+  }
+  const InvFreq table = make_table(head_dim, theta);
+  const int warps_per_cta = kThreads / kWarpSize;
+  const int64_t cap = int64_t(sm_count()) * 8;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int64_t heads = pass == 0 ? q_heads : k_heads;
+    if (heads == 0) continue;
+    const int64_t blocks = (tokens * heads + warps_per_cta - 1) / warps_per_cta;
+    norm_rope_scalar_kernel<T><<<unsigned(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
+        static_cast<const T*>(pass == 0 ? q : k), static_cast<const T*>(pass == 0 ? qw : kw), positions,
+        static_cast<T*>(pass == 0 ? q_out : k_out), tokens, heads, int(head_dim), eps, theta, table);
+  }
+  return launch_status("qk_norm_rope (scalar)");
+}
+
+}  // namespace
+
+int launch_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads, int64_t head_dim,
+                int64_t pos_period, float theta, int dtype, int mode, cudaStream_t s) {
+  return dtype == B2_F32
+             ? launch_rope_typed<float>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, s)
+             : launch_rope_typed<__half>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, s);
+}
+
+int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
+                        void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads, int64_t head_dim,
+                        float eps, float theta, int dtype, cudaStream_t s) {
+  return dtype == B2_F32 ? launch_qk_typed<float>(q, k, qw, kw, positions, q_out, k_out, tokens, q_heads, k_heads,
+                                                  head_dim, eps, theta, s)
+                         : launch_qk_typed<__half>(q, k, qw, kw, positions, q_out, k_out, tokens, q_heads, k_heads,
+                                                   head_dim, eps, theta, s);
+}
+
+}  // namespace b2

@@ -1,0 +1,452 @@
+// Vocabulary-wide row reductions for sm_100a: argmax and softmax over logits
+// [rows, width] with width ~ 150k.
+//
+// argmax   one pass over HBM.  A row is split over several CTAs so that few rows
+//          still fill the machine; each CTA folds its slice to one packed
+//          (value, index) key and merges it with a 64-bit atomicMax; the last CTA
+//          of a row (atomic ticket) publishes the result and re-zeroes the scratch.
+// softmax  fast mode keeps a whole row on chip: a thread-block cluster of up to 8
+//          CTAs holds it in distributed shared memory, exchanges the slice maxima
+//          and sums through DSMEM, and writes the probabilities, so HBM sees one
+//          read and one write.  Rows too long for that, and the vocabulary-sharded
+//          multi-GPU form, use a statistics pass plus an apply pass.
+//          Deterministic mode adds the exponentials in index order in fp32.
+//
+// Replaces reference kernels argmax_partial<T> + argmax_final (src/ops_cuda.cu:562-563,
+// with two cudaMalloc, two cudaFree and a blocking copy per call, :711) and softk<T>
+// (src/ops_cuda.cu:132: one thread per row, strided access).
+#include "common.cuh"
+#include "kernels.h"
+#include "b2ops.h"
+
+#include <cfloat>
+#include <climits>
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace b2 {
+namespace {
+
+// Calls f(value, i) for i in [0, n) of p[], every thread in ascending i.
+// kVec: p is 16-byte aligned; 16-byte loads, four in flight per thread.
+template <typename T, bool kVec, typename F>
+__device__ __forceinline__ void scan_range(const T* p, int64_t n, F&& f) {
+  constexpr int N = Elem<T>::kPerVec;
+  if (kVec) {
+    const int64_t nvec = n / N, step = blockDim.x;
+    const uint4* vp = reinterpret_cast<const uint4*>(p);
+    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += step * 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (v0 + k * step < nvec) r[k] = ld_stream(vp + v0 + k * step);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * step;
+        if (v < nvec) {
+          float e[N];
+          Elem<T>::unpack(r[k], e);
+#pragma unroll
+          for (int q = 0; q < N; ++q) f(e[q], v * N + q);
+        }
+      }
+    }
+    for (int64_t i = nvec * N + threadIdx.x; i < n; i += step) f(Elem<T>::load(p + i), i);
+  } else {
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) f(Elem<T>::load(p + i), i);
+  }
+}
+
+// ===========================================================================
+// argmax
+// ===========================================================================
+
+constexpr int kArgThreads = 256;
+constexpr int kNoIndex = INT_MAX;
+constexpr int64_t kMinChunk = 2048;
+
+// The reference's replacement rule (src/ops_cuda.cu:562): larger value, or equal value
+// and lower index.  (-FLT_MAX, kNoIndex) is "nothing seen" and never beats anything.
+__device__ __forceinline__ bool beats(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+// unsigned key whose order is (value ascending, index descending); 0 = nothing seen
+__device__ __forceinline__ unsigned long long pack_key(float v, uint32_t global_index) {
+  const uint32_t b = __float_as_uint(v);
+  const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return (static_cast<unsigned long long>(ordered) << 32) | (0xffffffffu - global_index);
+}
+constexpr unsigned long long kSignBit = 0x8000000000000000ull;
+
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kArgThreads)
+argmax_rows_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t chunk, int chunks,
+                   int64_t index_base, int32_t* out_ids, int64_t* out_keys, unsigned long long* keys,
+                   unsigned int* tickets) {
+  __shared__ float warp_v[kArgThreads / kWarpSize];
+  __shared__ int warp_i[kArgThreads / kWarpSize];
+  const int64_t row = blockIdx.x / chunks;
+  const int c = int(blockIdx.x - row * chunks);
+  const int64_t lo = int64_t(c) * chunk;
+  const int64_t n = width - lo < chunk ? width - lo : chunk;
+
+  float bv = -FLT_MAX;
+  int bi = kNoIndex;
+  // ascending indices within a thread: strictly-greater alone keeps the lowest index
+  scan_range<T, kVec>(logits + row * row_stride + lo, n, [&](float v, int64_t i) {
+    if (v > bv) { bv = v; bi = int(lo + i); }
+  });
+
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_down_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_down_sync(0xffffffffu, bi, offset);
+    if (beats(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { warp_v[warp] = bv; warp_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  for (int k = 1; k < kArgThreads / kWarpSize; ++k)
+    if (beats(warp_v[k], warp_i[k], bv, bi)) { bv = warp_v[k]; bi = warp_i[k]; }
+
+  unsigned long long key = bi == kNoIndex ? 0ull : pack_key(bv, uint32_t(index_base + bi));
+  if (chunks > 1) {
+    if (key != 0ull) atomicMax(keys + row, key);
+    __threadfence();
+    if (atomicAdd(tickets + row, 1u) != unsigned(chunks - 1)) return;
+    __threadfence();
+    key = atomicExch(keys + row, 0ull);  // read the merged key and leave the scratch zeroed
+    tickets[row] = 0u;
+  }
+  if (out_keys != nullptr) out_keys[row] = static_cast<int64_t>(key ^ kSignBit);
+  if (out_ids != nullptr) out_ids[row] = key == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(key & 0xffffffffull));
+}
+
+__global__ void argmax_decode_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids) {
+  const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const unsigned long long key = static_cast<unsigned long long>(keys[r]) ^ kSignBit;
+  out_ids[r] = key == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(key & 0xffffffffull));
+}
+
+// ===========================================================================
+// softmax
+// ===========================================================================
+
+constexpr int kSoftThreads = 512;
+constexpr size_t kClusterSliceBytes = 100 * 1024;  // two CTAs of a cluster fit one SM's shared memory
+
+// ---- fast mode: one cluster per row, the row stays in distributed shared memory
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kSoftThreads)
+softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
+  constexpr int N = Elem<T>::kPerVec;
+  extern __shared__ __align__(16) float vals[];
+  __shared__ float scratch[32];
+  __shared__ float published[2];  // [0] slice max, [1] slice sum: read by the other CTAs of the cluster
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
+  const int64_t row = blockIdx.x / ranks;
+  const int64_t lo = int64_t(rank) * slice;
+  const int64_t n = lo >= width ? 0 : (width - lo < slice ? width - lo : slice);
+  const T* src = x + row * width + lo;
+  T* dst = out + row * width + lo;
+
+  float m = -INFINITY;
+  scan_range<T, kVec>(src, n, [&](float v, int64_t i) { vals[i] = v; m = fmaxf(m, v); });
+  m = block_max(m, scratch);
+  if (threadIdx.x == 0) published[0] = m;
+  cluster.sync();
+  float row_max = -INFINITY;
+  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, *cluster.map_shared_rank(&published[0], r));
+
+  float s = 0.0f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const float e = expf(vals[i] - row_max);
+    vals[i] = e;
+    s += e;
+  }
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) published[1] = s;
+  cluster.sync();
+  float row_sum = 0.0f;
+  for (unsigned r = 0; r < ranks; ++r) row_sum += *cluster.map_shared_rank(&published[1], r);
+
+  if (kVec) {
+    const int64_t nvec = n / N;
+    for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float o[N];
+#pragma unroll
+      for (int q = 0; q < N; ++q) o[q] = __fdiv_rn(vals[v * N + q], row_sum);
+      st_stream(reinterpret_cast<uint4*>(dst) + v, Elem<T>::pack(o));
+    }
+    for (int64_t i = nvec * N + threadIdx.x; i < n; i += blockDim.x) Elem<T>::store(dst + i, __fdiv_rn(vals[i], row_sum));
+  } else {
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) Elem<T>::store(dst + i, __fdiv_rn(vals[i], row_sum));
+  }
+  cluster.sync();  // nobody leaves while a neighbour may still read its published[]
+}
+
+// ---- row statistics (max, sum of exp(x - max)), one CTA per row, one pass, online rescaling
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kSoftThreads)
+softmax_stats_kernel(const T* x, int64_t width, float* row_max, float* row_sum) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  float m = -INFINITY, s = 0.0f;
+  scan_range<T, kVec>(x + row * width, width, [&](float v, int64_t) {
+    if (v > m) { s *= expf(m - v); m = v; }   // first element: s = 0 * exp(-inf) = 0
+    if (m != -INFINITY) s += expf(v - m);     // a run of leading -inf (masked) entries adds nothing
+  });
+  const float big = block_max(m, scratch);
+  if (m != -INFINITY) s *= expf(m - big); else s = 0.0f;
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) { row_max[row] = big; row_sum[row] = s; }
+}
+
+__global__ void softmax_rebase_kernel(const float* row_max, const float* global_max, float* row_sum, int64_t rows) {
+  const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r < rows) row_sum[r] = row_max[r] == -INFINITY ? 0.0f : row_sum[r] * expf(row_max[r] - global_max[r]);
+}
+
+// ---- out = exp(x - max[r]) / sum[r]; blockIdx = row * tiles + tile
+constexpr int kApplyThreads = 256, kApplyVecs = 4;
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kApplyThreads)
+softmax_apply_kernel(const T* x, T* out, int64_t width, int tiles, int64_t tile_elems, const float* row_max,
+                     const float* row_sum) {
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t row = blockIdx.x / tiles;
+  const int64_t lo = int64_t(blockIdx.x - row * tiles) * tile_elems;
+  const int64_t n = width - lo < tile_elems ? width - lo : tile_elems;
+  const float m = row_max[row], z = row_sum[row];
+  const T* src = x + row * width + lo;
+  T* dst = out + row * width + lo;
+  if (kVec) {
+    const int64_t nvec = n / N;
+    uint4 raw[kApplyVecs];
+#pragma unroll
+    for (int k = 0; k < kApplyVecs; ++k) {
+      const int64_t v = threadIdx.x + k * kApplyThreads;
+      if (v < nvec) raw[k] = ld_stream(reinterpret_cast<const uint4*>(src) + v);
+    }
+#pragma unroll
+    for (int k = 0; k < kApplyVecs; ++k) {
+      const int64_t v = threadIdx.x + k * kApplyThreads;
+      if (v < nvec) {
+        float e[N];
+        Elem<T>::unpack(raw[k], e);
+#pragma unroll
+        for (int q = 0; q < N; ++q) e[q] = __fdiv_rn(expf(e[q] - m), z);
+        st_stream(reinterpret_cast<uint4*>(dst) + v, Elem<T>::pack(e));
+      }
+    }
+    for (int64_t i = nvec * N + threadIdx.x; i < n; i += kApplyThreads)
+      Elem<T>::store(dst + i, __fdiv_rn(expf(Elem<T>::load(src + i) - m), z));
+  } else {
+    for (int64_t i = threadIdx.x; i < n; i += kApplyThreads)
+      Elem<T>::store(dst + i, __fdiv_rn(expf(Elem<T>::load(src + i) - m), z));
+  }
+}
+
+// ---- deterministic mode: the reference's order (src/ops_cuda.cu:132; src/ops_cpu.cpp:13).
+// max by fmaxf from -FLT_MAX; e_j = expf(x_j - max) stored rounded; fp32 running sum of
+// the unrounded e_j in index order; out_j = round(float(stored e_j) / sum).
+constexpr int kOrdThreads = 256, kOrdChunk = 2048;
+template <typename T>
+__global__ void __launch_bounds__(kOrdThreads) softmax_ordered_kernel(const T* x, T* out, int64_t width) {
+  __shared__ float stage[kOrdChunk];
+  __shared__ float scratch[32];
+  __shared__ float total;
+  const T* src = x + int64_t(blockIdx.x) * width;
+  T* dst = out + int64_t(blockIdx.x) * width;
+  float m = -FLT_MAX;
+  for (int64_t i = threadIdx.x; i < width; i += kOrdThreads) m = fmaxf(m, Elem<T>::load(src + i));
+  m = block_max(m, scratch);
+  float sum = 0.0f;  // meaningful in thread 0 only
+  for (int64_t base = 0; base < width; base += kOrdChunk) {
+    const int n = int(width - base < kOrdChunk ? width - base : kOrdChunk);
+    for (int j = threadIdx.x; j < n; j += kOrdThreads) {
+      const float e = expf(Elem<T>::load(src + base + j) - m);
+      Elem<T>::store(dst + base + j, e);
+      stage[j] = e;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int j = 0; j < n; ++j) sum += stage[j];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) total = sum;
+  __syncthreads();
+  const float z = total;
+  // every thread re-reads exactly the elements it stored itself
+  for (int64_t i = threadIdx.x; i < width; i += kOrdThreads) Elem<T>::store(dst + i, __fdiv_rn(Elem<T>::load(dst + i), z));
+}
+
+template <typename T> bool rows_vector_ok(const void* p, int64_t row_stride) {
+  return aligned16(p) && (row_stride * int64_t(sizeof(T))) % 16 == 0;
+}
+
+// ---------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------
+
+template <typename T>
+int launch_argmax_typed(const void* logits_, int64_t rows, int64_t width, int64_t row_stride, int64_t index_base,
+                        int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  const T* logits = static_cast<const T*>(logits_);
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t target = int64_t(sm_count()) * 8;
+  int64_t chunks = target / rows;
+  const int64_t most = (width + kMinChunk - 1) / kMinChunk;
+  if (chunks > most) chunks = most;
+  if (chunks < 1) chunks = 1;
+  int64_t chunk = (width + chunks - 1) / chunks;
+  chunk = (chunk + 4 * N - 1) / (4 * N) * (4 * N);  // chunk starts stay 16-byte aligned
+  chunks = (width + chunk - 1) / chunk;
+  auto* keys = static_cast<unsigned long long*>(workspace);
+  auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
+  const unsigned grid = unsigned(rows * chunks);
+  if (rows_vector_ok<T>(logits, row_stride))
+    argmax_rows_kernel<T, true><<<grid, kArgThreads, 0, s>>>(logits, width, row_stride, chunk, int(chunks), index_base,
+                                                            out_ids, out_keys, keys, tickets);
+  else
+    argmax_rows_kernel<T, false><<<grid, kArgThreads, 0, s>>>(logits, width, row_stride, chunk, int(chunks), index_base,
+                                                             out_ids, out_keys, keys, tickets);
+  return launch_status("argmax_rows");
+}
+
+template <typename T, bool kVec>
+int launch_softmax_cluster(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
+  auto kernel = softmax_cluster_kernel<T, kVec>;
+  const size_t smem = size_t(slice) * sizeof(float);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(rows * ranks));
+  cfg.blockDim = dim3(slice <= 4096 ? 128 : kSoftThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(ranks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, x, out, width, slice) != cudaSuccess) {
+    cudaGetLastError();  // the two-pass path takes over
+    return B2_ERR_UNSUPPORTED;
+  }
+  return B2_OK;
+}
+
+template <typename T>
+int launch_stats_typed(const void* x, int64_t rows, int64_t width, float* row_max, float* row_sum, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  if (rows_vector_ok<T>(x, width))
+    softmax_stats_kernel<T, true><<<unsigned(rows), kSoftThreads, 0, s>>>(static_cast<const T*>(x), width, row_max, row_sum);
+  else
+    softmax_stats_kernel<T, false><<<unsigned(rows), kSoftThreads, 0, s>>>(static_cast<const T*>(x), width, row_max, row_sum);
+  return launch_status("softmax_stats");
+}
+
+template <typename T>
+int launch_apply_typed(const void* x, void* out, int64_t rows, int64_t width, const float* row_max,
+                       const float* row_sum, cudaStream_t s) {
+  if (rows == 0 || width == 0) return B2_OK;
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t tile_elems = int64_t(kApplyThreads) * kApplyVecs * N;
+  const int64_t tiles = (width + tile_elems - 1) / tile_elems;
+  const unsigned grid = unsigned(rows * tiles);
+  if (rows_vector_ok<T>(x, width) && aligned16(out))
+    softmax_apply_kernel<T, true><<<grid, kApplyThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(out), width,
+                                                                int(tiles), tile_elems, row_max, row_sum);
+  else
+    softmax_apply_kernel<T, false><<<grid, kApplyThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(out), width,
+                                                                 int(tiles), tile_elems, row_max, row_sum);
+  return launch_status("softmax_apply");
+}
+
+template <typename T>
+int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width, int mode, void* workspace,
+                         cudaStream_t s) {
+  if (rows == 0 || width == 0) return B2_OK;
+  const T* x = static_cast<const T*>(x_);
+  T* out = static_cast<T*>(out_);
+  constexpr int N = Elem<T>::kPerVec;
+  if (mode == B2_DETERMINISTIC) {
+    softmax_ordered_kernel<T><<<unsigned(rows), kOrdThreads, 0, s>>>(x, out, width);
+    return launch_status("softmax (deterministic)");
+  }
+  // smallest cluster whose slices fit, then widened (up to 8) while rows alone cannot fill the SMs
+  int ranks = 1;
+  while (ranks < 8 && size_t((width + ranks - 1) / ranks) * sizeof(float) > kClusterSliceBytes) ranks <<= 1;
+  while (ranks < 8 && rows * ranks < int64_t(sm_count()) * 2 && width / (ranks * 2) >= 1024) ranks <<= 1;
+  int64_t slice = (width + ranks - 1) / ranks;
+  slice = (slice + N - 1) / N * N;
+  if (size_t(slice) * sizeof(float) <= kClusterSliceBytes) {
+    const bool vec = rows_vector_ok<T>(x, width) && aligned16(out);
+    const int rc = vec ? launch_softmax_cluster<T, true>(x, out, rows, width, ranks, slice, s)
+                       : launch_softmax_cluster<T, false>(x, out, rows, width, ranks, slice, s);
+    if (rc == B2_OK) return B2_OK;
+  }
+  float* row_max = static_cast<float*>(workspace);
+  float* row_sum = row_max + rows;
+  const int rc = launch_stats_typed<T>(x, rows, width, row_max, row_sum, s);
+  if (rc != B2_OK) return rc;
+  return launch_apply_typed<T>(x, out, rows, width, row_max, row_sum, s);
+}
+
+}  // namespace
+
+size_t argmax_workspace_bytes(int64_t rows) {
+  const size_t raw = size_t(rows) * (sizeof(unsigned long long) + sizeof(unsigned int));
+  return (raw + 15) / 16 * 16;
+}
+
+int launch_argmax(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, int64_t index_base,
+                  int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s) {
+  return dtype == B2_F32
+             ? launch_argmax_typed<float>(logits, rows, width, row_stride, index_base, out_ids, out_keys, workspace, s)
+             : launch_argmax_typed<__half>(logits, rows, width, row_stride, index_base, out_ids, out_keys, workspace, s);
+}
+
+int launch_argmax_decode(const int64_t* keys, int64_t rows, int32_t* out_ids, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  argmax_decode_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(keys, rows, out_ids);
+  return launch_status("argmax_decode_keys");
+}
+
+size_t softmax_workspace_bytes(int64_t rows) { return (size_t(rows) * 2 * sizeof(float) + 15) / 16 * 16; }
+
+int launch_softmax(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode, void* workspace,
+                   cudaStream_t s) {
+  return dtype == B2_F32 ? launch_softmax_typed<float>(x, out, rows, width, mode, workspace, s)
+                         : launch_softmax_typed<__half>(x, out, rows, width, mode, workspace, s);
+}
+
+int launch_softmax_stats(const void* x, int64_t rows, int64_t width, int dtype, float* row_max, float* row_sum,
+                         cudaStream_t s) {
+  return dtype == B2_F32 ? launch_stats_typed<float>(x, rows, width, row_max, row_sum, s)
+                         : launch_stats_typed<__half>(x, rows, width, row_max, row_sum, s);
+}
+
+int launch_softmax_rebase(const float* row_max, const float* global_max, float* row_sum, int64_t rows, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  softmax_rebase_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(row_max, global_max, row_sum, rows);
+  return launch_status("softmax_rebase");
+}
+
+int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
+                         const float* row_sum, cudaStream_t s) {
+  return dtype == B2_F32 ? launch_apply_typed<float>(x, out, rows, width, row_max, row_sum, s)
+                         : launch_apply_typed<__half>(x, out, rows, width, row_max, row_sum, s);
+}
+
+}  // namespace b2

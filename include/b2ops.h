@@ -1,0 +1,209 @@
+/*
+ * b2ops — C ABI of the B200 (sm_100a) tensor-op library.
+ *
+ * Drop-in boundary for the memory-bound operators of cuda-llm's op library.  The
+ * reference has no FFI of its own: its operator API is the C++ header
+ * include/llm/ops_cuda.h.  Each entry point below is the raw-pointer form of one
+ * kernel family behind that header and names the reference interface it replaces
+ * (paths are relative to the reference tree).  The C++ functions with the
+ * reference's own signatures (include/llm/ops_cuda.h in this repository) validate
+ * their llm::Tensor arguments and forward here.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless a parameter says "host".
+ *   - Tensors are dense and row-major.  dtype: B2_F32 or B2_F16 storage; all
+ *     arithmetic is fp32 (fp64 where the deterministic mode needs it).
+ *   - Entry points never allocate, never synchronise and never copy to the host,
+ *     so all of them may be recorded into a CUDA graph; scratch memory is passed
+ *     in by the caller.  (b2_alloc/b2_free and the *_host helpers are the only
+ *     exceptions and say so.)
+ *   - `stream` is a cudaStream_t.  NULL means the calling thread's default stream
+ *     (the library is built with per-thread default streams, like the reference:
+ *     its CMakeLists.txt:9).
+ *   - Return value: B2_OK, or a negative b2_status.  b2_last_error() gives the
+ *     message of the calling thread's most recent failure.  Nothing throws.
+ *   - Outputs may alias inputs element-for-element (in-place use), as the
+ *     reference's callers do (src/qwen3_layer_cuda.cu:323, :703-704).
+ *   - mode: B2_FAST uses parallel fp32 partial sums.  B2_DETERMINISTIC reproduces
+ *     the summation order of the reference's kernels (fp64 running sum in index
+ *     order for the RMSNorm family, fp32 running sum in index order for softmax,
+ *     all-fp32 angles for RoPE) so that bit-level regressions can still be run.
+ */
+#ifndef B2OPS_H_
+#define B2OPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B2_API
+#else
+#define B2_API __attribute__((visibility("default")))
+#endif
+
+typedef enum { B2_F32 = 0, B2_F16 = 1 } b2_dtype;
+typedef enum { B2_FAST = 0, B2_DETERMINISTIC = 1 } b2_mode;
+typedef enum {
+  B2_OK = 0,
+  B2_ERR_INVALID = -1,     /* bad argument: null pointer, size, dtype, eps, theta */
+  B2_ERR_CUDA = -2,        /* the CUDA runtime refused the launch or the call */
+  B2_ERR_UNSUPPORTED = -3, /* valid request that this build has no kernel for */
+  B2_ERR_TOO_LARGE = -4    /* beyond a documented fixed capacity */
+} b2_status;
+
+typedef void* b2_stream; /* cudaStream_t */
+
+B2_API int b2_version(void);
+B2_API const char* b2_last_error(void);
+B2_API const char* b2_status_string(int status);
+
+/* ---- RMSNorm family ------------------------------------------------------ */
+
+/* out[r,:] = (x[r,:] * inv_r) * weight, inv_r = 1/sqrt(mean(x[r,:]^2) + eps).
+ * Covers the hidden-state norm and the per-head QK-norm (rows = tokens*heads,
+ * hidden = head_dim).  eps must be > 0.
+ * Replaces cuda_rms_norm / cuda_rms_norm_out and kernel rmsk<T>
+ * (include/llm/ops_cuda.h:77,113-114; src/ops_cuda.cu:112-131,672-673). */
+B2_API int b2_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int64_t hidden,
+                       float eps, int dtype, int mode, b2_stream stream);
+
+/* v = lhs + rhs; residual = round(v); normalized = RMSNorm(v) * weight.
+ * B2_FAST normalises the unrounded fp32 sum kept in registers; B2_DETERMINISTIC
+ * re-reads the rounded residual exactly as the reference kernel does.
+ * Replaces cuda_add_rms_norm_out and kernel add_rms_normk<T>
+ * (include/llm/ops_cuda.h:117-120; src/ops_cuda.cu:77-99,675-703). */
+B2_API int b2_add_rms_norm(const void* lhs, const void* rhs, const void* weight, void* residual,
+                           void* normalized, int64_t rows, int64_t hidden, float eps, int dtype,
+                           int mode, b2_stream stream);
+
+/* ---- streaming elementwise ----------------------------------------------- */
+
+/* out = a + b.  Replaces cuda_add / cuda_add_out and kernel addk<T>
+ * (include/llm/ops_cuda.h:78,115-116; src/ops_cuda.cu:76,674,704). */
+B2_API int b2_add(const void* a, const void* b, void* out, int64_t count, int dtype, b2_stream stream);
+
+/* out = (gate / (1 + exp(-gate))) * up.  mode B2_DETERMINISTIC uses the
+ * full-accuracy expf and IEEE division for both dtypes (the reference's formula);
+ * B2_FAST uses the hardware exponential for fp16 storage only, which stays inside
+ * half an fp16 ulp.  Replaces cuda_swiglu / cuda_swiglu_out and kernel siluk<T>
+ * (include/llm/ops_cuda.h:79,121-122; src/ops_cuda.cu:100,705-706). */
+B2_API int b2_swiglu(const void* gate, const void* up, void* out, int64_t count, int dtype, int mode,
+                     b2_stream stream);
+
+/* ---- rotary embedding (NeoX rotate-half) ----------------------------------- */
+
+/* x, out: [tokens, heads, head_dim]; positions: int32[tokens], one per token row.
+ * Pairs (i, i + head_dim/2) are rotated by angle positions[t] * theta^(-2i/head_dim).
+ * head_dim must be even, theta > 0.
+ * Replaces cuda_rope (after its host->device copy of the positions),
+ * cuda_rope_batched_positions_out and cuda_rope_token_positions_out, kernels ropek<T>
+ * and rope_decode_batched_kernel<T> (include/llm/ops_cuda.h:80,126-131;
+ * src/ops_cuda.cu:133,135,707,972-990,1083-1102). */
+B2_API int b2_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
+                   int64_t head_dim, float theta, int dtype, int mode, b2_stream stream);
+
+/* x, out: [batch, seq, heads, head_dim]; positions: int32[seq], shared by every
+ * batch entry.  Replaces cuda_rope_batched / cuda_rope_batched_out and kernel
+ * rope_batched_kernel<T> (include/llm/ops_cuda.h:81,123-125; src/ops_cuda.cu:134,708-709). */
+B2_API int b2_rope_batched(const void* x, const int32_t* positions, void* out, int64_t batch,
+                           int64_t seq, int64_t heads, int64_t head_dim, float theta, int dtype,
+                           int mode, b2_stream stream);
+
+/* Fused per-head RMSNorm + RoPE for the query and key projections of one layer:
+ * q [tokens, q_heads, head_dim] with q_weight[head_dim], k [tokens, k_heads,
+ * head_dim] with k_weight[head_dim], positions int32[tokens].  k (with k_weight,
+ * k_out) may be NULL when k_heads == 0.  One pass over HBM instead of the four
+ * the reference makes (cuda_rms_norm_out x2 then cuda_rope_token_positions_out x2,
+ * src/qwen3_layer_cuda.cu:289-292,867-872); the normalised value stays in fp32
+ * registers between the two steps.  Fast mode only. */
+B2_API int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                           const int32_t* positions, void* q_out, void* k_out, int64_t tokens,
+                           int64_t q_heads, int64_t k_heads, int64_t head_dim, float eps, float theta,
+                           int dtype, b2_stream stream);
+
+/* ---- embedding-row gather --------------------------------------------------- */
+
+/* out[t,:] = table[ids[t],:], bit-exact.  An id outside [0, vocab) never reaches
+ * memory: its row is written as zeros and, when `status` is not NULL, bit 0 of
+ * *status is set (the caller zeroes *status beforehand).
+ * Replaces cuda_embedding_lookup, cuda_embedding_lookup_out (after its host-side
+ * bounds check and host->device copy of the ids), cuda_embedding_lookup_device_ids_out
+ * and kernel embeddingk<T> (include/llm/ops_cuda.h:148-156; src/ops_cuda.cu:564,872-884). */
+B2_API int b2_embedding_gather(const void* table, const int32_t* ids, void* out, int64_t count,
+                               int64_t hidden, int64_t vocab, int dtype, int32_t* status,
+                               b2_stream stream);
+
+/* ---- vocabulary-wide reductions -------------------------------------------- */
+
+/* Row argmax with the reference's rule: largest value, ties to the lowest index;
+ * NaN, -inf and -FLT_MAX never win; a row with no winner gives 0.
+ * logits: rows x width, consecutive rows `row_stride` elements apart.
+ * workspace: b2_argmax_workspace_bytes(rows) bytes, zero-filled once before its
+ * first use (b2_argmax_workspace_init); every call leaves it zero-filled again, so
+ * it can be reused by later calls on the same stream.  Calls that share a
+ * workspace must not overlap on the device.
+ * Replaces cuda_argmax_last_row, argmax_row_impl and the temperature == 0 route of
+ * CudaSampler, kernels argmax_partial<T> + argmax_final
+ * (include/llm/ops_cuda.h:154; src/ops_cuda.cu:562-563,711,871,903-909). */
+B2_API size_t b2_argmax_workspace_bytes(int64_t rows);
+B2_API int b2_argmax_workspace_init(void* workspace, int64_t rows, b2_stream stream);
+B2_API int b2_argmax_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                          int32_t* out_ids, void* workspace, b2_stream stream);
+
+/* Vocabulary-sharded form: this GPU holds columns [index_base, index_base + width)
+ * of every row.  keys[r] = packed (value, index_base + local index) such that the
+ * signed 64-bit MAX over all shards' keys is the key of the global winner (one
+ * ncclAllReduce(ncclInt64, ncclMax) of `rows` elements).  b2_argmax_decode_keys
+ * turns reduced keys into int32 indices.  No reference counterpart: the reference
+ * is single-GPU. */
+B2_API int b2_argmax_keys(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                          int64_t index_base, int64_t* keys, void* workspace, b2_stream stream);
+B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out_ids, b2_stream stream);
+
+/* Row softmax over the last dimension: out = exp(x - max) / sum.
+ * B2_FAST keeps each row on chip (a thread-block cluster holds it in distributed
+ * shared memory) when it fits, otherwise makes two passes; B2_DETERMINISTIC adds the
+ * exponentials in index order in fp32, like ops_cpu and the reference kernel.
+ * workspace: b2_softmax_workspace_bytes(rows) bytes (contents irrelevant).
+ * Replaces cuda_softmax_last_dim and kernel softk<T>
+ * (include/llm/ops_cuda.h:82; src/ops_cuda.cu:132,710). */
+B2_API size_t b2_softmax_workspace_bytes(int64_t rows);
+B2_API int b2_softmax_rows(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode,
+                           void* workspace, b2_stream stream);
+
+/* Vocabulary-sharded softmax, three steps around two small all-reduces:
+ *   b2_softmax_stats     row_max[r] = max of the local columns,
+ *                        row_sum[r] = sum exp(x - row_max[r]) over the local columns
+ *   (all-reduce MAX of a copy of row_max -> global_max)
+ *   b2_softmax_rebase    row_sum[r] *= exp(row_max[r] - global_max[r])
+ *   (all-reduce SUM of row_sum -> global_sum)
+ *   b2_softmax_apply     out = exp(x - global_max[r]) / global_sum[r]
+ * No reference counterpart: the reference is single-GPU. */
+B2_API int b2_softmax_stats(const void* x, int64_t rows, int64_t width, int dtype, float* row_max,
+                            float* row_sum, b2_stream stream);
+B2_API int b2_softmax_rebase(const float* row_max, const float* global_max, float* row_sum, int64_t rows,
+                             b2_stream stream);
+B2_API int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype,
+                            const float* row_max, const float* row_sum, b2_stream stream);
+
+/* ---- device memory with the reference's allocation counters ----------------- */
+
+/* cudaMalloc / cudaFree plus the counters of the reference's CudaAllocationStats
+ * (include/llm/tensor.h:9-19; src/tensor_cuda.cu:12-54).  These two DO allocate and
+ * b2_free synchronises like cudaFree. */
+typedef struct {
+  uint64_t malloc_calls, free_calls, allocated_bytes_total, freed_bytes_total, live_bytes, peak_live_bytes;
+} b2_alloc_stats;
+B2_API void* b2_alloc(size_t bytes);
+B2_API int b2_free(void* ptr);
+B2_API void b2_get_alloc_stats(b2_alloc_stats* out);
+B2_API void b2_reset_alloc_stats(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2OPS_H_ */

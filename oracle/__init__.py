@@ -1,0 +1,295 @@
+"""ctypes doors into the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+Only tests/, the smoke check and the bench's CPU-baseline leg may import this
+package; the product (the CUDA library and its host side) never does.
+
+``port``  -> oracle/liboracle.so, the C restatement in oracle.c
+``ref``   -> oracle/_ref/liboracle_ref.so, the reference's own compiled CPU
+             operators (present when oracle/Makefile's ``ref`` target was built
+             where the reference tree exists; the binary then travels with the
+             snapshot).  ``ref`` is None when that binary is absent.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+F32, F16 = 0, 1  # dtype codes, the same as the product's C ABI
+
+
+def build(ref: bool = True) -> None:
+    """Compile oracle.c (and the reference-backed library when its sources exist)."""
+    subprocess.run(["make", "-C", _HERE, "all"] + (["ref"] if ref else []), check=True,
+                   stdout=subprocess.DEVNULL)
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class Port:
+    """The C restatement (oracle.c)."""
+
+    def __init__(self):
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build(ref=False)
+        self.lib = C.CDLL(path)
+        L = self.lib
+        L.orc_decode_f16.restype = C.c_float
+        L.orc_decode_f16.argtypes = [C.c_uint16]
+        L.orc_f32_to_f16_rn.restype = C.c_uint16
+        L.orc_f32_to_f16_rn.argtypes = [C.c_float]
+        L.orc_encode_f16_host.restype = C.c_uint16
+        L.orc_encode_f16_host.argtypes = [C.c_float]
+        L.orc_argmax_row_f32.restype = C.c_int32
+        L.orc_argmax_row_f16.restype = C.c_int32
+        L.orc_argmax_key.restype = C.c_int64
+        L.orc_argmax_key.argtypes = [C.c_float, C.c_int64]
+        L.orc_argmax_key_index.restype = C.c_int32
+        L.orc_argmax_key_index.argtypes = [C.c_int64]
+
+    # --- codecs
+    def decode_f16(self, bits) -> np.ndarray:
+        bits = np.ascontiguousarray(bits, dtype=np.uint16)
+        out = np.empty(bits.shape, np.float32)
+        self.lib.orc_decode_f16_array(_ptr(bits), _ptr(out), C.c_int64(bits.size))
+        return out
+
+    def f32_to_f16_rn(self, x) -> np.ndarray:
+        x = _f32(x)
+        out = np.empty(x.shape, np.uint16)
+        self.lib.orc_f32_to_f16_rn_array(_ptr(x), _ptr(out), C.c_int64(x.size))
+        return out
+
+    # --- CPU operators (fp32)
+    def rms_norm(self, x, w, eps):
+        x, w = _f32(x), _f32(w)
+        h = x.shape[-1]
+        out = np.empty_like(x)
+        self.lib.orc_cpu_rms_norm(_ptr(x), _ptr(w), C.c_float(eps), C.c_int64(x.size // h), C.c_int64(h), _ptr(out))
+        return out
+
+    def add(self, a, b):
+        a, b = _f32(a), _f32(b)
+        out = np.empty_like(a)
+        self.lib.orc_cpu_add(_ptr(a), _ptr(b), C.c_int64(a.size), _ptr(out))
+        return out
+
+    def add_rms_norm(self, lhs, rhs, w, eps):
+        lhs, rhs, w = _f32(lhs), _f32(rhs), _f32(w)
+        h = lhs.shape[-1]
+        res, nrm = np.empty_like(lhs), np.empty_like(lhs)
+        self.lib.orc_cpu_add_rms_norm(_ptr(lhs), _ptr(rhs), _ptr(w), C.c_float(eps), C.c_int64(lhs.size // h),
+                                      C.c_int64(h), _ptr(res), _ptr(nrm))
+        return res, nrm
+
+    def swiglu(self, gate, up):
+        gate, up = _f32(gate), _f32(up)
+        out = np.empty_like(gate)
+        self.lib.orc_cpu_swiglu(_ptr(gate), _ptr(up), C.c_int64(gate.size), _ptr(out))
+        return out
+
+    def rope(self, x, positions, theta):
+        x, positions = _f32(x), _i32(positions)
+        t, h, d = x.shape
+        out = np.empty_like(x)
+        rc = self.lib.orc_cpu_rope(_ptr(x), _ptr(positions), C.c_float(theta), C.c_int64(t), C.c_int64(h),
+                                   C.c_int64(d), _ptr(out))
+        if rc:
+            raise ValueError("rope: head_dim must be even and theta positive")
+        return out
+
+    def softmax(self, x):
+        x = _f32(x)
+        w = x.shape[-1]
+        out = np.empty_like(x)
+        self.lib.orc_cpu_softmax(_ptr(x), C.c_int64(x.size // w), C.c_int64(w), _ptr(out))
+        return out
+
+    def softmax_f64(self, x):
+        x = _f32(x)
+        w = x.shape[-1]
+        out = np.empty(x.shape, np.float64)
+        self.lib.orc_f64_softmax(_ptr(x), C.c_int64(x.size // w), C.c_int64(w), _ptr(out))
+        return out
+
+    def embedding_lookup(self, table, ids):
+        table, ids = _f32(table), _i32(ids)
+        out = np.empty((ids.size, table.shape[1]), np.float32)
+        rc = self.lib.orc_cpu_embedding_lookup(_ptr(table), C.c_int64(table.shape[0]), C.c_int64(table.shape[1]),
+                                               _ptr(ids), C.c_int64(ids.size), _ptr(out))
+        if rc:
+            raise IndexError("embedding_lookup: token id out of range")
+        return out
+
+    def argmax_rows(self, x) -> np.ndarray:
+        """Row argmax with the reference's tie rule; accepts float32 or float16 bit patterns (uint16)."""
+        x = np.ascontiguousarray(x)
+        w = x.shape[-1]
+        rows = x.reshape(-1, w)
+        out = np.empty(rows.shape[0], np.int32)
+        for r in range(rows.shape[0]):
+            if rows.dtype == np.uint16:
+                out[r] = self.lib.orc_argmax_row_f16(_ptr(rows[r]), C.c_int64(w))
+            else:
+                row = _f32(rows[r])
+                out[r] = self.lib.orc_argmax_row_f32(_ptr(row), C.c_int64(w))
+        return out
+
+    def argmax_key(self, value: float, index: int) -> int:
+        return int(self.lib.orc_argmax_key(C.c_float(value), C.c_int64(index)))
+
+    def argmax_key_index(self, key: int) -> int:
+        return int(self.lib.orc_argmax_key_index(C.c_int64(key)))
+
+    # --- device-order arithmetic; arrays are float32 (dtype F32) or uint16 half bits (dtype F16)
+    @staticmethod
+    def _code(a: np.ndarray) -> int:
+        if a.dtype == np.float32:
+            return F32
+        if a.dtype == np.uint16:
+            return F16
+        raise TypeError("device-order oracle takes float32 or uint16 (fp16 bits)")
+
+    def dev_add(self, a, b):
+        a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+        out = np.empty_like(a)
+        self.lib.orc_dev_add(_ptr(a), _ptr(b), C.c_int64(a.size), _ptr(out), C.c_int(self._code(a)))
+        return out
+
+    def dev_rms_norm(self, x, w, eps):
+        x, w = np.ascontiguousarray(x), np.ascontiguousarray(w)
+        h = x.shape[-1]
+        out = np.empty_like(x)
+        self.lib.orc_dev_rms_norm(_ptr(x), _ptr(w), C.c_float(eps), C.c_int64(x.size // h), C.c_int64(h), _ptr(out),
+                                  C.c_int(self._code(x)))
+        return out
+
+    def dev_add_rms_norm(self, lhs, rhs, w, eps):
+        lhs, rhs, w = map(np.ascontiguousarray, (lhs, rhs, w))
+        h = lhs.shape[-1]
+        res, nrm = np.empty_like(lhs), np.empty_like(lhs)
+        self.lib.orc_dev_add_rms_norm(_ptr(lhs), _ptr(rhs), _ptr(w), C.c_float(eps), C.c_int64(lhs.size // h),
+                                      C.c_int64(h), _ptr(res), _ptr(nrm), C.c_int(self._code(lhs)))
+        return res, nrm
+
+
+class Ref:
+    """The reference's own compiled CPU operators (oracle/_ref)."""
+
+    def __init__(self, path: str):
+        self.lib = C.CDLL(path)
+        self.lib.ref_decode_f16.restype = C.c_float
+        self.lib.ref_decode_f16.argtypes = [C.c_uint16]
+        self.lib.ref_encode_f16.restype = C.c_uint16
+        self.lib.ref_encode_f16.argtypes = [C.c_float]
+        self.lib.ref_time_add_rms_norm.restype = C.c_double
+
+    @staticmethod
+    def _ok(rc, what):
+        if rc == -2:
+            raise IndexError(what)
+        if rc:
+            raise ValueError(what)
+
+    def rms_norm(self, x, w, eps):
+        x, w = _f32(x), _f32(w)
+        h = x.shape[-1]
+        out = np.empty_like(x)
+        self._ok(self.lib.ref_rms_norm(_ptr(x), _ptr(w), C.c_float(eps), C.c_int64(x.size // h), C.c_int64(h),
+                                       _ptr(out)), "rms_norm")
+        return out
+
+    def add(self, a, b):
+        a, b = _f32(a), _f32(b)
+        out = np.empty_like(a)
+        self._ok(self.lib.ref_add(_ptr(a), _ptr(b), C.c_int64(a.size), _ptr(out)), "add")
+        return out
+
+    def add_rms_norm(self, lhs, rhs, w, eps):
+        lhs, rhs, w = _f32(lhs), _f32(rhs), _f32(w)
+        h = lhs.shape[-1]
+        res, nrm = np.empty_like(lhs), np.empty_like(lhs)
+        self._ok(self.lib.ref_add_rms_norm(_ptr(lhs), _ptr(rhs), _ptr(w), C.c_float(eps), C.c_int64(lhs.size // h),
+                                           C.c_int64(h), _ptr(res), _ptr(nrm)), "add_rms_norm")
+        return res, nrm
+
+    def time_add_rms_norm(self, lhs, rhs, w, eps, threads: int) -> float:
+        lhs, rhs, w = _f32(lhs), _f32(rhs), _f32(w)
+        h = lhs.shape[-1]
+        res, nrm = np.empty_like(lhs), np.empty_like(lhs)
+        dt = self.lib.ref_time_add_rms_norm(_ptr(lhs), _ptr(rhs), _ptr(w), C.c_float(eps), C.c_int64(lhs.size // h),
+                                            C.c_int64(h), _ptr(res), _ptr(nrm), C.c_int(threads))
+        if dt < 0:
+            raise RuntimeError("reference add+rms_norm failed")
+        return float(dt)
+
+    def hardware_threads(self) -> int:
+        return int(self.lib.ref_hardware_threads())
+
+    def swiglu(self, gate, up):
+        gate, up = _f32(gate), _f32(up)
+        out = np.empty_like(gate)
+        self._ok(self.lib.ref_swiglu(_ptr(gate), _ptr(up), C.c_int64(gate.size), _ptr(out)), "swiglu")
+        return out
+
+    def rope(self, x, positions, theta):
+        x, positions = _f32(x), _i32(positions)
+        t, h, d = x.shape
+        out = np.empty_like(x)
+        self._ok(self.lib.ref_rope(_ptr(x), _ptr(positions), C.c_float(theta), C.c_int64(t), C.c_int64(h),
+                                   C.c_int64(d), _ptr(out)), "rope")
+        return out
+
+    def softmax(self, x):
+        x = _f32(x)
+        w = x.shape[-1]
+        out = np.empty_like(x)
+        self._ok(self.lib.ref_softmax(_ptr(x), C.c_int64(x.size // w), C.c_int64(w), _ptr(out)), "softmax")
+        return out
+
+    def embedding_lookup(self, table, ids):
+        table, ids = _f32(table), _i32(ids)
+        out = np.empty((ids.size, table.shape[1]), np.float32)
+        self._ok(self.lib.ref_embedding_lookup(_ptr(table), C.c_int64(table.shape[0]), C.c_int64(table.shape[1]),
+                                               _ptr(ids), C.c_int64(ids.size), _ptr(out)), "embedding_lookup")
+        return out
+
+    def decode_f16(self, h: int) -> float:
+        return float(self.lib.ref_decode_f16(C.c_uint16(h)))
+
+    def encode_f16(self, x: float) -> int:
+        return int(self.lib.ref_encode_f16(C.c_float(x)))
+
+
+_port = None
+_ref = False
+
+
+def port() -> Port:
+    global _port
+    if _port is None:
+        _port = Port()
+    return _port
+
+
+def ref():
+    """The reference-backed oracle, or None when oracle/_ref was not built."""
+    global _ref
+    if _ref is False:
+        path = os.path.join(_HERE, "_ref", "liboracle_ref.so")
+        _ref = Ref(path) if os.path.exists(path) else None
+    return _ref
