@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-op hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--no-ops]
+
+Headline workload (one "step" = one launch of the fused residual-add + RMSNorm
+kernel over one batch): configuration 2 of the baseline at its largest shape,
+rows = 65536, hidden = 4096, fp16 in/out with fp32 accumulation, per GPU (weak
+scaling: token rows are independent, so ranks share nothing and no collective is
+on the data path).  The working set (2.1 GB per GPU) is far larger than L2.
+
+One JSON line is printed by rank 0.  Beside the contract keys it carries
+  roofline      achieved algorithmic GB/s of the kernel vs the measured HBM copy peak
+  cpu_baseline  the reference's own CPU operators timed on this box's host cores
+  e2e           the same metric with host buffers: pinned H2D of both inputs, the kernel,
+                D2H of both outputs, every step
+  ops           per-operator GB/s (and rows/s) of the other benchmark configurations
+Inputs are synthetic (seeded normal / uniform draws of the named shapes); no dataset is involved.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, HIDDEN = 65536, 4096
+METRIC = "fused_add_rmsnorm_hbm_gbs"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu
+# capture summarised in profiles/ (None until a capture of this build exists).
+HEADLINE_TRAFFIC_BYTES = None
+
+
+def algorithmic_bytes(rows: int, hidden: int, elem: int = 2) -> int:
+    """Two inputs read, two outputs written, one weight vector read."""
+    return 4 * rows * hidden * elem + hidden * elem
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def config_block(n_gpus: int):
+    return {"workload": f"config2 fused residual-add + RMSNorm, rows={ROWS} x hidden={HIDDEN} per GPU, fp16 in/out, "
+                        f"fp32 accumulation, eps=1e-6",
+            "rows_per_gpu": ROWS, "hidden": HIDDEN, "parallelism": f"row-sharded x{n_gpus}, no collective",
+            "l2": "inputs (2.1 GB per GPU) larger than L2, no flush needed"}
+
+
+# ------------------------------------------------------------------------------------------
+# clocks: NVML reads only (never sets anything)
+# ------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline: the reference's own operators (oracle/_ref) or, without them, the C port
+# ------------------------------------------------------------------------------------------
+
+def cpu_baseline(target_seconds: float, steps: int = 1, warmup: int = 0):
+    """Times add + rms_norm as the reference's CPU layer runs them, rows split over all host
+    threads.  Returns (equivalent GB/s of the fp16 workload's algorithmic bytes, description dict)."""
+    import numpy as np
+    import oracle
+    ref = oracle.ref()
+    rng = np.random.default_rng(2000)
+    w = (rng.random(HIDDEN, dtype=np.float32) + np.float32(0.5))
+
+    def make(rows):
+        return rng.standard_normal((rows, HIDDEN), dtype=np.float32), rng.standard_normal((rows, HIDDEN), dtype=np.float32)
+
+    if ref is not None:
+        kind, cores = "reference", max(1, ref.hardware_threads())
+        run = lambda x, r: ref.time_add_rms_norm(x, r, w, 1e-6, cores)
+    else:
+        kind, cores = "port", 1
+        port = oracle.port()
+
+        def run(x, r):
+            t0 = time.perf_counter()
+            port.add_rms_norm(x, r, w, 1e-6)
+            return time.perf_counter() - t0
+    probe_rows = 64 * cores
+    x, r = make(probe_rows)
+    run(x, r)
+    rate = probe_rows / run(x, r)
+    rows = int(min(ROWS, max(probe_rows, rate * target_seconds)))
+    x, r = make(rows)
+    for _ in range(warmup):
+        run(x, r)
+    times = [run(x, r) for _ in range(max(1, steps))]
+    per_step = sum(times) / len(times)
+    gbs = algorithmic_bytes(rows, HIDDEN) / per_step / 1e9
+    return gbs, per_step, {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": kind,
+                           "rows_per_s": round(rows / per_step, 1),
+                           "sample": f"{rows} of {ROWS} rows x hidden {HIDDEN}, fp16 inputs de-quantised to the fp32 the "
+                                     f"CPU operators take; GB/s counts the fp16 workload's algorithmic bytes per row"}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    total = args.steps + args.warmup
+    per_step = min(1.0, 120.0 / max(1, total))
+    gbs, sec, desc = cpu_baseline(per_step, steps=args.steps, warmup=args.warmup)
+    desc["value"] = round(gbs, 4)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_block(args.gpus),
+        "cpu_baseline": desc,
+        "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------
+# the B200 arm
+# ------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--rows", type=int, default=ROWS, help=argparse.SUPPRESS)   # smaller cases for profiler captures
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from cuda_llm_b200 import build, lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    L = lib.load()
+    warmup = max(args.warmup, 3)
+    rows = args.rows
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    stream = torch.cuda.Stream(device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000 + rank)
+    with torch.cuda.stream(stream):
+        x = torch.randn(rows, HIDDEN, device=dev, dtype=torch.float32, generator=gen).half()
+        res = torch.randn(rows, HIDDEN, device=dev, dtype=torch.float32, generator=gen).half()
+        gamma = (torch.rand(HIDDEN, device=dev, generator=gen) + 0.5).half()
+        out_res, out_nrm = torch.empty_like(x), torch.empty_like(x)
+
+        def step():
+            lib.check(L.b2_add_rms_norm(x.data_ptr(), res.data_ptr(), gamma.data_ptr(), out_res.data_ptr(),
+                                        out_nrm.data_ptr(), rows, HIDDEN, 1e-6, lib.F16, lib.FAST, stream.cuda_stream))
+
+        for _ in range(warmup):
+            step()
+        sampler = ClockSampler(local)
+        barrier()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        local_ms = e0.elapsed_time(e1)
+        total_ms = max_over_ranks(local_ms)
+        ms_per_step = total_ms / args.steps
+        alg = algorithmic_bytes(rows, HIDDEN)
+        value = world * alg / (ms_per_step * 1e-3) / 1e9
+        kernel_gbs = alg / (local_ms / args.steps * 1e-3) / 1e9
+
+        # ---- end to end: host buffers in, host buffers out, every step
+        e2e_steps = max(1, min(args.steps, 10))
+        hx = torch.empty(rows, HIDDEN, dtype=torch.float16).pin_memory()
+        hr = torch.empty(rows, HIDDEN, dtype=torch.float16).pin_memory()
+        hx.copy_(x, non_blocking=False)
+        hr.copy_(res, non_blocking=False)
+        h_res, h_nrm = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+
+        def e2e_step():
+            x.copy_(hx, non_blocking=True)
+            res.copy_(hr, non_blocking=True)
+            step()
+            h_res.copy_(out_res, non_blocking=True)
+            h_nrm.copy_(out_nrm, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+        e2e_value = world * alg / (e2e_ms * 1e-3) / 1e9
+        del hx, hr, h_res, h_nrm
+
+        op_table = None
+        if not args.no_ops:
+            from cuda_llm_b200 import opbench
+            del x, res, out_res, out_nrm
+            torch.cuda.empty_cache()
+            op_table = opbench.run(L, lib, dev, stream, world, rank, barrier, max_over_ranks)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak()
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic", "config": config_block(world),
+        "rows_per_s": round(world * rows / (ms_per_step * 1e-3), 1),
+        "frac_of_nominal_8TBs": round(value / world / NOMINAL_HBM_GBS, 4),
+        "roofline": {"bound": "hbm", "achieved": round(kernel_gbs, 2), "peak": peak, "unit": UNIT,
+                     "frac": round(kernel_gbs / peak, 4), "traffic": HEADLINE_TRAFFIC_BYTES, "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": alg, "kernel": "rms_norm_rows_kernel<__half, 2, true>"},
+        "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": 2 * rows * HIDDEN * 2,
+                "d2h_bytes_per_step": 2 * rows * HIDDEN * 2, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+        "gpu_launches": args.steps, "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu:
+        try:
+            _, _, line["cpu_baseline"] = cpu_baseline(10.0)
+        except Exception as exc:  # the baseline is reported, never required for the GPU number
+            line["cpu_baseline"] = {"error": str(exc)}
+    if op_table is not None:
+        line["ops"] = op_table
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

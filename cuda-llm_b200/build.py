@@ -55,3 +55,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+
+
+SHIM_DIR = os.path.join(CSRC, "llm")
+SHIM_LIB = os.path.join(LIB_DIR, "libb2llm.so")
+
+
+def shim_sources():
+    return sorted(glob.glob(os.path.join(SHIM_DIR, "*.cu")) + glob.glob(os.path.join(SHIM_DIR, "*.cpp")))
+
+
+def build_shim(force: bool = False) -> str:
+    """Build lib/libb2llm.so: the C++ functions with the reference's own signatures
+    (namespace llm, headers under include/llm/), linked against libb2ops.so.
+    Returns the path, or "" when the sources are not present."""
+    srcs = shim_sources()
+    if not srcs:
+        return ""
+    build(force=False)
+    deps = srcs + glob.glob(os.path.join(ROOT, "include", "llm", "*.h")) + [LIB]
+    if not force and _newer(SHIM_LIB, deps):
+        return SHIM_LIB
+    nvcc = os.environ.get("NVCC", "nvcc")
+    flags = [f for f in NVCC_FLAGS if f != "-fPIC,-fvisibility=hidden"] + ["-fPIC"]
+    cmd = [nvcc] + flags + ["-x", "cu", "-I", os.path.join(ROOT, "include"), "-o", SHIM_LIB] + srcs + \
+        ["-L", LIB_DIR, "-lb2ops", "-Xlinker", "-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc (shim) failed:\n" + proc.stdout + proc.stderr)
+    return SHIM_LIB

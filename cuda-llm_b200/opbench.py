@@ -1,0 +1,175 @@
+"""Per-operator throughput table of the benchmark configurations (used by bench.py).
+
+Every entry is timed with CUDA events on the launching stream after warm-up, over
+`reps` back-to-back launches.  Working sets smaller than a few times L2 are rotated
+through enough distinct buffer sets to exceed 512 MB, so the bytes really come from
+HBM.  GB/s = algorithmic bytes / time: the bytes an ideal kernel must move (inputs
+read once, outputs written once).
+
+With several ranks the row-independent operators split configuration 4's T tokens
+over the ranks (no collective) and the vocabulary reductions split V over the ranks
+with the NCCL exchange inside the timed region; times are the maximum over ranks.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+VOCAB = 151936
+NOMINAL = 8000.0
+
+
+def _peak():
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        return float(json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
+    from . import sharded
+    peak = _peak()
+    s = stream.cuda_stream
+    F16, F32, FAST = lib.F16, lib.F32, lib.FAST
+    table = []
+    half = torch.float16
+
+    def randn(*shape, sigma=1.0, dtype=half):
+        return (torch.randn(*shape, device=dev, dtype=torch.float32) * sigma).to(dtype)
+
+    def timed(calls, reps, warm=3):
+        """calls: list of zero-argument launchers (one per buffer set); returns ms per launch (max over ranks)."""
+        n = len(calls)
+        for i in range(warm):
+            calls[i % n]()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(reps):
+            calls[i % n]()
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / reps
+
+    def sets_for(bytes_per_set):
+        return max(1, min(8, -(-512 * 1024 * 1024 // max(1, bytes_per_set))))
+
+    def record(op, shape, alg_bytes_local, ms, rows_local=None, note=None, sharded_over=1):
+        gbs = sharded_over * alg_bytes_local / (ms * 1e-3) / 1e9
+        e = {"op": op, "shape": shape, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
+             "frac_measured_copy": round(gbs / sharded_over / peak, 4), "frac_nominal": round(gbs / sharded_over / NOMINAL, 4)}
+        if rows_local is not None:
+            e["rows_per_s"] = round(sharded_over * rows_local / (ms * 1e-3), 1)
+        if note:
+            e["note"] = note
+        table.append(e)
+
+    # ---- configuration 2: fused add + RMSNorm sweep (single-GPU shapes; every rank runs them alike)
+    for rows in (1, 64, 4096, 65536):
+        for hidden in (1024, 2048, 4096):
+            per_set = 4 * rows * hidden * 2
+            n = sets_for(per_set) if rows >= 4096 else 1
+            bufs = [(randn(rows, hidden), randn(rows, hidden), torch.empty(rows, hidden, device=dev, dtype=half),
+                     torch.empty(rows, hidden, device=dev, dtype=half)) for _ in range(n)]
+            g = (torch.rand(hidden, device=dev) + 0.5).half()
+            calls = [(lambda b=b: lib.check(L.b2_add_rms_norm(b[0].data_ptr(), b[1].data_ptr(), g.data_ptr(),
+                                                               b[2].data_ptr(), b[3].data_ptr(), rows, hidden, 1e-6, F16,
+                                                               FAST, s))) for b in bufs]
+            ms = timed(calls, 20 if rows >= 4096 else 100)
+            record("add_rms_norm", f"{rows}x{hidden} f16", per_set + 2 * hidden, ms, rows,
+                   note=None if rows >= 4096 else "latency-bound: cannot fill the GPU")
+            del bufs, calls
+    if quick:
+        return table
+
+    # ---- plain RMSNorm and add at the headline shape
+    rows, hidden = 65536, 4096
+    a, b_, o = randn(rows, hidden), randn(rows, hidden), torch.empty(rows, hidden, device=dev, dtype=half)
+    g = (torch.rand(hidden, device=dev) + 0.5).half()
+    ms = timed([lambda: lib.check(L.b2_rms_norm(a.data_ptr(), g.data_ptr(), o.data_ptr(), rows, hidden, 1e-6, F16, FAST, s))], 20)
+    record("rms_norm", f"{rows}x{hidden} f16", 2 * rows * hidden * 2 + 2 * hidden, ms, rows)
+    ms = timed([lambda: lib.check(L.b2_add(a.data_ptr(), b_.data_ptr(), o.data_ptr(), rows * hidden, F16, s))], 20)
+    record("add", f"{rows}x{hidden} f16", 3 * rows * hidden * 2, ms, rows)
+    del a, b_, o
+
+    # ---- configuration 3: packed-prefill QK-norm + RoPE, T = 16384, 16 + 8 heads of 128
+    T, HQ, HK, D = 16384, 16, 8, 128
+    lens = torch.randint(1, 513, (64,))
+    pos = torch.cat([torch.arange(int(n)) for n in lens])[:T]
+    pos = torch.cat([pos, torch.arange(T - pos.numel())]).to(torch.int32).to(dev)
+    gq, gk = (torch.rand(D, device=dev) + 0.5).half(), (torch.rand(D, device=dev) + 0.5).half()
+    per_set = 2 * T * (HQ + HK) * D * 2
+    n = sets_for(per_set)
+    bufs = [(randn(T, HQ, D), randn(T, HK, D), torch.empty(T, HQ, D, device=dev, dtype=half),
+             torch.empty(T, HK, D, device=dev, dtype=half)) for _ in range(n)]
+    calls = [(lambda b=b: lib.check(L.b2_qk_norm_rope(b[0].data_ptr(), b[1].data_ptr(), gq.data_ptr(), gk.data_ptr(),
+                                                       pos.data_ptr(), b[2].data_ptr(), b[3].data_ptr(), T, HQ, HK, D,
+                                                       1e-6, 1e6, F16, s))) for b in bufs]
+    ms = timed(calls, 40)
+    record("qk_norm_rope (fused)", f"T={T} {HQ}+{HK} heads x {D} f16", per_set + 4 * T + 512, ms, T)
+
+    def unfused(b):
+        lib.check(L.b2_rms_norm(b[0].data_ptr(), gq.data_ptr(), b[2].data_ptr(), T * HQ, D, 1e-6, F16, FAST, s))
+        lib.check(L.b2_rms_norm(b[1].data_ptr(), gk.data_ptr(), b[3].data_ptr(), T * HK, D, 1e-6, F16, FAST, s))
+        lib.check(L.b2_rope(b[2].data_ptr(), pos.data_ptr(), b[2].data_ptr(), T, HQ, D, 1e6, F16, FAST, s))
+        lib.check(L.b2_rope(b[3].data_ptr(), pos.data_ptr(), b[3].data_ptr(), T, HK, D, 1e6, F16, FAST, s))
+    ms = timed([(lambda b=b: unfused(b)) for b in bufs], 40)
+    record("rms_norm x2 + rope x2 (reference-shaped)", f"T={T} {HQ}+{HK} heads x {D} f16", 2 * per_set + 8 * T + 1024, ms, T,
+           note="four launches; bytes counted per launch sequence")
+    del bufs, calls
+
+    # ---- configuration 4: SwiGLU and embedding gather, T = 262144 tokens split over the ranks
+    T4 = 262144
+    lo, hi = sharded.row_range(T4, world, rank)
+    t_local = hi - lo
+    for inter in (3072, 12288):
+        gate, up = randn(t_local, inter, sigma=2.0), randn(t_local, inter, sigma=2.0)
+        out = torch.empty_like(gate)
+        ms = timed([lambda: lib.check(L.b2_swiglu(gate.data_ptr(), up.data_ptr(), out.data_ptr(), t_local * inter, F16, FAST, s))], 10)
+        record("swiglu", f"T={T4}/{world} x I={inter} f16", 3 * t_local * inter * 2, ms, t_local, sharded_over=world)
+        del gate, up, out
+    table_w = randn(VOCAB, 4096, sigma=0.02)
+    ids = torch.randint(0, VOCAB, (t_local,), device=dev, dtype=torch.int32)
+    out = torch.empty(t_local, 4096, device=dev, dtype=half)
+    ms = timed([lambda: lib.check(L.b2_embedding_gather(table_w.data_ptr(), ids.data_ptr(), out.data_ptr(), t_local, 4096,
+                                                         VOCAB, F16, None, s))], 10)
+    record("embedding_gather", f"T={T4}/{world} x 4096 f16, table {VOCAB}x4096", 2 * t_local * 4096 * 2 + 4 * t_local, ms,
+           t_local, sharded_over=world)
+    del table_w, ids, out
+
+    # ---- configuration 5: LM-head reductions over [256, V], V split over the ranks
+    R = 256
+    c_lo, c_hi = sharded.column_range(VOCAB, world, rank)
+    width = c_hi - c_lo
+    per_set = R * width * 4
+    n = sets_for(per_set)
+    logits = [randn(R, width, sigma=4.0, dtype=torch.float32) for _ in range(n)]
+    outs = [torch.empty(R, width, device=dev) for _ in range(min(n, 4))]
+    if world == 1:
+        from . import ops
+        ids_out = torch.empty(R, dtype=torch.int32, device=dev)
+        ws = ops.argmax_workspace(dev, R)
+        calls = [(lambda x=x: lib.check(L.b2_argmax_rows(x.data_ptr(), R, width, width, F32, ids_out.data_ptr(), ws.data_ptr(), s)))
+                 for x in logits]
+        ms = timed(calls, 40)
+        record("argmax_rows", f"{R}x{VOCAB} f32", per_set + 4 * R, ms, R)
+        sws = ops.softmax_workspace(dev, R)
+        calls = [(lambda x=x, i=i: lib.check(L.b2_softmax_rows(x.data_ptr(), outs[i % len(outs)].data_ptr(), R, width, F32,
+                                                                FAST, sws.data_ptr(), s))) for i, x in enumerate(logits)]
+        ms = timed(calls, 40)
+        record("softmax_rows", f"{R}x{VOCAB} f32", 2 * per_set, ms, R)
+    else:
+        calls = [(lambda x=x: sharded.sharded_argmax(x, c_lo)) for x in logits]
+        ms = timed(calls, 40)
+        record("argmax (vocab-sharded + all-reduce MAX of packed keys)", f"{R}x{VOCAB}/{world} f32", per_set + 4 * R, ms, R,
+               sharded_over=world, note="rows_per_s counts each of the 256 rows once per rank; exchange is 2 KB per rank")
+        table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+        calls = [(lambda x=x, i=i: sharded.sharded_softmax(x, out=outs[i % len(outs)])) for i, x in enumerate(logits)]
+        ms = timed(calls, 40)
+        record("softmax (vocab-sharded + all-reduce MAX, SUM)", f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R,
+               sharded_over=world)
+        table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+    return table
