@@ -37,7 +37,7 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu
 # capture summarised in profiles/ (None until a capture of this build exists).
-HEADLINE_TRAFFIC_BYTES = None
+HEADLINE_TRAFFIC_BYTES = 1950959616  # 4 x (268.457 + 219.283) MB: profiles/add_rms_norm_f16_65536x4096.md
 
 
 def algorithmic_bytes(rows: int, hidden: int, elem: int = 2) -> int:

@@ -176,8 +176,9 @@ def test_fused_qk_norm_rope_f16_config3(b2, port, golden, tokens):
     pos = dev(c["positions"])
     ops.cuda_rope_token_positions_out(qn, pos, wl.THETA, qn)
     ops.cuda_rope_token_positions_out(kn, pos, wl.THETA, kn)
-    for got, want in ((host(qn)[pick], want_q), (host(kn)[pick], want_k)):
-        err = np.abs(got.astype(np.float64) - want) / ulp16(np.maximum(np.abs(want), 1.0))
+    for got, want, x, gm in ((host(qn)[pick], want_q, c["q"], c["gamma_q"]), (host(kn)[pick], want_k, c["k"], c["gamma_k"])):
+        nrm = port.rms_norm(dequant(port, x[pick]).reshape(-1, 128), dequant(port, gm), wl.EPS).reshape(want.shape)
+        err = np.abs(got.astype(np.float64) - want) / ulp16(np.maximum(np.abs(want), pair_scale(nrm)))
         assert float(err.max()) <= 2.0
 
 

@@ -104,13 +104,28 @@ def test_vocab_sharded_argmax_keys_single_gpu_emulation(b2, port, world):
 
 # ---- softmax ---------------------------------------------------------------------------------
 
-def softmax_check(got, x, port, rtol, what):
-    """Elementwise |got - ref| <= rtol * max(|ref|, row max probability)."""
-    want = port.softmax(x)
+def scaled_err(got, want):
+    """max |got - want| / max(|want|, row max probability)."""
+    want = np.asarray(want, dtype=np.float64)
     floor = want.max(axis=-1, keepdims=True)
-    err = np.abs(got.astype(np.float64) - want) / np.maximum(want, floor)
-    assert float(err.max()) <= rtol, f"{what}: worst scaled error {float(err.max()):.3e}"
-    return want
+    return float((np.abs(got.astype(np.float64) - want) / np.maximum(want, floor)).max())
+
+
+def softmax_check(got, x, port, mode, what):
+    """The CPU operator adds ~150k exponentials into one fp32 accumulator in index order
+    (src/ops_cpu.cpp:13): once the sum is ~1, terms below half an ulp of it are dropped, and the
+    result drifts from the exact softmax by up to a few 1e-4 at vocabulary width.  So:
+      deterministic mode (same order, same fp32 accumulator) must match the CPU operator to 1e-5;
+      fast mode (parallel partial sums) must match the EXACT softmax to 1e-5, and the CPU operator
+      to 1e-5 plus that operator's own measured distance from the exact answer on this input."""
+    cpu, exact = port.softmax(x), port.softmax_f64(x)
+    if mode == "deterministic":
+        assert scaled_err(got, cpu) <= 1e-5, f"{what}: {scaled_err(got, cpu):.3e} vs ops_cpu"
+    else:
+        assert scaled_err(got, exact) <= 1e-5, f"{what}: {scaled_err(got, exact):.3e} vs exact"
+        drift = scaled_err(cpu, exact)
+        assert scaled_err(got, cpu) <= 1e-5 + drift, f"{what}: {scaled_err(got, cpu):.3e} vs ops_cpu (its drift {drift:.3e})"
+        assert abs(float(got.astype(np.float64).sum(axis=-1).max()) - 1) <= 1e-5
 
 
 @pytest.mark.parametrize("rows,width", [(2, 4), (1, 1), (5, 1000), (3, 4099), (4, 8192), (7, 30000), (2, 151936),
@@ -120,13 +135,7 @@ def test_softmax_f32(b2, port, rows, width, mode):
     rng = np.random.default_rng(rows + width)
     x = wl.normal(rng, (rows, width), 4.0)
     got = host(ops.cuda_softmax_last_dim(dev(x), mode))
-    want = softmax_check(got, x, port, 1e-5, f"softmax {mode} {rows}x{width}")
-    # pure relative error, reported against the exact (fp64) answer as well
-    exact = port.softmax_f64(x)
-    big = exact > 1e-30
-    assert float((np.abs(got[big] - exact[big]) / exact[big]).max()) <= 2e-5
-    assert abs(float(got.astype(np.float64).sum(axis=-1).max()) - 1) <= 1e-5
-    assert want.shape == got.shape
+    softmax_check(got, x, port, mode, f"softmax {mode} {rows}x{width}")
 
 
 def test_softmax_reference_test_literals(b2, port):
@@ -146,13 +155,14 @@ def test_softmax_reference_test_literals(b2, port):
 
 def test_softmax_committed_reference_output_and_config5(b2, port, golden):
     c5 = wl.config5(rows=4, vocab=8192, seed=5002)
-    want = golden("small_reference")["c5_softmax"]
-    for mode in ("fast", "deterministic"):
-        got = host(ops.cuda_softmax_last_dim(dev(c5["logits"]), mode))
-        assert float((np.abs(got - want) / np.maximum(want, want.max(axis=1, keepdims=True))).max()) <= 1e-5
+    want = golden("small_reference")["c5_softmax"]          # the reference's compiled softmax_last_dim
+    got = host(ops.cuda_softmax_last_dim(dev(c5["logits"]), "deterministic"))
+    assert scaled_err(got, want) <= 1e-5
+    got = host(ops.cuda_softmax_last_dim(dev(c5["logits"]), "fast"))
+    assert scaled_err(got, want) <= 1e-5 + scaled_err(want, port.softmax_f64(c5["logits"]))
     full = wl.config5(rows=16)
     for mode in ("fast", "deterministic"):
-        softmax_check(host(ops.cuda_softmax_last_dim(dev(full["logits"]), mode)), full["logits"], port, 1e-5,
+        softmax_check(host(ops.cuda_softmax_last_dim(dev(full["logits"]), mode)), full["logits"], port, mode,
                       f"config5 {mode}")
 
 
@@ -179,7 +189,7 @@ def test_vocab_sharded_softmax_single_gpu_emulation(b2, port, world):
         o = torch.empty_like(t)
         lib.check(L.b2_softmax_apply(t.data_ptr(), o.data_ptr(), 8, t.shape[1], 0, gmax.data_ptr(), gsum.data_ptr(), s))
         outs.append(host(o))
-    softmax_check(np.concatenate(outs, axis=1), x, port, 1e-5, f"sharded softmax world={world}")
+    softmax_check(np.concatenate(outs, axis=1), x, port, "fast", f"sharded softmax world={world}")
     # the driver function itself, as a world of one (no process group initialised)
-    softmax_check(host(sharded.sharded_softmax(dev(x))), x, port, 1e-5, "sharded softmax, one rank")
+    softmax_check(host(sharded.sharded_softmax(dev(x))), x, port, "fast", "sharded softmax, one rank")
     assert np.array_equal(host(sharded.sharded_argmax(dev(x), 0)), port.argmax_rows(x))
