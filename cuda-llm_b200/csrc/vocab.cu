@@ -22,6 +22,7 @@
 #include <cfloat>
 #include <climits>
 #include <cooperative_groups.h>
+#include <mutex>
 
 namespace cg = cooperative_groups;
 
@@ -450,3 +451,74 @@ int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, 
 }
 
 }  // namespace b2
+
+// ---------------------------------------------------------------------------
+// Argmax without a caller workspace and without any allocation.
+//
+// For hosts that must not call cudaMalloc after start-up (all device memory already
+// belongs to their own pool) and plug-ins that receive tensors but no allocator.  The
+// scratch the argmax kernel needs (one 64-bit key and one 32-bit ticket per row) is a
+// fixed array in the library image.  In host code the array's NAME is only a handle:
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device
+// with that device current.
+// ---------------------------------------------------------------------------
+namespace b2 {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(B2_ARGMAX_STATIC_MAX_ROWS) * 12;
+static __device__ __align__(256) unsigned char g_argmax_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_address[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device, or nullptr (error recorded).
+void* static_scratch_for_current_device() {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    set_error("b2_argmax_rows_static: cannot identify the current device: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_argmax_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("b2_argmax_rows_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      return nullptr;
+    }
+    g_static_scratch_address[device] = p;
+  }
+  return g_static_scratch_address[device];
+}
+
+}  // namespace
+}  // namespace b2
+
+extern "C" int b2_argmax_rows_static(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                                     int32_t* out_ids, b2_stream stream) {
+  using namespace b2;
+  const char* op = "b2_argmax_rows_static";
+  if (dtype != B2_F32 && dtype != B2_F16) { set_error("%s: dtype must be B2_F32 or B2_F16", op); return B2_ERR_INVALID; }
+  if (rows < 0 || width <= 0 || width > 0x7fffffffll || row_stride < width) {
+    set_error("%s: rows must be >= 0, 0 < width < 2^31 and row_stride >= width", op);
+    return B2_ERR_INVALID;
+  }
+  if (rows > B2_ARGMAX_STATIC_MAX_ROWS) {
+    set_error("%s: %lld rows exceed the built-in scratch of %d rows; use b2_argmax_rows with a workspace", op,
+              static_cast<long long>(rows), B2_ARGMAX_STATIC_MAX_ROWS);
+    return B2_ERR_TOO_LARGE;
+  }
+  if (rows == 0) return B2_OK;
+  if (logits == nullptr || out_ids == nullptr) { set_error("%s: null pointer", op); return B2_ERR_INVALID; }
+  void* scratch = static_scratch_for_current_device();
+  if (scratch == nullptr) return B2_ERR_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: clear the part this call uses, in stream order
+  if (cudaMemsetAsync(scratch, 0, argmax_workspace_bytes(rows), s) != cudaSuccess) return launch_status(op);
+  return launch_argmax(logits, rows, width, row_stride, dtype, 0, out_ids, nullptr, scratch, s);
+}
+

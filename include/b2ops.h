@@ -13,10 +13,9 @@
  *   - Every pointer is a DEVICE pointer unless a parameter says "host".
  *   - Tensors are dense and row-major.  dtype: B2_F32 or B2_F16 storage; all
  *     arithmetic is fp32 (fp64 where the deterministic mode needs it).
- *   - Entry points never allocate, never synchronise and never copy to the host,
- *     so all of them may be recorded into a CUDA graph; scratch memory is passed
- *     in by the caller.  (b2_alloc/b2_free and the *_host helpers are the only
- *     exceptions and say so.)
+ *   - Entry points never allocate, never synchronise and never copy to the host;
+ *     scratch memory is passed in by the caller, so those calls may be recorded
+ *     into a CUDA graph.  (b2_alloc/b2_free are the exceptions and say so.)
  *   - `stream` is a cudaStream_t.  NULL means the calling thread's default stream
  *     (the library is built with per-thread default streams, like the reference:
  *     its CMakeLists.txt:9).
@@ -153,6 +152,27 @@ B2_API size_t b2_argmax_workspace_bytes(int64_t rows);
 B2_API int b2_argmax_workspace_init(void* workspace, int64_t rows, b2_stream stream);
 B2_API int b2_argmax_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
                           int32_t* out_ids, void* workspace, b2_stream stream);
+
+/* Row argmax for callers that cannot allocate device memory and have no scratch buffer to
+ * hand over: same inputs, outputs and result as b2_argmax_rows, but the scratch lives in a
+ * fixed array inside the library image instead of a caller workspace.  Meant for a host
+ * that gave all device memory to its own pool at start-up and treats any later cudaMalloc
+ * as an error (it may fail, and it stalls the device), or a plug-in that is handed tensors
+ * by its host application but no allocator.  This entry point has no counterpart in the
+ * reference, whose argmax allocates and frees two buffers on every call
+ * (src/ops_cuda.cu:711).
+ *   - rows must be <= B2_ARGMAX_STATIC_MAX_ROWS; more returns B2_ERR_TOO_LARGE.
+ *   - The array (B2_ARGMAX_STATIC_MAX_ROWS * 12 bytes) is held on every GPU that loads the
+ *     library, until the process exits.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.  No call
+ *     uses cudaMalloc, cudaFree or any allocating routine.
+ *   - All calls on a device share the one array: the part a call uses is cleared on its
+ *     stream first, and two calls whose kernels overlap on the GPU (different streams
+ *     without ordering) race on it.  Order them, or use b2_argmax_rows with one workspace each. */
+#define B2_ARGMAX_STATIC_MAX_ROWS 4096
+B2_API int b2_argmax_rows_static(const void* logits, int64_t rows, int64_t width, int64_t row_stride,
+                                 int dtype, int32_t* out_ids, b2_stream stream);
 
 /* Vocabulary-sharded form: this GPU holds columns [index_base, index_base + width)
  * of every row.  keys[r] = packed (value, index_base + local index) such that the
