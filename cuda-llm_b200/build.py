@@ -77,7 +77,7 @@ def build_shim(force: bool = False) -> str:
     if not force and _newer(SHIM_LIB, deps):
         return SHIM_LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    flags = [f for f in NVCC_FLAGS if f != "-fPIC,-fvisibility=hidden"] + ["-fPIC"]
+    flags = [f if f != "-fPIC,-fvisibility=hidden" else "-fPIC" for f in NVCC_FLAGS]   # llm:: symbols stay visible
     cmd = [nvcc] + flags + ["-x", "cu", "-I", os.path.join(ROOT, "include"), "-o", SHIM_LIB] + srcs + \
         ["-L", LIB_DIR, "-lb2ops", "-Xlinker", "-rpath,$ORIGIN"]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,8 +1,8 @@
 // Rotary embedding (NeoX rotate-half) for sm_100a, alone or fused behind the
-// per-head QK RMSNorm.  A CTA takes a tile of tokens: it first builds the tile's
-// cos/sin table in shared memory, once per (token, frequency) instead of once per
-// (token, head, frequency) as the reference does, then streams every head of those
-// tokens through 16-byte loads and stores.
+// per-head QK RMSNorm.  A warp takes a token: it first builds the token's cos/sin
+// table in shared memory, once per (token, frequency) instead of once per
+// (token, head, frequency) as the reference does, then streams every head of that
+// token through 16-byte loads and stores.
 //
 // Replaces reference kernels ropek<T>, rope_batched_kernel<T> and
 // rope_decode_batched_kernel<T> (src/ops_cuda.cu:133-135) and, in the fused form,
@@ -18,7 +18,6 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxTableHalf = 128;   // inverse-frequency table passed by value: head_dim <= 256
-constexpr int kMaxTileTokens = 8;
 
 struct InvFreq { double v[kMaxTableHalf]; };
 
@@ -26,7 +25,7 @@ struct InvFreq { double v[kMaxTableHalf]; };
 // Fast mode: the angle is formed in fp64 from a host-built table of
 // pow(double(theta), -2j/D) (the same expression as the CPU operator,
 // src/ops_cpu.cpp:11), reduced to [-pi, pi] in fp64 with a two-term 2*pi, and only
-// then handed to the fp32 sincosf: about 1 ulp of fp32 at any position.
+// then handed to the fp32 hardware sine/cosine: 4e-7 absolute at any position.
 // Deterministic mode: the reference kernel's all-fp32 expression.
 template <bool kOrdered>
 __device__ __forceinline__ float2 rope_cos_sin(int32_t position, int j, int head_dim, float theta,
@@ -42,9 +41,10 @@ __device__ __forceinline__ float2 rope_cos_sin(int32_t position, int j, int head
   const double turns = rint(angle * 1.591549430918953456e-01);
   double r = fma(-turns, two_pi_hi, angle);
   r = fma(-turns, two_pi_lo, r);
-  float s, c;
-  sincosf(float(r), &s, &c);
-  return make_float2(c, s);
+  // |r| <= pi: the hardware sine/cosine are within 2^-21.4 (absolute) there, 25x inside the
+  // 1e-5 parity bound and 1000x inside an fp16 ulp
+  const float rf = float(r);
+  return make_float2(__cosf(rf), __sinf(rf));
 }
 
 // rotate one (low, high) pair
@@ -55,9 +55,8 @@ __device__ __forceinline__ void rotate(float a, float b, float2 cs, float& lo, f
     lo = a * cs.x - b * cs.y;
     hi = b * cs.x + a * cs.y;
   } else {
-    // individually rounded products, like the CPU operator built without FMA
-    lo = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
-    hi = __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+    lo = fmaf(a, cs.x, -(b * cs.y));
+    hi = fmaf(a, cs.y, b * cs.x);
   }
 }
 
@@ -66,60 +65,59 @@ struct HeadSet {           // one [tokens, heads, head_dim] tensor with its opti
 };
 
 // ---------------------------------------------------------------------------
-// Vector kernel.  Work item = one 16-byte vector of the low half of a head plus
-// its partner in the high half.  hv = (head_dim/2)/kPerVec items make one head and
-// are consecutive lanes of one warp (hv is a power of two <= 32), so the fused
-// norm reduces over them with xor-shuffles.  Two tensors (q and k) are served by
-// one launch: items [0, q.heads*hv) of a token belong to q, the rest to k.
+// Vector kernel: one warp per token, no CTA-wide barrier anywhere.
+// The warp first writes the token's cos/sin (head_dim/2 pairs, 2 per lane at
+// head_dim 128) into its own slice of shared memory, then streams every head of
+// the token.  Work item = one 16-byte vector of the low half of a head plus its
+// partner in the high half; hv = (head_dim/2)/kPerVec items make one head and sit
+// in consecutive lanes (hv is a power of two <= 32), so the fused norm reduces
+// over them with xor-shuffles.  A lane always works on the same vector position
+// `v` of a head, so its cos/sin values and norm weights are loaded once per token
+// and the per-item work is: two 16-byte loads, the arithmetic, two stores.  The
+// loads of kItemUnroll items are issued before any of them is used.
+// The kernel is issue-bound before it is HBM-bound, hence the care about
+// instruction count: shifts instead of divisions, hoisted weights, fused
+// multiply-adds and the hardware reciprocal square root in fast mode.
 // ---------------------------------------------------------------------------
+constexpr int kItemUnroll = 4;
+constexpr int kWarpsPerCta = kThreads / kWarpSize;
+
 template <typename T, bool kNorm, bool kOrdered>
-__global__ void __launch_bounds__(kThreads)
-rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int tile_tokens,
-                   int head_dim, int hv, int64_t pos_period, float eps, float theta,
-                   const __grid_constant__ InvFreq freq) {
+__device__ __forceinline__ void rope_token_heads(const uint4* x, const uint4* w, uint4* out, int items, int hv,
+                                                 int hv_shift, int lane, const float2* cs, float inv_dim, float eps) {
   constexpr int N = Elem<T>::kPerVec;
-  extern __shared__ float2 table[];   // [tile_tokens][half]
-  const int half = head_dim >> 1;
-  const int items_q = q.heads * hv, items_per_token = (q.heads + k.heads) * hv;
-  const int64_t tiles = (tokens + tile_tokens - 1) / tile_tokens;
-  const int vecs_per_head = 2 * hv;
-
-  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const int64_t token0 = tile * tile_tokens;
-    const int here = int(tokens - token0 < tile_tokens ? tokens - token0 : tile_tokens);
-
-    for (int e = threadIdx.x; e < here * half; e += kThreads) {
-      const int tl = e / half, j = e - tl * half;
-      const int64_t t = token0 + tl;
-      const int32_t p = positions[pos_period ? t % pos_period : t];
-      table[e] = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+  const int v = lane & (hv - 1);
+  float wl[N], wh[N];
+  if (kNorm) {
+    Elem<T>::unpack(ld_reuse(w + v), wl);
+    Elem<T>::unpack(ld_reuse(w + hv + v), wh);
+  }
+  // every lane runs the same number of steps, so the shuffles below are converged
+  for (int base = 0; base < items; base += kWarpSize * kItemUnroll) {
+    uint4 raw_lo[kItemUnroll], raw_hi[kItemUnroll];
+    int where[kItemUnroll];
+    bool ok[kItemUnroll];
+#pragma unroll
+    for (int u = 0; u < kItemUnroll; ++u) {
+      const int item = base + u * kWarpSize + lane;
+      ok[u] = item < items;
+      where[u] = ((item >> hv_shift) << (hv_shift + 1)) + v;   // head * (2*hv) + v
+      if (ok[u]) {
+        raw_lo[u] = ld_stream(x + where[u]);
+        raw_hi[u] = ld_stream(x + where[u] + hv);
+      }
     }
-    __syncthreads();
-
-    const int work = here * items_per_token;
-    // every lane of a warp runs the same number of steps so the shuffles below are converged
-    for (int base = 0; base < work; base += kThreads) {
-      const int item = base + threadIdx.x;
-      const bool ok = item < work;
-      const int tl = ok ? item / items_per_token : 0;
-      const int in_token = ok ? item - tl * items_per_token : 0;
-      const bool is_k = in_token >= items_q;
-      const HeadSet& set = is_k ? k : q;
-      const int local = is_k ? in_token - items_q : in_token;
-      const int head = local / hv, v = local - head * hv;
-      const size_t head_vec0 = (size_t(token0 + tl) * set.heads + head) * size_t(vecs_per_head);
-      const uint4* src = reinterpret_cast<const uint4*>(set.x) + head_vec0;
-
+#pragma unroll
+    for (int u = 0; u < kItemUnroll; ++u) {
+      if (base + u * kWarpSize >= items) break;   // uniform across the warp
       float lo[N], hi[N];
-      if (ok) {
-        const uint4 raw_lo = ld_stream(src + v), raw_hi = ld_stream(src + hv + v);
-        Elem<T>::unpack(raw_lo, lo);
-        Elem<T>::unpack(raw_hi, hi);
+      if (ok[u]) {
+        Elem<T>::unpack(raw_lo[u], lo);
+        Elem<T>::unpack(raw_hi[u], hi);
       } else {
 #pragma unroll
         for (int e = 0; e < N; ++e) lo[e] = hi[e] = 0.0f;
       }
-
       if (kNorm) {
         float ss = 0.0f;
 #pragma unroll
@@ -127,31 +125,53 @@ rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, 
 #pragma unroll
         for (int e = 0; e < N; ++e) ss = fmaf(hi[e], hi[e], ss);
         ss = group_sum(ss, hv);
-        const float inv = 1.0f / sqrtf(ss / float(head_dim) + eps);
-        if (ok) {
-          float wl[N], wh[N];
-          const uint4* wv = reinterpret_cast<const uint4*>(set.w);
-          Elem<T>::unpack(ld_reuse(wv + v), wl);
-          Elem<T>::unpack(ld_reuse(wv + hv + v), wh);
+        const float inv = rsqrtf(fmaf(ss, inv_dim, eps));
 #pragma unroll
-          for (int e = 0; e < N; ++e) {
-            lo[e] = __fmul_rn(__fmul_rn(lo[e], inv), wl[e]);
-            hi[e] = __fmul_rn(__fmul_rn(hi[e], inv), wh[e]);
-          }
+        for (int e = 0; e < N; ++e) {
+          lo[e] = (lo[e] * inv) * wl[e];
+          hi[e] = (hi[e] * inv) * wh[e];
         }
       }
-
-      if (ok) {
-        const float2* cs = table + tl * half + v * N;
+      if (ok[u]) {
         float out_lo[N], out_hi[N];
 #pragma unroll
         for (int e = 0; e < N; ++e) rotate<kOrdered>(lo[e], hi[e], cs[e], out_lo[e], out_hi[e]);
-        uint4* dst = reinterpret_cast<uint4*>(set.out) + head_vec0;
-        st_stream(dst + v, Elem<T>::pack(out_lo));
-        st_stream(dst + hv + v, Elem<T>::pack(out_hi));
+        st_stream(out + where[u], Elem<T>::pack(out_lo));
+        st_stream(out + where[u] + hv, Elem<T>::pack(out_hi));
       }
     }
-    __syncthreads();  // the table is rebuilt for the next tile
+  }
+}
+
+template <typename T, bool kNorm, bool kOrdered>
+__global__ void __launch_bounds__(kThreads, 2)
+rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
+                   int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
+  constexpr int N = Elem<T>::kPerVec;
+  extern __shared__ float2 table[];   // [warps per CTA][half]
+  const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float2* cs_row = table + warp * half;
+  const int vecs_per_head = 2 * hv;
+  const float inv_dim = 1.0f / float(head_dim);
+
+  for (int64_t t = int64_t(blockIdx.x) * kWarpsPerCta + warp; t < tokens; t += int64_t(gridDim.x) * kWarpsPerCta) {
+    const int32_t p = positions[pos_period ? t % pos_period : t];
+    for (int j = lane; j < half; j += kWarpSize) cs_row[j] = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+    __syncwarp();
+    float2 cs[N];                       // this lane's frequencies: the same for every head
+#pragma unroll
+    for (int e = 0; e < N; ++e) cs[e] = cs_row[(lane & (hv - 1)) * N + e];
+
+    rope_token_heads<T, kNorm, kOrdered>(
+        reinterpret_cast<const uint4*>(q.x) + size_t(t) * q.heads * vecs_per_head, reinterpret_cast<const uint4*>(q.w),
+        reinterpret_cast<uint4*>(q.out) + size_t(t) * q.heads * vecs_per_head, q.heads * hv, hv, hv_shift, lane, cs,
+        inv_dim, eps);
+    if (k.heads > 0)
+      rope_token_heads<T, kNorm, kOrdered>(
+          reinterpret_cast<const uint4*>(k.x) + size_t(t) * k.heads * vecs_per_head, reinterpret_cast<const uint4*>(k.w),
+          reinterpret_cast<uint4*>(k.out) + size_t(t) * k.heads * vecs_per_head, k.heads * hv, hv, hv_shift, lane, cs,
+          inv_dim, eps);
+    __syncwarp();  // the warp's table slice is rewritten for its next token
   }
 }
 
@@ -229,17 +249,13 @@ template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
 template <typename T, bool kNorm, bool kOrdered>
 int launch_vector(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv,
                   int64_t pos_period, float eps, float theta, cudaStream_t s, const char* what) {
-  const int items_per_token = (q.heads + k.heads) * hv;
-  // enough tokens per tile to occupy the CTA once, but a small table
-  int tile_tokens = (kThreads + items_per_token - 1) / items_per_token;
-  if (tile_tokens < 1) tile_tokens = 1;
-  if (tile_tokens > kMaxTileTokens) tile_tokens = kMaxTileTokens;
-  const int64_t tiles = (tokens + tile_tokens - 1) / tile_tokens;
-  const int64_t cap = int64_t(sm_count()) * 8;
-  const unsigned grid = unsigned(tiles < cap ? tiles : cap);
-  const size_t smem = size_t(tile_tokens) * size_t(head_dim / 2) * sizeof(float2);
+  const int64_t ctas = (tokens + kWarpsPerCta - 1) / kWarpsPerCta, cap = int64_t(sm_count()) * 64;
+  const unsigned grid = unsigned(ctas < cap ? ctas : cap);
+  const size_t smem = size_t(kWarpsPerCta) * size_t(head_dim / 2) * sizeof(float2);
+  int hv_shift = 0;
+  while ((1 << hv_shift) < hv) ++hv_shift;
   rope_tokens_kernel<T, kNorm, kOrdered><<<grid, kThreads, smem, s>>>(
-      q, k, positions, tokens, tile_tokens, int(head_dim), hv, pos_period, eps, theta, make_table(head_dim, theta));
+      q, k, positions, tokens, int(head_dim), hv, hv_shift, pos_period, eps, theta, make_table(head_dim, theta));
   return launch_status(what);
 }
 

@@ -22,6 +22,7 @@
 #include <cfloat>
 #include <climits>
 #include <cooperative_groups.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace cg = cooperative_groups;
@@ -137,54 +138,128 @@ __global__ void argmax_decode_kernel(const int64_t* keys, int64_t rows, int32_t*
 constexpr int kSoftThreads = 512;
 constexpr size_t kClusterSliceBytes = 100 * 1024;  // two CTAs of a cluster fit one SM's shared memory
 
-// ---- fast mode: one cluster per row, the row stays in distributed shared memory
+// exp(x - m) in the fast paths is 2^(x*log2(e) - m*log2(e)): one fused multiply-add and one
+// hardware exponential (ex2.approx, 2^-22 relative).  The rounding of m*log2(e) is a factor
+// common to every element of the row, so it cancels in the normalisation.
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Running (max, sum of exp(x - max)) of a stream of values, updated one small group at a time:
+// one rescale per group instead of one per element.  Works on t = x*log2(e).
+template <int COUNT>
+__device__ __forceinline__ void online_update(float& m, float& m2, float& s, const float* x) {
+  float t[COUNT];
+  float gx = x[0];
+#pragma unroll
+  for (int q = 1; q < COUNT; ++q) gx = fmaxf(gx, x[q]);
+#pragma unroll
+  for (int q = 0; q < COUNT; ++q) t[q] = x[q] * kLog2e;
+  m = fmaxf(m, gx);                                     // the maximum itself, in the units of x
+  const float gm = gx * kLog2e;                         // rounding is monotonic: this is max(t[])
+  if (gm > m2) { s *= fast_exp2(m2 - gm); m2 = gm; }   // first group: s = 0 * 2^(-inf) = 0
+  if (m2 != -INFINITY) {                                // a run of leading -inf (masked) entries adds nothing
+#pragma unroll
+    for (int q = 0; q < COUNT; ++q) s += fast_exp2(t[q] - m2);
+  }
+}
+
+// ---- fast mode: one cluster per row, the row stays in distributed shared memory.
+// The kernel is bound by instruction issue before HBM unless every pass is lean, so:
+//   pass A  HBM -> shared memory (16-byte loads, four in flight), running max: ~1.5 instr/element
+//           cluster barrier, row max from all slices through DSMEM
+//   pass B  shared memory in place: e = 2^(x*log2e - max*log2e), running sum: ~3.5 instr/element
+//           cluster barrier, row sum from all slices
+//   pass C  shared memory -> HBM: e * (1/sum), 16-byte stores: ~1.75 instr/element
 template <typename T, bool kVec>
-__global__ void __launch_bounds__(kSoftThreads)
+__global__ void __launch_bounds__(kSoftThreads, 2)
 softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ __align__(16) float vals[];
   __shared__ float scratch[32];
-  __shared__ float published[2];  // [0] slice max, [1] slice sum: read by the other CTAs of the cluster
+  __shared__ float published[2];  // slice max, slice sum: read by the whole cluster
 
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
   const int64_t row = blockIdx.x / ranks;
   const int64_t lo = int64_t(rank) * slice;
-  const int64_t n = lo >= width ? 0 : (width - lo < slice ? width - lo : slice);
+  const int n = int(lo >= width ? 0 : (width - lo < slice ? width - lo : slice));
   const T* src = x + row * width + lo;
   T* dst = out + row * width + lo;
+  const int step = blockDim.x, tid = threadIdx.x;
+  const int n4 = n >> 2;                       // whole float4 groups of the slice in shared memory
+  float4* vals4 = reinterpret_cast<float4*>(vals);
 
+  // ---- pass A
   float m = -INFINITY;
-  scan_range<T, kVec>(src, n, [&](float v, int64_t i) { vals[i] = v; m = fmaxf(m, v); });
+  if (kVec) {
+    const int nvec = n / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    for (int v0 = tid; v0 < nvec; v0 += step * 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (v0 + k * step < nvec) r[k] = ld_stream(vp + v0 + k * step);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = v0 + k * step;
+        if (v < nvec) {
+          float e[N];
+          Elem<T>::unpack(r[k], e);
+#pragma unroll
+          for (int q = 0; q < N; q += 4) {
+            vals4[(v * N + q) >> 2] = make_float4(e[q], e[q + 1], e[q + 2], e[q + 3]);
+            m = fmaxf(fmaxf(m, fmaxf(e[q], e[q + 1])), fmaxf(e[q + 2], e[q + 3]));
+          }
+        }
+      }
+    }
+    for (int i = nvec * N + tid; i < n; i += step) { const float e = Elem<T>::load(src + i); vals[i] = e; m = fmaxf(m, e); }
+  } else {
+    for (int i = tid; i < n; i += step) { const float e = Elem<T>::load(src + i); vals[i] = e; m = fmaxf(m, e); }
+  }
   m = block_max(m, scratch);
-  if (threadIdx.x == 0) published[0] = m;
+  if (tid == 0) published[0] = m;
   cluster.sync();
   float row_max = -INFINITY;
   for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, *cluster.map_shared_rank(&published[0], r));
+  const float neg_m2 = -row_max * kLog2e;
 
-  float s = 0.0f;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-    const float e = expf(vals[i] - row_max);
-    vals[i] = e;
-    s += e;
+  // ---- pass B
+  float s0 = 0.0f, s1 = 0.0f;
+  for (int g = tid; g < n4; g += step) {
+    float4 t = vals4[g];
+    t.x = fast_exp2(fmaf(t.x, kLog2e, neg_m2)); t.y = fast_exp2(fmaf(t.y, kLog2e, neg_m2));
+    t.z = fast_exp2(fmaf(t.z, kLog2e, neg_m2)); t.w = fast_exp2(fmaf(t.w, kLog2e, neg_m2));
+    vals4[g] = t;
+    s0 += t.x + t.y;
+    s1 += t.z + t.w;
   }
-  s = block_sum(s, scratch);
-  if (threadIdx.x == 0) published[1] = s;
+  for (int i = (n4 << 2) + tid; i < n; i += step) { const float e = fast_exp2(fmaf(vals[i], kLog2e, neg_m2)); vals[i] = e; s0 += e; }
+  const float s = block_sum(s0 + s1, scratch);
+  if (tid == 0) published[1] = s;
   cluster.sync();
   float row_sum = 0.0f;
-  for (unsigned r = 0; r < ranks; ++r) row_sum += *cluster.map_shared_rank(&published[1], r);
+  for (unsigned r = 0; r < ranks; ++r) row_sum += *cluster.map_shared_rank(&published[1], r);  // rank order on every CTA
+  const float inv_sum = 1.0f / row_sum;
 
+  // ---- pass C
   if (kVec) {
-    const int64_t nvec = n / N;
-    for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const int nvec = n / N;
+    for (int v = tid; v < nvec; v += step) {
       float o[N];
 #pragma unroll
-      for (int q = 0; q < N; ++q) o[q] = __fdiv_rn(vals[v * N + q], row_sum);
+      for (int q = 0; q < N; q += 4) {
+        const float4 t = vals4[(v * N + q) >> 2];
+        o[q] = t.x * inv_sum; o[q + 1] = t.y * inv_sum; o[q + 2] = t.z * inv_sum; o[q + 3] = t.w * inv_sum;
+      }
       st_stream(reinterpret_cast<uint4*>(dst) + v, Elem<T>::pack(o));
     }
-    for (int64_t i = nvec * N + threadIdx.x; i < n; i += blockDim.x) Elem<T>::store(dst + i, __fdiv_rn(vals[i], row_sum));
+    for (int i = nvec * N + tid; i < n; i += step) Elem<T>::store(dst + i, vals[i] * inv_sum);
   } else {
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) Elem<T>::store(dst + i, __fdiv_rn(vals[i], row_sum));
+    for (int i = tid; i < n; i += step) Elem<T>::store(dst + i, vals[i] * inv_sum);
   }
   cluster.sync();  // nobody leaves while a neighbour may still read its published[]
 }
@@ -193,22 +268,42 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kSoftThreads)
 softmax_stats_kernel(const T* x, int64_t width, float* row_max, float* row_sum) {
+  constexpr int N = Elem<T>::kPerVec;
   __shared__ float scratch[32];
   const int64_t row = blockIdx.x;
-  float m = -INFINITY, s = 0.0f;
-  scan_range<T, kVec>(x + row * width, width, [&](float v, int64_t) {
-    if (v > m) { s *= expf(m - v); m = v; }   // first element: s = 0 * exp(-inf) = 0
-    if (m != -INFINITY) s += expf(v - m);     // a run of leading -inf (masked) entries adds nothing
-  });
-  const float big = block_max(m, scratch);
-  if (m != -INFINITY) s *= expf(m - big); else s = 0.0f;
+  const T* src = x + row * width;
+  const int64_t step = blockDim.x;
+  float m = -INFINITY, m2 = -INFINITY, s = 0.0f;   // max of x, max of x*log2(e), sum of 2^(x*log2(e) - m2)
+  if (kVec) {
+    const int64_t nvec = width / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += step * 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (v0 + k * step < nvec) r[k] = ld_stream(vp + v0 + k * step);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (v0 + k * step < nvec) {
+          float e[N];
+          Elem<T>::unpack(r[k], e);
+          online_update<N>(m, m2, s, e);
+        }
+      }
+    }
+    for (int64_t i = nvec * N + threadIdx.x; i < width; i += step) { const float e = Elem<T>::load(src + i); online_update<1>(m, m2, s, &e); }
+  } else {
+    for (int64_t i = threadIdx.x; i < width; i += step) { const float e = Elem<T>::load(src + i); online_update<1>(m, m2, s, &e); }
+  }
+  const float big = block_max(m, scratch);       // max of x over the row; big*log2(e) is the max of t
+  s = m2 == -INFINITY ? 0.0f : s * fast_exp2(m2 - big * kLog2e);
   s = block_sum(s, scratch);
   if (threadIdx.x == 0) { row_max[row] = big; row_sum[row] = s; }
 }
 
 __global__ void softmax_rebase_kernel(const float* row_max, const float* global_max, float* row_sum, int64_t rows) {
   const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (r < rows) row_sum[r] = row_max[r] == -INFINITY ? 0.0f : row_sum[r] * expf(row_max[r] - global_max[r]);
+  // the same 2^(m*log2e - M*log2e) form as the kernels on either side of the exchange
+  if (r < rows) row_sum[r] = row_max[r] == -INFINITY ? 0.0f : row_sum[r] * fast_exp2(row_max[r] * kLog2e - global_max[r] * kLog2e);
 }
 
 // ---- out = exp(x - max[r]) / sum[r]; blockIdx = row * tiles + tile
@@ -221,7 +316,7 @@ softmax_apply_kernel(const T* x, T* out, int64_t width, int tiles, int64_t tile_
   const int64_t row = blockIdx.x / tiles;
   const int64_t lo = int64_t(blockIdx.x - row * tiles) * tile_elems;
   const int64_t n = width - lo < tile_elems ? width - lo : tile_elems;
-  const float m = row_max[row], z = row_sum[row];
+  const float neg_m2 = -row_max[row] * kLog2e, inv_z = 1.0f / row_sum[row];
   const T* src = x + row * width + lo;
   T* dst = out + row * width + lo;
   if (kVec) {
@@ -239,15 +334,15 @@ softmax_apply_kernel(const T* x, T* out, int64_t width, int tiles, int64_t tile_
         float e[N];
         Elem<T>::unpack(raw[k], e);
 #pragma unroll
-        for (int q = 0; q < N; ++q) e[q] = __fdiv_rn(expf(e[q] - m), z);
+        for (int q = 0; q < N; ++q) e[q] = fast_exp2(fmaf(e[q], kLog2e, neg_m2)) * inv_z;
         st_stream(reinterpret_cast<uint4*>(dst) + v, Elem<T>::pack(e));
       }
     }
     for (int64_t i = nvec * N + threadIdx.x; i < n; i += kApplyThreads)
-      Elem<T>::store(dst + i, __fdiv_rn(expf(Elem<T>::load(src + i) - m), z));
+      Elem<T>::store(dst + i, fast_exp2(fmaf(Elem<T>::load(src + i), kLog2e, neg_m2)) * inv_z);
   } else {
     for (int64_t i = threadIdx.x; i < n; i += kApplyThreads)
-      Elem<T>::store(dst + i, __fdiv_rn(expf(Elem<T>::load(src + i) - m), z));
+      Elem<T>::store(dst + i, fast_exp2(fmaf(Elem<T>::load(src + i), kLog2e, neg_m2)) * inv_z);
   }
 }
 
@@ -328,6 +423,10 @@ int launch_softmax_cluster(const T* x, T* out, int64_t rows, int64_t width, int 
     cudaGetLastError();
     return B2_ERR_UNSUPPORTED;
   }
+  if (ranks > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(rows * ranks));
   cfg.blockDim = dim3(slice <= 4096 ? 128 : kSoftThreads);
@@ -386,9 +485,15 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
     return launch_status("softmax (deterministic)");
   }
   // smallest cluster whose slices fit, then widened (up to 8) while rows alone cannot fill the SMs
+  static const int max_ranks = [] {                 // tuning aid: B2_SOFTMAX_CLUSTER=16 opts in to the
+    const char* v = std::getenv("B2_SOFTMAX_CLUSTER");   // non-portable cluster size
+    const int n = v ? std::atoi(v) : 8;
+    return n == 16 || n == 4 || n == 2 || n == 1 ? n : 8;
+  }();
   int ranks = 1;
-  while (ranks < 8 && size_t((width + ranks - 1) / ranks) * sizeof(float) > kClusterSliceBytes) ranks <<= 1;
-  while (ranks < 8 && rows * ranks < int64_t(sm_count()) * 2 && width / (ranks * 2) >= 1024) ranks <<= 1;
+  while (ranks < max_ranks && size_t((width + ranks - 1) / ranks) * sizeof(float) > kClusterSliceBytes) ranks <<= 1;
+  while (ranks < max_ranks && rows * ranks < int64_t(sm_count()) * 2 && width / (ranks * 2) >= 1024) ranks <<= 1;
+  if (max_ranks == 16 && width / 16 >= 1024) ranks = 16;
   int64_t slice = (width + ranks - 1) / ranks;
   slice = (slice + N - 1) / N * N;
   if (size_t(slice) * sizeof(float) <= kClusterSliceBytes) {

@@ -29,8 +29,16 @@ def _peak():
         return 6650.0
 
 
-def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
+def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, only=None, reps_scale=1.0):
+    """only: substring selecting one group of entries ("add_rms_norm", "headline_shape", "qk_norm_rope",
+    "swiglu", "gather", "argmax", "softmax"); reps_scale shortens the runs for profiler captures."""
     from . import sharded
+
+    def want(group):
+        return only is None or only in group
+
+    def nreps(n):
+        return max(1, int(n * reps_scale))
     peak = _peak()
     s = stream.cuda_stream
     F16, F32, FAST = lib.F16, lib.F32, lib.FAST
@@ -68,7 +76,7 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
         table.append(e)
 
     # ---- configuration 2: fused add + RMSNorm sweep (single-GPU shapes; every rank runs them alike)
-    for rows in (1, 64, 4096, 65536):
+    for rows in ((1, 64, 4096, 65536) if want("add_rms_norm") else ()):
         for hidden in (1024, 2048, 4096):
             per_set = 4 * rows * hidden * 2
             n = sets_for(per_set) if rows >= 4096 else 1
@@ -78,23 +86,40 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
             calls = [(lambda b=b: lib.check(L.b2_add_rms_norm(b[0].data_ptr(), b[1].data_ptr(), g.data_ptr(),
                                                                b[2].data_ptr(), b[3].data_ptr(), rows, hidden, 1e-6, F16,
                                                                FAST, s))) for b in bufs]
-            ms = timed(calls, 20 if rows >= 4096 else 100)
+            ms = timed(calls, nreps(20 if rows >= 4096 else 100))
             record("add_rms_norm", f"{rows}x{hidden} f16", per_set + 2 * hidden, ms, rows,
                    note=None if rows >= 4096 else "latency-bound: cannot fill the GPU")
             del bufs, calls
     if quick:
         return table
 
+    if want("headline_shape"):
+        _headline_shape_ops(L, lib, dev, s, timed, record, randn, nreps)
+    if want("qk_norm_rope"):
+        _config3(L, lib, dev, s, timed, record, randn, sets_for, nreps)
+    if want("swiglu") or want("gather"):
+        _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, nreps)
+    if want("argmax") or want("softmax"):
+        _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table)
+    return table
+
+
+def _headline_shape_ops(L, lib, dev, s, timed, record, randn, nreps):
+    F16, FAST, half = lib.F16, lib.FAST, torch.float16
     # ---- plain RMSNorm and add at the headline shape
     rows, hidden = 65536, 4096
     a, b_, o = randn(rows, hidden), randn(rows, hidden), torch.empty(rows, hidden, device=dev, dtype=half)
     g = (torch.rand(hidden, device=dev) + 0.5).half()
-    ms = timed([lambda: lib.check(L.b2_rms_norm(a.data_ptr(), g.data_ptr(), o.data_ptr(), rows, hidden, 1e-6, F16, FAST, s))], 20)
+    ms = timed([lambda: lib.check(L.b2_rms_norm(a.data_ptr(), g.data_ptr(), o.data_ptr(), rows, hidden, 1e-6, F16, FAST, s))], nreps(20))
     record("rms_norm", f"{rows}x{hidden} f16", 2 * rows * hidden * 2 + 2 * hidden, ms, rows)
-    ms = timed([lambda: lib.check(L.b2_add(a.data_ptr(), b_.data_ptr(), o.data_ptr(), rows * hidden, F16, s))], 20)
+    ms = timed([lambda: lib.check(L.b2_add(a.data_ptr(), b_.data_ptr(), o.data_ptr(), rows * hidden, F16, s))], nreps(20))
     record("add", f"{rows}x{hidden} f16", 3 * rows * hidden * 2, ms, rows)
     del a, b_, o
 
+
+
+def _config3(L, lib, dev, s, timed, record, randn, sets_for, nreps):
+    F16, FAST, half = lib.F16, lib.FAST, torch.float16
     # ---- configuration 3: packed-prefill QK-norm + RoPE, T = 16384, 16 + 8 heads of 128
     T, HQ, HK, D = 16384, 16, 8, 128
     lens = torch.randint(1, 513, (64,))
@@ -108,7 +133,7 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
     calls = [(lambda b=b: lib.check(L.b2_qk_norm_rope(b[0].data_ptr(), b[1].data_ptr(), gq.data_ptr(), gk.data_ptr(),
                                                        pos.data_ptr(), b[2].data_ptr(), b[3].data_ptr(), T, HQ, HK, D,
                                                        1e-6, 1e6, F16, s))) for b in bufs]
-    ms = timed(calls, 40)
+    ms = timed(calls, nreps(40))
     record("qk_norm_rope (fused)", f"T={T} {HQ}+{HK} heads x {D} f16", per_set + 4 * T + 512, ms, T)
 
     def unfused(b):
@@ -116,21 +141,27 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
         lib.check(L.b2_rms_norm(b[1].data_ptr(), gk.data_ptr(), b[3].data_ptr(), T * HK, D, 1e-6, F16, FAST, s))
         lib.check(L.b2_rope(b[2].data_ptr(), pos.data_ptr(), b[2].data_ptr(), T, HQ, D, 1e6, F16, FAST, s))
         lib.check(L.b2_rope(b[3].data_ptr(), pos.data_ptr(), b[3].data_ptr(), T, HK, D, 1e6, F16, FAST, s))
-    ms = timed([(lambda b=b: unfused(b)) for b in bufs], 40)
+    ms = timed([(lambda b=b: unfused(b)) for b in bufs], nreps(40))
     record("rms_norm x2 + rope x2 (reference-shaped)", f"T={T} {HQ}+{HK} heads x {D} f16", 2 * per_set + 8 * T + 1024, ms, T,
            note="four launches; bytes counted per launch sequence")
     del bufs, calls
 
+
+
+def _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, nreps):
+    F16, FAST, half = lib.F16, lib.FAST, torch.float16
     # ---- configuration 4: SwiGLU and embedding gather, T = 262144 tokens split over the ranks
     T4 = 262144
     lo, hi = sharded.row_range(T4, world, rank)
     t_local = hi - lo
-    for inter in (3072, 12288):
+    for inter in ((3072, 12288) if want("swiglu") else ()):
         gate, up = randn(t_local, inter, sigma=2.0), randn(t_local, inter, sigma=2.0)
         out = torch.empty_like(gate)
-        ms = timed([lambda: lib.check(L.b2_swiglu(gate.data_ptr(), up.data_ptr(), out.data_ptr(), t_local * inter, F16, FAST, s))], 10)
+        ms = timed([lambda: lib.check(L.b2_swiglu(gate.data_ptr(), up.data_ptr(), out.data_ptr(), t_local * inter, F16, FAST, s))], nreps(10))
         record("swiglu", f"T={T4}/{world} x I={inter} f16", 3 * t_local * inter * 2, ms, t_local, sharded_over=world)
         del gate, up, out
+    if not want("gather"):
+        return
     table_w = randn(VOCAB, 4096, sigma=0.02)
     ids = torch.randint(0, VOCAB, (t_local,), device=dev, dtype=torch.int32)
     out = torch.empty(t_local, 4096, device=dev, dtype=half)
@@ -140,6 +171,10 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
            t_local, sharded_over=world)
     del table_w, ids, out
 
+
+
+def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table):
+    F16, F32, FAST = lib.F16, lib.F32, lib.FAST
     # ---- configuration 5: LM-head reductions over [256, V], V split over the ranks
     R = 256
     c_lo, c_hi = sharded.column_range(VOCAB, world, rank)
@@ -154,22 +189,44 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False):
         ws = ops.argmax_workspace(dev, R)
         calls = [(lambda x=x: lib.check(L.b2_argmax_rows(x.data_ptr(), R, width, width, F32, ids_out.data_ptr(), ws.data_ptr(), s)))
                  for x in logits]
-        ms = timed(calls, 40)
+        ms = timed(calls, nreps(40))
         record("argmax_rows", f"{R}x{VOCAB} f32", per_set + 4 * R, ms, R)
         sws = ops.softmax_workspace(dev, R)
         calls = [(lambda x=x, i=i: lib.check(L.b2_softmax_rows(x.data_ptr(), outs[i % len(outs)].data_ptr(), R, width, F32,
                                                                 FAST, sws.data_ptr(), s))) for i, x in enumerate(logits)]
-        ms = timed(calls, 40)
+        ms = timed(calls, nreps(40))
         record("softmax_rows", f"{R}x{VOCAB} f32", 2 * per_set, ms, R)
     else:
         calls = [(lambda x=x: sharded.sharded_argmax(x, c_lo)) for x in logits]
-        ms = timed(calls, 40)
+        ms = timed(calls, nreps(40))
         record("argmax (vocab-sharded + all-reduce MAX of packed keys)", f"{R}x{VOCAB}/{world} f32", per_set + 4 * R, ms, R,
                sharded_over=world, note="rows_per_s counts each of the 256 rows once per rank; exchange is 2 KB per rank")
         table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
         calls = [(lambda x=x, i=i: sharded.sharded_softmax(x, out=outs[i % len(outs)])) for i, x in enumerate(logits)]
-        ms = timed(calls, 40)
+        ms = timed(calls, nreps(40))
         record("softmax (vocab-sharded + all-reduce MAX, SUM)", f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R,
                sharded_over=world)
         table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
-    return table
+
+
+def main():
+    """python -m cuda_llm_b200.opbench [--only GROUP] [--reps-scale X]: the single-GPU table, one line per entry."""
+    import argparse
+    from . import build, lib
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--reps-scale", type=float, default=1.0)
+    args = ap.parse_args()
+    build.build()
+    L = lib.load()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        rows = run(L, lib, dev, stream, 1, 0, torch.cuda.synchronize, lambda ms: ms, only=args.only,
+                   reps_scale=args.reps_scale)
+    for e in rows:
+        print(json.dumps(e))
+
+
+if __name__ == "__main__":
+    main()
