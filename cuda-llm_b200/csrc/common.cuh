@@ -25,6 +25,14 @@ template <> struct Elem<float> {
   static __device__ __forceinline__ uint4 pack(const float* f) {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
   }
+  // the same vector as kPerVec/2 pairs, for the packed fp32x2 arithmetic of sm_100
+  static __device__ __forceinline__ void unpack2(const uint4& v, float2* f) {
+    f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+    f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+  }
+  static __device__ __forceinline__ uint4 pack2(const float2* f) {
+    return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
+  }
 };
 template <> struct Elem<__half> {
   static constexpr int kPerVec = 8;
@@ -41,6 +49,18 @@ template <> struct Elem<__half> {
     __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+  }
+  static __device__ __forceinline__ void unpack2(const uint4& v, float2* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __half22float2(h[i]);
+  }
+  static __device__ __forceinline__ uint4 pack2(const float2* f) {
+    uint4 v;
+    __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __float22half2_rn(f[i]);
     return v;
   }
 };

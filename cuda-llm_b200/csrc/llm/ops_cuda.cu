@@ -259,7 +259,7 @@ Tensor cuda_softmax_last_dim(const Tensor& x) {
   Tensor out(x.dtype(), x.shape(), DeviceType::CUDA);
   const int64_t width = x.shape().back(), rows = int64_t(x.numel()) / width;
   if (rows == 0) throw std::runtime_error("CUDA error: cuda_softmax_last_dim launch with an empty grid");
-  void* ws = scratch("softmax").get(b2_softmax_workspace_bytes(rows), false);
+  void* ws = scratch("softmax").get(b2_softmax_workspace_bytes(rows), true);
   check(b2_softmax_rows(x.data(), out.data(), rows, width, dtype_code(x), mode_code(), ws, 0));
   return out;
 }

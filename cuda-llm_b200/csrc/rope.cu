@@ -82,16 +82,22 @@ struct HeadSet {           // one [tokens, heads, head_dim] tensor with its opti
 constexpr int kItemUnroll = 4;
 constexpr int kWarpsPerCta = kThreads / kWarpSize;
 
+// cos and sin of the lane's frequencies, two consecutive frequencies per float2 (the layout of the
+// packed fp32x2 instructions of sm_100: one instruction, two results)
+template <int P> struct LaneAngles { float2 c[P], s[P], neg_s[P]; };
+
 template <typename T, bool kNorm, bool kOrdered>
 __device__ __forceinline__ void rope_token_heads(const uint4* x, const uint4* w, uint4* out, int items, int hv,
-                                                 int hv_shift, int lane, const float2* cs, float inv_dim, float eps) {
-  constexpr int N = Elem<T>::kPerVec;
+                                                 int hv_shift, int lane, const LaneAngles<Elem<T>::kPerVec / 2>& ang,
+                                                 float inv_dim, float eps) {
+  constexpr int P = Elem<T>::kPerVec / 2;   // element pairs per 16-byte vector
   const int v = lane & (hv - 1);
-  float wl[N], wh[N];
+  float2 wl[P], wh[P];
   if (kNorm) {
-    Elem<T>::unpack(ld_reuse(w + v), wl);
-    Elem<T>::unpack(ld_reuse(w + hv + v), wh);
+    Elem<T>::unpack2(ld_reuse(w + v), wl);
+    Elem<T>::unpack2(ld_reuse(w + hv + v), wh);
   }
+  const int last = items - 1;
   // every lane runs the same number of steps, so the shuffles below are converged
   for (int base = 0; base < items; base += kWarpSize * kItemUnroll) {
     uint4 raw_lo[kItemUnroll], raw_hi[kItemUnroll];
@@ -101,8 +107,11 @@ __device__ __forceinline__ void rope_token_heads(const uint4* x, const uint4* w,
     for (int u = 0; u < kItemUnroll; ++u) {
       const int item = base + u * kWarpSize + lane;
       ok[u] = item < items;
-      where[u] = ((item >> hv_shift) << (hv_shift + 1)) + v;   // head * (2*hv) + v
-      if (ok[u]) {
+      // a lane past the end re-reads the last head (same vector position): valid memory, a consistent
+      // group for the shuffles, and nothing is stored for it
+      const int head = (ok[u] ? item : last) >> hv_shift;
+      where[u] = (head << (hv_shift + 1)) + v;   // head * (2*hv) + v
+      if (base + u * kWarpSize < items) {
         raw_lo[u] = ld_stream(x + where[u]);
         raw_hi[u] = ld_stream(x + where[u] + hv);
       }
@@ -110,34 +119,41 @@ __device__ __forceinline__ void rope_token_heads(const uint4* x, const uint4* w,
 #pragma unroll
     for (int u = 0; u < kItemUnroll; ++u) {
       if (base + u * kWarpSize >= items) break;   // uniform across the warp
-      float lo[N], hi[N];
-      if (ok[u]) {
-        Elem<T>::unpack(raw_lo[u], lo);
-        Elem<T>::unpack(raw_hi[u], hi);
-      } else {
-#pragma unroll
-        for (int e = 0; e < N; ++e) lo[e] = hi[e] = 0.0f;
-      }
+      float2 lo[P], hi[P];
+      Elem<T>::unpack2(raw_lo[u], lo);
+      Elem<T>::unpack2(raw_hi[u], hi);
       if (kNorm) {
-        float ss = 0.0f;
+        float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int e = 0; e < N; ++e) ss = fmaf(lo[e], lo[e], ss);
+        for (int e = 0; e < P; ++e) acc = __ffma2_rn(lo[e], lo[e], acc);
 #pragma unroll
-        for (int e = 0; e < N; ++e) ss = fmaf(hi[e], hi[e], ss);
-        ss = group_sum(ss, hv);
+        for (int e = 0; e < P; ++e) acc = __ffma2_rn(hi[e], hi[e], acc);
+        const float ss = group_sum(acc.x + acc.y, hv);
         const float inv = rsqrtf(fmaf(ss, inv_dim, eps));
+        const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-        for (int e = 0; e < N; ++e) {
-          lo[e] = (lo[e] * inv) * wl[e];
-          hi[e] = (hi[e] * inv) * wh[e];
+        for (int e = 0; e < P; ++e) {
+          lo[e] = __fmul2_rn(__fmul2_rn(lo[e], inv2), wl[e]);
+          hi[e] = __fmul2_rn(__fmul2_rn(hi[e], inv2), wh[e]);
+        }
+      }
+      float2 out_lo[P], out_hi[P];
+#pragma unroll
+      for (int e = 0; e < P; ++e) {
+        if (kOrdered) {
+          // written as in the reference kernel, contraction left to the compiler as it is there
+          out_lo[e].x = lo[e].x * ang.c[e].x - hi[e].x * ang.s[e].x;
+          out_hi[e].x = hi[e].x * ang.c[e].x + lo[e].x * ang.s[e].x;
+          out_lo[e].y = lo[e].y * ang.c[e].y - hi[e].y * ang.s[e].y;
+          out_hi[e].y = hi[e].y * ang.c[e].y + lo[e].y * ang.s[e].y;
+        } else {
+          out_lo[e] = __ffma2_rn(hi[e], ang.neg_s[e], __fmul2_rn(lo[e], ang.c[e]));   // a*c - b*s
+          out_hi[e] = __ffma2_rn(lo[e], ang.s[e], __fmul2_rn(hi[e], ang.c[e]));       // a*s + b*c
         }
       }
       if (ok[u]) {
-        float out_lo[N], out_hi[N];
-#pragma unroll
-        for (int e = 0; e < N; ++e) rotate<kOrdered>(lo[e], hi[e], cs[e], out_lo[e], out_hi[e]);
-        st_stream(out + where[u], Elem<T>::pack(out_lo));
-        st_stream(out + where[u] + hv, Elem<T>::pack(out_hi));
+        st_stream(out + where[u], Elem<T>::pack2(out_lo));
+        st_stream(out + where[u] + hv, Elem<T>::pack2(out_hi));
       }
     }
   }
@@ -148,28 +164,38 @@ __global__ void __launch_bounds__(kThreads, 2)
 rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
                    int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
   constexpr int N = Elem<T>::kPerVec;
-  extern __shared__ float2 table[];   // [warps per CTA][half]
+  extern __shared__ float table[];    // per warp: cos[half] then sin[half]
   const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float2* cs_row = table + warp * half;
+  float* cos_row = table + warp * head_dim;
+  float* sin_row = cos_row + half;
   const int vecs_per_head = 2 * hv;
   const float inv_dim = 1.0f / float(head_dim);
 
   for (int64_t t = int64_t(blockIdx.x) * kWarpsPerCta + warp; t < tokens; t += int64_t(gridDim.x) * kWarpsPerCta) {
     const int32_t p = positions[pos_period ? t % pos_period : t];
-    for (int j = lane; j < half; j += kWarpSize) cs_row[j] = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+    for (int j = lane; j < half; j += kWarpSize) {
+      const float2 cs = rope_cos_sin<kOrdered>(p, j, head_dim, theta, freq, half);
+      cos_row[j] = cs.x;
+      sin_row[j] = cs.y;
+    }
     __syncwarp();
-    float2 cs[N];                       // this lane's frequencies: the same for every head
+    LaneAngles<N / 2> ang;              // this lane's frequencies: the same for every head
+    const int first = (lane & (hv - 1)) * N;
 #pragma unroll
-    for (int e = 0; e < N; ++e) cs[e] = cs_row[(lane & (hv - 1)) * N + e];
+    for (int e = 0; e < N / 2; ++e) {
+      ang.c[e] = *reinterpret_cast<const float2*>(cos_row + first + 2 * e);
+      ang.s[e] = *reinterpret_cast<const float2*>(sin_row + first + 2 * e);
+      ang.neg_s[e] = make_float2(-ang.s[e].x, -ang.s[e].y);
+    }
 
     rope_token_heads<T, kNorm, kOrdered>(
         reinterpret_cast<const uint4*>(q.x) + size_t(t) * q.heads * vecs_per_head, reinterpret_cast<const uint4*>(q.w),
-        reinterpret_cast<uint4*>(q.out) + size_t(t) * q.heads * vecs_per_head, q.heads * hv, hv, hv_shift, lane, cs,
+        reinterpret_cast<uint4*>(q.out) + size_t(t) * q.heads * vecs_per_head, q.heads * hv, hv, hv_shift, lane, ang,
         inv_dim, eps);
     if (k.heads > 0)
       rope_token_heads<T, kNorm, kOrdered>(
           reinterpret_cast<const uint4*>(k.x) + size_t(t) * k.heads * vecs_per_head, reinterpret_cast<const uint4*>(k.w),
-          reinterpret_cast<uint4*>(k.out) + size_t(t) * k.heads * vecs_per_head, k.heads * hv, hv, hv_shift, lane, cs,
+          reinterpret_cast<uint4*>(k.out) + size_t(t) * k.heads * vecs_per_head, k.heads * hv, hv, hv_shift, lane, ang,
           inv_dim, eps);
     __syncwarp();  // the warp's table slice is rewritten for its next token
   }
@@ -251,7 +277,7 @@ int launch_vector(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens
                   int64_t pos_period, float eps, float theta, cudaStream_t s, const char* what) {
   const int64_t ctas = (tokens + kWarpsPerCta - 1) / kWarpsPerCta, cap = int64_t(sm_count()) * 64;
   const unsigned grid = unsigned(ctas < cap ? ctas : cap);
-  const size_t smem = size_t(kWarpsPerCta) * size_t(head_dim / 2) * sizeof(float2);
+  const size_t smem = size_t(kWarpsPerCta) * size_t(head_dim) * sizeof(float);
   int hv_shift = 0;
   while ((1 << hv_shift) < hv) ++hv_shift;
   rope_tokens_kernel<T, kNorm, kOrdered><<<grid, kThreads, smem, s>>>(

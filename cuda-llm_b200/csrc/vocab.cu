@@ -167,20 +167,59 @@ __device__ __forceinline__ void online_update(float& m, float& m2, float& s, con
   }
 }
 
+// ---- bulk asynchronous copy (TMA without a tensor map) and its mbarrier, in raw PTX.
+// Source, destination and size must be multiples of 16 bytes.  Never used with multicast.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbarrier_init(uint64_t* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbarrier_expect_bytes(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* global_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
+               "l"(global_src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbarrier_done(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(done)
+               : "r"(smem_addr(bar)), "r"(parity)
+               : "memory");
+  return done != 0;
+}
+// Bounded wait: about a quarter of a second of polling, then give up (the caller raises a status bit).
+__device__ __forceinline__ bool mbarrier_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    if (mbarrier_done(bar, parity)) return true;
+    __nanosleep(32);
+  }
+  return false;
+}
+
 // ---- fast mode: one cluster per row, the row stays in distributed shared memory.
-// The kernel is bound by instruction issue before HBM unless every pass is lean, so:
-//   pass A  HBM -> shared memory (16-byte loads, four in flight), running max: ~1.5 instr/element
-//           cluster barrier, row max from all slices through DSMEM
-//   pass B  shared memory in place: e = 2^(x*log2e - max*log2e), running sum: ~3.5 instr/element
-//           cluster barrier, row sum from all slices
-//   pass C  shared memory -> HBM: e * (1/sum), 16-byte stores: ~1.75 instr/element
-template <typename T, bool kVec>
+//   load    kBulk: one thread issues bulk asynchronous copies (TMA) for the CTA's whole slice, so
+//           all of it is in flight at once and no register holds it; otherwise 16-byte thread loads
+//   pass A  running max over the slice in shared memory; slice max pushed into every CTA of the cluster
+//   pass B  in place: e = 2^(x*log2e - max*log2e), running sum; slice sum pushed likewise
+//   pass C  shared memory -> HBM: e * (1/sum), 16-byte stores
+// Values cross CTAs by remote shared-memory stores (DSMEM) followed by a cluster barrier, so
+// nothing reads a neighbour's memory after the last barrier and CTAs retire independently.
+// `status` (may be null): bit 0 is raised if the bulk-copy wait ran out; outputs are then invalid.
+constexpr int kMaxClusterRanks = 16;
+constexpr uint32_t kBulkChunk = 16 * 1024;
+
+template <typename T, bool kVec, bool kBulk>
 __global__ void __launch_bounds__(kSoftThreads, 2)
-softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
+softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice, int* status) {
   constexpr int N = Elem<T>::kPerVec;
-  extern __shared__ __align__(16) float vals[];
+  extern __shared__ __align__(128) float vals[];
   __shared__ float scratch[32];
-  __shared__ float published[2];  // slice max, slice sum: read by the whole cluster
+  __shared__ float peer_max[kMaxClusterRanks], peer_sum[kMaxClusterRanks];   // written by the other CTAs
+  __shared__ __align__(8) uint64_t load_barrier;
 
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
@@ -193,9 +232,18 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
   const int n4 = n >> 2;                       // whole float4 groups of the slice in shared memory
   float4* vals4 = reinterpret_cast<float4*>(vals);
 
-  // ---- pass A
-  float m = -INFINITY;
-  if (kVec) {
+  // ---- load
+  if (kBulk) {
+    if (tid == 0) {
+      mbarrier_init(&load_barrier, 1);
+      const uint32_t bytes = uint32_t(n4) * 16u;            // the 16-byte multiple; a tail of < 4 floats is loaded below
+      mbarrier_expect_bytes(&load_barrier, bytes);
+      for (uint32_t off = 0; off < bytes; off += kBulkChunk)
+        bulk_load(reinterpret_cast<char*>(vals) + off, reinterpret_cast<const char*>(src) + off,
+                  bytes - off < kBulkChunk ? bytes - off : kBulkChunk, &load_barrier);
+    }
+    for (int i = (n4 << 2) + tid; i < n; i += step) vals[i] = Elem<T>::load(src + i);
+  } else if (kVec) {
     const int nvec = n / N;
     const uint4* vp = reinterpret_cast<const uint4*>(src);
     for (int v0 = tid; v0 < nvec; v0 += step * 4) {
@@ -209,22 +257,36 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
           float e[N];
           Elem<T>::unpack(r[k], e);
 #pragma unroll
-          for (int q = 0; q < N; q += 4) {
-            vals4[(v * N + q) >> 2] = make_float4(e[q], e[q + 1], e[q + 2], e[q + 3]);
-            m = fmaxf(fmaxf(m, fmaxf(e[q], e[q + 1])), fmaxf(e[q + 2], e[q + 3]));
-          }
+          for (int q = 0; q < N; q += 4) vals4[(v * N + q) >> 2] = make_float4(e[q], e[q + 1], e[q + 2], e[q + 3]);
         }
       }
     }
-    for (int i = nvec * N + tid; i < n; i += step) { const float e = Elem<T>::load(src + i); vals[i] = e; m = fmaxf(m, e); }
+    for (int i = nvec * N + tid; i < n; i += step) vals[i] = Elem<T>::load(src + i);
   } else {
-    for (int i = tid; i < n; i += step) { const float e = Elem<T>::load(src + i); vals[i] = e; m = fmaxf(m, e); }
+    for (int i = tid; i < n; i += step) vals[i] = Elem<T>::load(src + i);
   }
-  m = block_max(m, scratch);
-  if (tid == 0) published[0] = m;
+  // every CTA of the cluster is running (and this CTA's barrier is initialised) before anyone
+  // polls or writes into a neighbour's shared memory
+  cluster.sync();
+  bool load_ok = true;
+  if (kBulk) {
+    load_ok = mbarrier_wait_bounded(&load_barrier, 0);
+    if (!load_ok && tid == 0 && status != nullptr) atomicOr(status, 1);
+  }
+
+  // ---- pass A
+  float m0 = -INFINITY, m1 = -INFINITY;
+  for (int g = tid; g < n4; g += step) {
+    const float4 t = vals4[g];
+    m0 = fmaxf(m0, fmaxf(t.x, t.y));
+    m1 = fmaxf(m1, fmaxf(t.z, t.w));
+  }
+  for (int i = (n4 << 2) + tid; i < n; i += step) m0 = fmaxf(m0, vals[i]);
+  const float slice_max = block_max(fmaxf(m0, m1), scratch);
+  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_max[rank], tid) = slice_max;
   cluster.sync();
   float row_max = -INFINITY;
-  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, *cluster.map_shared_rank(&published[0], r));
+  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, peer_max[r]);
   const float neg_m2 = -row_max * kLog2e;
 
   // ---- pass B
@@ -238,11 +300,11 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
     s1 += t.z + t.w;
   }
   for (int i = (n4 << 2) + tid; i < n; i += step) { const float e = fast_exp2(fmaf(vals[i], kLog2e, neg_m2)); vals[i] = e; s0 += e; }
-  const float s = block_sum(s0 + s1, scratch);
-  if (tid == 0) published[1] = s;
+  const float slice_sum = block_sum(s0 + s1, scratch);
+  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_sum[rank], tid) = slice_sum;
   cluster.sync();
   float row_sum = 0.0f;
-  for (unsigned r = 0; r < ranks; ++r) row_sum += *cluster.map_shared_rank(&published[1], r);  // rank order on every CTA
+  for (unsigned r = 0; r < ranks; ++r) row_sum += peer_sum[r];   // rank order: the same sum on every CTA of the row
   const float inv_sum = 1.0f / row_sum;
 
   // ---- pass C
@@ -261,7 +323,86 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice) {
   } else {
     for (int i = tid; i < n; i += step) Elem<T>::store(dst + i, vals[i] * inv_sum);
   }
-  cluster.sync();  // nobody leaves while a neighbour may still read its published[]
+  // a copy that had not landed when the first wait gave up must not outlive this CTA's shared memory
+  if (kBulk && !load_ok) mbarrier_wait_bounded(&load_barrier, 0);
+}
+
+// ---- fast mode, register-resident form: the same three steps, but every thread keeps its K
+// 16-byte vectors of the row in registers from the load to the store.  All loads of the slice
+// are in flight at once (K per thread), nothing passes through shared memory, and the loops are
+// fully unrolled: ~6 instructions per element.  Used whenever the slice fits K <= 12 vectors
+// per thread; the shared-memory kernel above takes the rest.
+template <typename T, int K>
+__global__ void __launch_bounds__(kSoftThreads, 2)
+softmax_cluster_reg_kernel(const T* x, T* out, int64_t width, int64_t slice) {
+  constexpr int N = Elem<T>::kPerVec;
+  __shared__ float scratch[32];
+  __shared__ float peer_max[kMaxClusterRanks], peer_sum[kMaxClusterRanks];   // written by the other CTAs
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
+  const int64_t row = blockIdx.x / ranks;
+  const int64_t lo = int64_t(rank) * slice;
+  const int nvec = int(lo >= width ? 0 : (width - lo < slice ? width - lo : slice)) / N;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * width + lo);
+  uint4* dst = reinterpret_cast<uint4*>(out + row * width + lo);
+  const int tid = threadIdx.x;
+
+  uint4 raw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int v = tid + k * kSoftThreads;
+    if (v < nvec) raw[k] = ld_stream(src + v);
+  }
+  cluster.sync();   // every CTA of the cluster is running before anyone writes into a neighbour's shared memory
+
+  float e[K][N];
+  float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    if (tid + k * kSoftThreads < nvec) {
+      Elem<T>::unpack(raw[k], e[k]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < N; ++q) e[k][q] = -INFINITY;   // contributes exp(-inf) = 0
+    }
+#pragma unroll
+    for (int q = 0; q < N; q += 2) { m0 = fmaxf(m0, e[k][q]); m1 = fmaxf(m1, e[k][q + 1]); }
+  }
+  const float slice_max = block_max(fmaxf(m0, m1), scratch);
+  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_max[rank], tid) = slice_max;
+  cluster.sync();
+  float row_max = -INFINITY;
+  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, peer_max[r]);
+  const float neg_m2 = -row_max * kLog2e;
+
+  float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+#pragma unroll
+    for (int q = 0; q < N; q += 2) {
+      e[k][q] = fast_exp2(fmaf(e[k][q], kLog2e, neg_m2));
+      e[k][q + 1] = fast_exp2(fmaf(e[k][q + 1], kLog2e, neg_m2));
+      s0 += e[k][q];
+      s1 += e[k][q + 1];
+    }
+  }
+  const float slice_sum = block_sum(s0 + s1, scratch);
+  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_sum[rank], tid) = slice_sum;
+  cluster.sync();
+  float row_sum = 0.0f;
+  for (unsigned r = 0; r < ranks; ++r) row_sum += peer_sum[r];   // rank order: the same sum on every CTA of the row
+  const float inv_sum = 1.0f / row_sum;
+
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int v = tid + k * kSoftThreads;
+    if (v < nvec) {
+#pragma unroll
+      for (int q = 0; q < N; ++q) e[k][q] *= inv_sum;
+      st_stream(dst + v, Elem<T>::pack(e[k]));
+    }
+  }
 }
 
 // ---- row statistics (max, sum of exp(x - max)), one CTA per row, one pass, online rescaling
@@ -414,9 +555,10 @@ int launch_argmax_typed(const void* logits_, int64_t rows, int64_t width, int64_
   return launch_status("argmax_rows");
 }
 
-template <typename T, bool kVec>
-int launch_softmax_cluster(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
-  auto kernel = softmax_cluster_kernel<T, kVec>;
+template <typename T, bool kVec, bool kBulk>
+int launch_softmax_cluster(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, int* status,
+                           cudaStream_t s) {
+  auto kernel = softmax_cluster_kernel<T, kVec, kBulk>;
   const size_t smem = size_t(slice) * sizeof(float);
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
@@ -439,11 +581,57 @@ int launch_softmax_cluster(const T* x, T* out, int64_t rows, int64_t width, int 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, x, out, width, slice) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, x, out, width, slice, status) != cudaSuccess) {
     cudaGetLastError();  // the two-pass path takes over
     return B2_ERR_UNSUPPORTED;
   }
   return B2_OK;
+}
+
+template <typename T, int K>
+int launch_softmax_reg(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
+  auto kernel = softmax_cluster_reg_kernel<T, K>;
+  if (ranks > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(rows * ranks));
+  cfg.blockDim = dim3(kSoftThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(ranks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, x, out, width, slice) != cudaSuccess) {
+    cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
+  return B2_OK;
+}
+
+// K vectors of N elements per thread stay in registers: at most 48 floats (64 registers at two CTAs per SM).
+template <typename T, int K>
+int launch_softmax_reg_if_fits(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
+  if constexpr (K * Elem<T>::kPerVec <= 48) return launch_softmax_reg<T, K>(x, out, rows, width, ranks, slice, s);
+  else return B2_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+int launch_softmax_reg_any(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
+  const int64_t vecs = slice / Elem<T>::kPerVec, per_thread = (vecs + kSoftThreads - 1) / kSoftThreads;
+  if (per_thread <= 1) return launch_softmax_reg_if_fits<T, 1>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 2) return launch_softmax_reg_if_fits<T, 2>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 4) return launch_softmax_reg_if_fits<T, 4>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 6) return launch_softmax_reg_if_fits<T, 6>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 8) return launch_softmax_reg_if_fits<T, 8>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 10) return launch_softmax_reg_if_fits<T, 10>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 12) return launch_softmax_reg_if_fits<T, 12>(x, out, rows, width, ranks, slice, s);
+  return B2_ERR_UNSUPPORTED;
 }
 
 template <typename T>
@@ -498,8 +686,16 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
   slice = (slice + N - 1) / N * N;
   if (size_t(slice) * sizeof(float) <= kClusterSliceBytes) {
     const bool vec = rows_vector_ok<T>(x, width) && aligned16(out);
-    const int rc = vec ? launch_softmax_cluster<T, true>(x, out, rows, width, ranks, slice, s)
-                       : launch_softmax_cluster<T, false>(x, out, rows, width, ranks, slice, s);
+    // status word: the last 16 bytes of the workspace (after the 2*rows floats of the two-pass path)
+    int* status = reinterpret_cast<int*>(static_cast<char*>(workspace) + softmax_workspace_bytes(rows) - 16);
+    int rc;
+    static const bool reg_path = [] { const char* v = std::getenv("B2_SOFTMAX_REG"); return !v || std::atoi(v) != 0; }();
+    if (vec && reg_path && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, s) == B2_OK) return B2_OK;
+    if (vec && sizeof(T) == 4 && slice % 4 == 0)   // fp32 rows: shared memory holds the input's own bytes -> bulk copy
+      rc = launch_softmax_cluster<T, true, true>(x, out, rows, width, ranks, slice, status, s);
+    else
+      rc = vec ? launch_softmax_cluster<T, true, false>(x, out, rows, width, ranks, slice, status, s)
+               : launch_softmax_cluster<T, false, false>(x, out, rows, width, ranks, slice, status, s);
     if (rc == B2_OK) return B2_OK;
   }
   float* row_max = static_cast<float*>(workspace);
@@ -529,7 +725,8 @@ int launch_argmax_decode(const int64_t* keys, int64_t rows, int32_t* out_ids, cu
   return launch_status("argmax_decode_keys");
 }
 
-size_t softmax_workspace_bytes(int64_t rows) { return (size_t(rows) * 2 * sizeof(float) + 15) / 16 * 16; }
+// 2*rows floats of row statistics for the two-pass path, then one 16-byte slot whose first int32 is a status word
+size_t softmax_workspace_bytes(int64_t rows) { return (size_t(rows) * 2 * sizeof(float) + 15) / 16 * 16 + 16; }
 
 int launch_softmax(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode, void* workspace,
                    cudaStream_t s) {

@@ -345,9 +345,16 @@ def softmax_workspace(device, rows: int) -> torch.Tensor:
     need = _lib.load().b2_softmax_workspace_bytes(rows)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(need, 4096), dtype=torch.uint8, device=device)   # the trailing status word starts clear
         _workspaces[key] = ws
     return ws
+
+
+def softmax_status(device, rows: int) -> int:
+    """Status word of the softmax workspace used for `rows` rows (0 = every bulk copy completed)."""
+    ws = softmax_workspace(device, rows)
+    need = _lib.load().b2_softmax_workspace_bytes(rows)
+    return int(ws[need - 16:need - 12].view(torch.int32).item())
 
 
 def _logits_req(logits, op):

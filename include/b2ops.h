@@ -188,7 +188,9 @@ B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out
  * B2_FAST keeps each row on chip (a thread-block cluster holds it in distributed
  * shared memory) when it fits, otherwise makes two passes; B2_DETERMINISTIC adds the
  * exponentials in index order in fp32, like ops_cpu and the reference kernel.
- * workspace: b2_softmax_workspace_bytes(rows) bytes (contents irrelevant).
+ * workspace: b2_softmax_workspace_bytes(rows) bytes.  Its last 16 bytes begin with an int32
+ * status word that the kernel only ever ORs into: bit 0 = a bounded wait for an on-chip bulk
+ * copy ran out and the outputs of that call are invalid.  Zero it once; the rest is scratch.
  * Replaces cuda_softmax_last_dim and kernel softk<T>
  * (include/llm/ops_cuda.h:82; src/ops_cuda.cu:132,710). */
 B2_API size_t b2_softmax_workspace_bytes(int64_t rows);

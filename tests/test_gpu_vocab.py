@@ -136,6 +136,7 @@ def test_softmax_f32(b2, port, rows, width, mode):
     x = wl.normal(rng, (rows, width), 4.0)
     got = host(ops.cuda_softmax_last_dim(dev(x), mode))
     softmax_check(got, x, port, mode, f"softmax {mode} {rows}x{width}")
+    assert ops.softmax_status(DEV, rows) == 0          # no bounded wait ran out
 
 
 def test_softmax_reference_test_literals(b2, port):
