@@ -176,6 +176,14 @@ int b2_embedding_gather(const void* table, const int32_t* ids, void* out, int64_
   return launch_gather(table, ids, out, count, hidden, vocab, dtype, status, as_stream(stream));
 }
 
+int b2_bulk_copy_timeouts(uint32_t* count) {
+  if (count == nullptr) return invalid("b2_bulk_copy_timeouts", "null pointer");
+  unsigned int n = 0;
+  const int rc = rope_bulk_timeouts(&n);
+  *count = n;
+  return rc;
+}
+
 size_t b2_argmax_workspace_bytes(int64_t rows) { return rows > 0 ? argmax_workspace_bytes(rows) : 0; }
 
 int b2_argmax_workspace_init(void* workspace, int64_t rows, b2_stream stream) {

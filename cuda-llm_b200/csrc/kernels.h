@@ -21,6 +21,7 @@ int launch_rope(const void* x, const int32_t* positions, void* out, int64_t toke
 int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
                         void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads,
                         int64_t head_dim, float eps, float theta, int dtype, cudaStream_t s);
+int rope_bulk_timeouts(unsigned int* out);   // blocking read of a device counter
 // gather.cu
 int launch_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden,
                   int64_t vocab, int dtype, int32_t* status, cudaStream_t s);

@@ -8,10 +8,12 @@
 // rope_decode_batched_kernel<T> (src/ops_cuda.cu:133-135) and, in the fused form,
 // the rmsk<T> launches in front of them (src/qwen3_layer_cuda.cu:289-292).
 #include "common.cuh"
+#include "bulk_copy.cuh"
 #include "kernels.h"
 #include "b2ops.h"
 
 #include <cmath>
+#include <cstdlib>
 
 namespace b2 {
 namespace {
@@ -202,6 +204,144 @@ rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, 
 }
 
 // ---------------------------------------------------------------------------
+// Bulk-copy (TMA) form of the vector kernel, fast mode.  The register kernel above is
+// bound by latency, not bandwidth: a warp's chain per token is position -> angles ->
+// loads -> arithmetic -> stores, and few warps fit beside its registers.  Here lane 0 of
+// each warp asks the copy engine for the NEXT token's q and k rows (one bulk copy each,
+// into the warp's second shared-memory stage, tracked by an mbarrier) before the warp
+// starts on the current token, so HBM reads are always one token ahead and cost no
+// registers.  Persistent grid: a warp walks tokens warp_id, warp_id + all_warps, ...
+// Shared memory per warp: two stages of (q row + k row) and the cos/sin table.
+// ---------------------------------------------------------------------------
+static __device__ unsigned int g_rope_bulk_timeouts = 0;   // bounded waits that ran out (0 in a healthy run)
+
+template <typename T, bool kNorm>
+__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int items, int hv,
+                                                       int hv_shift, int lane,
+                                                       const LaneAngles<Elem<T>::kPerVec / 2>& ang, float inv_dim,
+                                                       float eps) {
+  constexpr int P = Elem<T>::kPerVec / 2;
+  const int v = lane & (hv - 1);
+  float2 wl[P], wh[P];
+  if (kNorm) {
+    Elem<T>::unpack2(ld_reuse(w + v), wl);
+    Elem<T>::unpack2(ld_reuse(w + hv + v), wh);
+  }
+  const int last = items - 1;
+  for (int base = 0; base < items; base += kWarpSize) {     // uniform trip count: shuffles stay converged
+    const int item = base + lane;
+    const bool ok = item < items;
+    const int where = (((ok ? item : last) >> hv_shift) << (hv_shift + 1)) + v;
+    float2 lo[P], hi[P];
+    Elem<T>::unpack2(xs[where], lo);
+    Elem<T>::unpack2(xs[where + hv], hi);
+    if (kNorm) {
+      float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+      for (int e = 0; e < P; ++e) acc = __ffma2_rn(lo[e], lo[e], acc);
+#pragma unroll
+      for (int e = 0; e < P; ++e) acc = __ffma2_rn(hi[e], hi[e], acc);
+      const float ss = group_sum(acc.x + acc.y, hv);
+      const float inv = rsqrtf(fmaf(ss, inv_dim, eps));
+      const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+      for (int e = 0; e < P; ++e) {
+        lo[e] = __fmul2_rn(__fmul2_rn(lo[e], inv2), wl[e]);
+        hi[e] = __fmul2_rn(__fmul2_rn(hi[e], inv2), wh[e]);
+      }
+    }
+    float2 out_lo[P], out_hi[P];
+#pragma unroll
+    for (int e = 0; e < P; ++e) {
+      out_lo[e] = __ffma2_rn(hi[e], ang.neg_s[e], __fmul2_rn(lo[e], ang.c[e]));   // a*c - b*s
+      out_hi[e] = __ffma2_rn(lo[e], ang.s[e], __fmul2_rn(hi[e], ang.c[e]));       // a*s + b*c
+    }
+    if (ok) {
+      st_stream(out + where, Elem<T>::pack2(out_lo));
+      st_stream(out + where + hv, Elem<T>::pack2(out_hi));
+    }
+  }
+}
+
+template <typename T, bool kNorm>
+__global__ void __launch_bounds__(kThreads, 2)
+rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
+                        int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
+  constexpr int N = Elem<T>::kPerVec;
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int vecs_per_head = 2 * hv;
+  const uint32_t q_bytes = uint32_t(q.heads) * vecs_per_head * 16u, k_bytes = uint32_t(k.heads) * vecs_per_head * 16u;
+  const uint32_t stage_bytes = q_bytes + k_bytes, per_warp = 2u * stage_bytes + uint32_t(head_dim) * 4u;
+  unsigned char* mine = bulk_smem + size_t(warp) * per_warp;
+  float* cos_row = reinterpret_cast<float*>(mine + 2u * stage_bytes);
+  float* sin_row = cos_row + half;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem + size_t(warps) * per_warp) + 2 * warp;
+  const float inv_dim = 1.0f / float(head_dim);
+
+  if (lane == 0) { mbarrier_init(&bars[0], 1); mbarrier_init(&bars[1], 1); }
+  __syncwarp();
+
+  const int64_t stride = int64_t(gridDim.x) * warps;
+  int64_t t = int64_t(blockIdx.x) * warps + warp;
+  // lane 0 only: ask for one token's rows into a stage
+  auto request = [&](int64_t token, int stage) {
+    unsigned char* dst = mine + uint32_t(stage) * stage_bytes;
+    mbarrier_expect_bytes(&bars[stage], stage_bytes);
+    bulk_load(dst, static_cast<const unsigned char*>(q.x) + size_t(token) * q_bytes, q_bytes, &bars[stage]);
+    if (k_bytes != 0u)
+      bulk_load(dst + q_bytes, static_cast<const unsigned char*>(k.x) + size_t(token) * k_bytes, k_bytes, &bars[stage]);
+  };
+  if (t < tokens && lane == 0) request(t, 0);
+  int32_t p = t < tokens ? positions[pos_period ? t % pos_period : t] : 0;
+
+  for (int it = 0; t < tokens; ++it, t += stride) {
+    const int stage = it & 1;
+    const int64_t t_next = t + stride;
+    int32_t p_next = 0;
+    if (t_next < tokens) {
+      // the other stage was last read during the previous step; every lane passed the __syncwarp
+      // that ends that step after consuming what it read
+      if (lane == 0) { fence_before_bulk_copy(); request(t_next, stage ^ 1); }
+      p_next = positions[pos_period ? t_next % pos_period : t_next];
+    }
+    for (int j = lane; j < half; j += kWarpSize) {
+      const float2 cs = rope_cos_sin<false>(p, j, head_dim, theta, freq, half);
+      cos_row[j] = cs.x;
+      sin_row[j] = cs.y;
+    }
+    __syncwarp();
+    LaneAngles<N / 2> ang;
+    const int first = (lane & (hv - 1)) * N;
+#pragma unroll
+    for (int e = 0; e < N / 2; ++e) {
+      ang.c[e] = *reinterpret_cast<const float2*>(cos_row + first + 2 * e);
+      ang.s[e] = *reinterpret_cast<const float2*>(sin_row + first + 2 * e);
+      ang.neg_s[e] = make_float2(-ang.s[e].x, -ang.s[e].y);
+    }
+
+    const uint32_t parity = uint32_t(it >> 1) & 1u;
+    if (!mbarrier_wait_bounded(&bars[stage], parity)) {
+      // never expected: record it, give both stages' copies one more bounded chance to land, and stop
+      if (lane == 0) atomicAdd(&g_rope_bulk_timeouts, 1u);
+      mbarrier_wait_bounded(&bars[stage], parity);
+      if (t_next < tokens) mbarrier_wait_bounded(&bars[stage ^ 1], uint32_t((it + 1) >> 1) & 1u);
+      break;
+    }
+    const uint4* xs = reinterpret_cast<const uint4*>(mine + uint32_t(stage) * stage_bytes);
+    rope_heads_from_shared<T, kNorm>(xs, reinterpret_cast<const uint4*>(q.w),
+                                     reinterpret_cast<uint4*>(q.out) + size_t(t) * q.heads * vecs_per_head, q.heads * hv, hv,
+                                     hv_shift, lane, ang, inv_dim, eps);
+    if (k.heads > 0)
+      rope_heads_from_shared<T, kNorm>(xs + q.heads * vecs_per_head, reinterpret_cast<const uint4*>(k.w),
+                                       reinterpret_cast<uint4*>(k.out) + size_t(t) * k.heads * vecs_per_head, k.heads * hv,
+                                       hv, hv_shift, lane, ang, inv_dim, eps);
+    __syncwarp();   // stage and table are free again
+    p = p_next;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Scalar kernel for shapes the vector kernel cannot take (tiny or odd head_dim,
 // unaligned views): one (low, high) pair per thread per step.  With kNorm one warp
 // owns a head and reduces it with shuffles.
@@ -272,9 +412,38 @@ template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
   return true;
 }
 
+template <typename T, bool kNorm>
+bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv, int hv_shift,
+                 int64_t pos_period, float eps, float theta, cudaStream_t s) {
+  static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
+  if (!enabled) return false;
+  const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = 2 * stage + size_t(head_dim) * 4;
+  const size_t budget = 100 * 1024;                       // two CTAs per SM
+  int warps = int(budget / (per_warp + 16));
+  if (warps < 1) return false;                            // rows too long for two stages: the register kernel takes over
+  if (warps > kWarpsPerCta) warps = kWarpsPerCta;
+  if (int64_t(warps) > tokens) warps = int(tokens);
+  const size_t smem = size_t(warps) * per_warp + size_t(warps) * 16;
+  auto kernel = rope_tokens_bulk_kernel<T, kNorm>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * 2;
+  kernel<<<unsigned(ctas < cap ? ctas : cap), warps * kWarpSize, smem, s>>>(q, k, positions, tokens, int(head_dim), hv,
+                                                                          hv_shift, pos_period, eps, theta,
+                                                                          make_table(head_dim, theta));
+  return true;
+}
+
 template <typename T, bool kNorm, bool kOrdered>
 int launch_vector(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv,
                   int64_t pos_period, float eps, float theta, cudaStream_t s, const char* what) {
+  if (!kOrdered) {
+    int shift = 0;
+    while ((1 << shift) < hv) ++shift;
+    if (launch_bulk<T, kNorm>(q, k, positions, tokens, head_dim, hv, shift, pos_period, eps, theta, s)) return launch_status(what);
+  }
   const int64_t ctas = (tokens + kWarpsPerCta - 1) / kWarpsPerCta, cap = int64_t(sm_count()) * 64;
   const unsigned grid = unsigned(ctas < cap ? ctas : cap);
   const size_t smem = size_t(kWarpsPerCta) * size_t(head_dim) * sizeof(float);
@@ -340,6 +509,10 @@ int launch_qk_typed(const void* q, const void* k, const void* qw, const void* kw
 }
 
 }  // namespace
+
+int rope_bulk_timeouts(unsigned int* out) {
+  return cudaMemcpyFromSymbol(out, g_rope_bulk_timeouts, sizeof(unsigned int)) == cudaSuccess ? B2_OK : launch_status("b2_bulk_copy_timeouts");
+}
 
 int launch_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads, int64_t head_dim,
                 int64_t pos_period, float theta, int dtype, int mode, cudaStream_t s) {

@@ -16,6 +16,7 @@
 // with two cudaMalloc, two cudaFree and a blocking copy per call, :711) and softk<T>
 // (src/ops_cuda.cu:132: one thread per row, strided access).
 #include "common.cuh"
+#include "bulk_copy.cuh"
 #include "kernels.h"
 #include "b2ops.h"
 
@@ -165,39 +166,6 @@ __device__ __forceinline__ void online_update(float& m, float& m2, float& s, con
 #pragma unroll
     for (int q = 0; q < COUNT; ++q) s += fast_exp2(t[q] - m2);
   }
-}
-
-// ---- bulk asynchronous copy (TMA without a tensor map) and its mbarrier, in raw PTX.
-// Source, destination and size must be multiples of 16 bytes.  Never used with multicast.
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbarrier_init(uint64_t* bar, uint32_t arrivals) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void mbarrier_expect_bytes(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* global_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
-               "l"(global_src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
-}
-__device__ __forceinline__ bool mbarrier_done(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-               : "=r"(done)
-               : "r"(smem_addr(bar)), "r"(parity)
-               : "memory");
-  return done != 0;
-}
-// Bounded wait: about a quarter of a second of polling, then give up (the caller raises a status bit).
-__device__ __forceinline__ bool mbarrier_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    if (mbarrier_done(bar, parity)) return true;
-    __nanosleep(32);
-  }
-  return false;
 }
 
 // ---- fast mode: one cluster per row, the row stays in distributed shared memory.

@@ -124,6 +124,13 @@ B2_API int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, c
                            int64_t q_heads, int64_t k_heads, int64_t head_dim, float eps, float theta,
                            int dtype, b2_stream stream);
 
+/* Health check for the kernels that stage rows through on-chip bulk copies: every wait on such a
+ * copy is bounded, and *count (host memory) receives how many waits have run out on the current
+ * device since the library was loaded.  0 in a healthy run; anything else means outputs of some
+ * earlier b2_rope / b2_qk_norm_rope call are invalid.  Blocking (it copies a device counter to
+ * the host).  No reference counterpart. */
+B2_API int b2_bulk_copy_timeouts(uint32_t* count);
+
 /* ---- embedding-row gather --------------------------------------------------- */
 
 /* out[t,:] = table[ids[t],:], bit-exact.  An id outside [0, vocab) never reaches

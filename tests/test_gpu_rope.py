@@ -190,3 +190,10 @@ def test_fused_scalar_fallback_and_q_only(b2, port):
     ops.qk_norm_rope_out(dev(q), None, dev(gq), None, dev(pos), wl.EPS, 1e4, qo, None)
     nrm = port.rms_norm(q.reshape(-1, 6), gq, wl.EPS).reshape(q.shape)
     close_rope_f32(host(qo), port.rope(nrm, pos, 1e4), nrm, "fused scalar")
+
+
+def test_no_bulk_copy_wait_ran_out(b2):
+    """The bulk-copy kernels bound every wait; a healthy run never exhausts one (runs after the tests above)."""
+    import ctypes
+    n = ctypes.c_uint32(12345)
+    assert b2.b2_bulk_copy_timeouts(ctypes.byref(n)) == 0 and n.value == 0
