@@ -215,55 +215,72 @@ rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, 
 // ---------------------------------------------------------------------------
 static __device__ unsigned int g_rope_bulk_timeouts = 0;   // bounded waits that ran out (0 in a healthy run)
 
-template <typename T, bool kNorm>
-__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int items, int hv,
-                                                       int hv_shift, int lane,
+// One step: the item at vector index `where` of the staged row (low half; partner at where + hv).
+template <typename T, bool kNorm, int P>
+__device__ __forceinline__ void rope_item_from_shared(const uint4* xs, uint4* out, int where, int hv, bool store,
+                                                      const float2* wl, const float2* wh, const LaneAngles<P>& ang,
+                                                      float inv_dim, float eps) {
+  float2 lo[P], hi[P];
+  Elem<T>::unpack2(xs[where], lo);
+  Elem<T>::unpack2(xs[where + hv], hi);
+  if (kNorm) {
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int e = 0; e < P; ++e) acc = __ffma2_rn(lo[e], lo[e], acc);
+#pragma unroll
+    for (int e = 0; e < P; ++e) acc = __ffma2_rn(hi[e], hi[e], acc);
+    const float ss = group_sum(acc.x + acc.y, hv);
+    const float inv = rsqrtf(fmaf(ss, inv_dim, eps));
+    const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+    for (int e = 0; e < P; ++e) {
+      lo[e] = __fmul2_rn(__fmul2_rn(lo[e], inv2), wl[e]);
+      hi[e] = __fmul2_rn(__fmul2_rn(hi[e], inv2), wh[e]);
+    }
+  }
+  float2 out_lo[P], out_hi[P];
+#pragma unroll
+  for (int e = 0; e < P; ++e) {
+    out_lo[e] = __ffma2_rn(hi[e], ang.neg_s[e], __fmul2_rn(lo[e], ang.c[e]));   // a*c - b*s
+    out_hi[e] = __ffma2_rn(lo[e], ang.s[e], __fmul2_rn(hi[e], ang.c[e]));       // a*s + b*c
+  }
+  if (store) {
+    st_stream(out + where, Elem<T>::pack2(out_lo));
+    st_stream(out + where + hv, Elem<T>::pack2(out_hi));
+  }
+}
+
+// All heads of one tensor for one token, from the staged row.  kHv > 0 fixes hv (vectors per half head)
+// at compile time.  The 32 lanes cover 32/hv heads per step, i.e. always 64 vectors: the lane's vector
+// index simply advances by 64 per step, so full steps carry no index arithmetic and no predicates.
+template <typename T, bool kNorm, int kHv>
+__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int heads, int hv_rt,
+                                                       int hv_shift_rt, int lane,
                                                        const LaneAngles<Elem<T>::kPerVec / 2>& ang, float inv_dim,
                                                        float eps) {
   constexpr int P = Elem<T>::kPerVec / 2;
+  const int hv = kHv > 0 ? kHv : hv_rt;
+  const int shift = kHv > 0 ? (kHv == 1 ? 0 : kHv == 2 ? 1 : kHv == 4 ? 2 : kHv == 8 ? 3 : kHv == 16 ? 4 : 5) : hv_shift_rt;
   const int v = lane & (hv - 1);
   float2 wl[P], wh[P];
   if (kNorm) {
     Elem<T>::unpack2(ld_reuse(w + v), wl);
     Elem<T>::unpack2(ld_reuse(w + hv + v), wh);
   }
-  const int last = items - 1;
-  for (int base = 0; base < items; base += kWarpSize) {     // uniform trip count: shuffles stay converged
-    const int item = base + lane;
-    const bool ok = item < items;
-    const int where = (((ok ? item : last) >> hv_shift) << (hv_shift + 1)) + v;
-    float2 lo[P], hi[P];
-    Elem<T>::unpack2(xs[where], lo);
-    Elem<T>::unpack2(xs[where + hv], hi);
-    if (kNorm) {
-      float2 acc = make_float2(0.0f, 0.0f);
-#pragma unroll
-      for (int e = 0; e < P; ++e) acc = __ffma2_rn(lo[e], lo[e], acc);
-#pragma unroll
-      for (int e = 0; e < P; ++e) acc = __ffma2_rn(hi[e], hi[e], acc);
-      const float ss = group_sum(acc.x + acc.y, hv);
-      const float inv = rsqrtf(fmaf(ss, inv_dim, eps));
-      const float2 inv2 = make_float2(inv, inv);
-#pragma unroll
-      for (int e = 0; e < P; ++e) {
-        lo[e] = __fmul2_rn(__fmul2_rn(lo[e], inv2), wl[e]);
-        hi[e] = __fmul2_rn(__fmul2_rn(hi[e], inv2), wh[e]);
-      }
-    }
-    float2 out_lo[P], out_hi[P];
-#pragma unroll
-    for (int e = 0; e < P; ++e) {
-      out_lo[e] = __ffma2_rn(hi[e], ang.neg_s[e], __fmul2_rn(lo[e], ang.c[e]));   // a*c - b*s
-      out_hi[e] = __ffma2_rn(lo[e], ang.s[e], __fmul2_rn(hi[e], ang.c[e]));       // a*s + b*c
-    }
-    if (ok) {
-      st_stream(out + where, Elem<T>::pack2(out_lo));
-      st_stream(out + where + hv, Elem<T>::pack2(out_hi));
-    }
+  const int items = heads << shift;
+  int where = ((lane >> shift) << (shift + 1)) + v;
+  const int full = items >> 5;
+  for (int i = 0; i < full; ++i, where += 2 * kWarpSize)
+    rope_item_from_shared<T, kNorm, P>(xs, out, where, hv, true, wl, wh, ang, inv_dim, eps);
+  if (items & 31) {
+    // ragged last step: lanes past the end redo the last head (valid memory, converged shuffles) and store nothing
+    const bool ok = (full << 5) + lane < items;
+    const int last_where = (((items - 1) >> shift) << (shift + 1)) + v;
+    rope_item_from_shared<T, kNorm, P>(xs, out, ok ? where : last_where, hv, ok, wl, wh, ang, inv_dim, eps);
   }
 }
 
-template <typename T, bool kNorm>
+template <typename T, bool kNorm, int kHv>
 __global__ void __launch_bounds__(kThreads, 2)
 rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
                         int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
@@ -278,6 +295,12 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
   float* sin_row = cos_row + half;
   uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem + size_t(warps) * per_warp) + 2 * warp;
   const float inv_dim = 1.0f / float(head_dim);
+  // kernel parameters used inside the token loop, as plain locals
+  const int q_heads = q.heads, k_heads = k.heads, q_vecs = q.heads * vecs_per_head, k_vecs = k.heads * vecs_per_head;
+  const uint4* q_w = reinterpret_cast<const uint4*>(q.w);
+  const uint4* k_w = reinterpret_cast<const uint4*>(k.w);
+  uint4* q_out = reinterpret_cast<uint4*>(q.out);
+  uint4* k_out = reinterpret_cast<uint4*>(k.out);
 
   if (lane == 0) { mbarrier_init(&bars[0], 1); mbarrier_init(&bars[1], 1); }
   __syncwarp();
@@ -329,13 +352,10 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
       break;
     }
     const uint4* xs = reinterpret_cast<const uint4*>(mine + uint32_t(stage) * stage_bytes);
-    rope_heads_from_shared<T, kNorm>(xs, reinterpret_cast<const uint4*>(q.w),
-                                     reinterpret_cast<uint4*>(q.out) + size_t(t) * q.heads * vecs_per_head, q.heads * hv, hv,
-                                     hv_shift, lane, ang, inv_dim, eps);
-    if (k.heads > 0)
-      rope_heads_from_shared<T, kNorm>(xs + q.heads * vecs_per_head, reinterpret_cast<const uint4*>(k.w),
-                                       reinterpret_cast<uint4*>(k.out) + size_t(t) * k.heads * vecs_per_head, k.heads * hv,
-                                       hv, hv_shift, lane, ang, inv_dim, eps);
+    rope_heads_from_shared<T, kNorm, kHv>(xs, q_w, q_out + size_t(t) * q_vecs, q_heads, hv, hv_shift, lane, ang, inv_dim, eps);
+    if (k_heads > 0)
+      rope_heads_from_shared<T, kNorm, kHv>(xs + q_vecs, k_w, k_out + size_t(t) * k_vecs, k_heads, hv, hv_shift, lane, ang,
+                                            inv_dim, eps);
     __syncwarp();   // stage and table are free again
     p = p_next;
   }
@@ -418,13 +438,15 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
   static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
   if (!enabled) return false;
   const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = 2 * stage + size_t(head_dim) * 4;
-  const size_t budget = 100 * 1024;                       // two CTAs per SM
+  const size_t budget = 110 * 1024;                       // two CTAs per SM (227 KB)
   int warps = int(budget / (per_warp + 16));
   if (warps < 1) return false;                            // rows too long for two stages: the register kernel takes over
   if (warps > kWarpsPerCta) warps = kWarpsPerCta;
   if (int64_t(warps) > tokens) warps = int(tokens);
   const size_t smem = size_t(warps) * per_warp + size_t(warps) * 16;
-  auto kernel = rope_tokens_bulk_kernel<T, kNorm>;
+  // the two head sizes of the model family get hv fixed at compile time (head_dim 128: 8 vectors of fp16, 16 of fp32)
+  auto kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16>
+                                                                         : rope_tokens_bulk_kernel<T, kNorm, 0>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
     cudaGetLastError();
     return false;
