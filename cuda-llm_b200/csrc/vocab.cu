@@ -295,95 +295,6 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice, int* st
   if (kBulk && !load_ok) mbarrier_wait_bounded(&load_barrier, 0);
 }
 
-// ---- fast mode, persistent form (fp32 rows): few clusters, each walking rows
-// cluster_id, cluster_id + clusters, ...; one CTA per SM with TWO shared-memory stages.
-// Thread 0 asks the copy engine (bulk copies) for the NEXT row's slice before the CTA starts the
-// passes over the current one, so HBM reads run continuously underneath the arithmetic, the
-// cluster barriers and the stores, instead of alternating with them.
-constexpr int kPersistThreads = 1024;
-
-__global__ void __launch_bounds__(kPersistThreads, 1)
-softmax_persistent_kernel(const float* x, float* out, int64_t rows, int64_t width, int64_t slice, int* status) {
-  extern __shared__ __align__(128) float stage_mem[];      // [2][slice]
-  __shared__ float scratch[32];
-  __shared__ float peer_max[kMaxClusterRanks], peer_sum[kMaxClusterRanks];   // written by the other CTAs
-  __shared__ __align__(8) uint64_t bars[2];
-
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
-  const int64_t cluster_id = blockIdx.x / ranks, clusters = gridDim.x / ranks;
-  const int64_t lo = int64_t(rank) * slice;
-  const int n = int(lo >= width ? 0 : (width - lo < slice ? width - lo : slice));   // a multiple of 4 (host-checked)
-  const int n4 = n >> 2, tid = threadIdx.x;
-  const uint32_t bytes = uint32_t(n4) * 16u;
-
-  auto request = [&](int64_t row, int stage) {               // thread 0 only
-    const char* src = reinterpret_cast<const char*>(x + row * width + lo);
-    char* dst = reinterpret_cast<char*>(stage_mem + size_t(stage) * size_t(slice));
-    mbarrier_expect_bytes(&bars[stage], bytes);
-    for (uint32_t off = 0; off < bytes; off += kBulkChunk)
-      bulk_load(dst + off, src + off, bytes - off < kBulkChunk ? bytes - off : kBulkChunk, &bars[stage]);
-  };
-  if (tid == 0) {
-    mbarrier_init(&bars[0], 1);
-    mbarrier_init(&bars[1], 1);
-    if (cluster_id < rows) request(cluster_id, 0);
-  }
-  cluster.sync();   // barriers initialised; every CTA of the cluster runs before anyone writes into a neighbour
-
-  bool all_ok = true;
-  int it = 0;
-  for (int64_t row = cluster_id; row < rows; row += clusters, ++it) {
-    const int stage = it & 1;
-    float4* vals4 = reinterpret_cast<float4*>(stage_mem + size_t(stage) * size_t(slice));
-    // the other stage was last read in pass C of the previous row; the __syncthreads() that ends that row is behind us
-    if (tid == 0 && row + clusters < rows) { fence_before_bulk_copy(); request(row + clusters, stage ^ 1); }
-    if (!mbarrier_wait_bounded(&bars[stage], uint32_t(it >> 1) & 1u)) {
-      all_ok = false;
-      if (tid == 0 && status != nullptr) atomicOr(status, 1);
-    }
-
-    float m0 = -INFINITY, m1 = -INFINITY;
-    for (int g = tid; g < n4; g += kPersistThreads) {
-      const float4 t = vals4[g];
-      m0 = fmaxf(m0, fmaxf(t.x, t.y));
-      m1 = fmaxf(m1, fmaxf(t.z, t.w));
-    }
-    const float slice_max = block_max(fmaxf(m0, m1), scratch);
-    if (tid < int(ranks)) *cluster.map_shared_rank(&peer_max[rank], tid) = slice_max;
-    cluster.sync();
-    float row_max = -INFINITY;
-    for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, peer_max[r]);
-    const float neg_m2 = -row_max * kLog2e;
-
-    float s0 = 0.0f, s1 = 0.0f;
-    for (int g = tid; g < n4; g += kPersistThreads) {
-      float4 t = vals4[g];
-      t.x = fast_exp2(fmaf(t.x, kLog2e, neg_m2)); t.y = fast_exp2(fmaf(t.y, kLog2e, neg_m2));
-      t.z = fast_exp2(fmaf(t.z, kLog2e, neg_m2)); t.w = fast_exp2(fmaf(t.w, kLog2e, neg_m2));
-      vals4[g] = t;
-      s0 += t.x + t.y;
-      s1 += t.z + t.w;
-    }
-    const float slice_sum = block_sum(s0 + s1, scratch);
-    if (tid < int(ranks)) *cluster.map_shared_rank(&peer_sum[rank], tid) = slice_sum;
-    cluster.sync();
-    float row_sum = 0.0f;
-    for (unsigned r = 0; r < ranks; ++r) row_sum += peer_sum[r];   // rank order: the same sum on every CTA of the row
-    const float inv_sum = 1.0f / row_sum;
-
-    float4* dst4 = reinterpret_cast<float4*>(out + row * width + lo);
-    for (int g = tid; g < n4; g += kPersistThreads) {
-      float4 t = vals4[g];
-      t.x *= inv_sum; t.y *= inv_sum; t.z *= inv_sum; t.w *= inv_sum;
-      __stcs(dst4 + g, t);
-    }
-    __syncthreads();   // this stage may be refilled two rows from now; peer arrays are reused by the next row
-  }
-  // a copy that had not landed when a wait gave up must not outlive this CTA's shared memory
-  if (!all_ok) { mbarrier_wait_bounded(&bars[0], 0); mbarrier_wait_bounded(&bars[1], 0); }
-}
-
 // ---- fast mode, register-resident form: the same three steps, but every thread keeps its K
 // 16-byte vectors of the row in registers from the load to the store.  All loads of the slice
 // are in flight at once (K per thread), nothing passes through shared memory, and the loops are
@@ -691,36 +602,6 @@ int launch_softmax_reg_any(const T* x, T* out, int64_t rows, int64_t width, int 
   return B2_ERR_UNSUPPORTED;
 }
 
-// Returns B2_OK when the persistent kernel was launched.
-int launch_softmax_persistent(const float* x, float* out, int64_t rows, int64_t width, int ranks, int64_t slice, int* status,
-                              cudaStream_t s) {
-  const size_t smem = 2 * size_t(slice) * sizeof(float);
-  const int64_t clusters_max = sm_count() / ranks;
-  if (smem > 220 * 1024 || clusters_max < 1 || rows < 2 * clusters_max) return B2_ERR_UNSUPPORTED;
-  auto kernel = softmax_persistent_kernel;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-    cudaGetLastError();
-    return B2_ERR_UNSUPPORTED;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(unsigned(clusters_max * ranks));
-  cfg.blockDim = dim3(kPersistThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = unsigned(ranks);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, x, out, rows, width, slice, status) != cudaSuccess) {
-    cudaGetLastError();
-    return B2_ERR_UNSUPPORTED;
-  }
-  return B2_OK;
-}
-
 template <typename T>
 int launch_stats_typed(const void* x, int64_t rows, int64_t width, float* row_max, float* row_sum, cudaStream_t s) {
   if (rows == 0) return B2_OK;
@@ -776,13 +657,6 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
     // status word: the last 16 bytes of the workspace (after the 2*rows floats of the two-pass path)
     int* status = reinterpret_cast<int*>(static_cast<char*>(workspace) + softmax_workspace_bytes(rows) - 16);
     int rc;
-    static const bool persistent_path = [] { const char* v = std::getenv("B2_SOFTMAX_PERSISTENT"); return v && std::atoi(v) != 0; }();
-    if constexpr (sizeof(T) == 4) {
-      if (vec && persistent_path && ranks <= 8 && slice % 4 == 0 && width % 4 == 0 &&
-          launch_softmax_persistent(reinterpret_cast<const float*>(x), reinterpret_cast<float*>(out), rows, width, ranks, slice,
-                                    status, s) == B2_OK)
-        return B2_OK;
-    }
     static const bool reg_path = [] { const char* v = std::getenv("B2_SOFTMAX_REG"); return !v || std::atoi(v) != 0; }();
     if (vec && reg_path && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, s) == B2_OK) return B2_OK;
     if (vec && sizeof(T) == 4 && slice % 4 == 0)   // fp32 rows: shared memory holds the input's own bytes -> bulk copy
