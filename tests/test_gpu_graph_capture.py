@@ -1,0 +1,69 @@
+"""The `*_out` operators allocate nothing, never synchronise and copy nothing to the host, so a
+decoder layer's operator sequence can be recorded into a CUDA graph and replayed, as the reference
+does for its decode step (src/qwen3_cuda_model.cpp:797-816).  The GEMMs and attention between the
+operators are outside this library; their outputs are stand-in tensors here."""
+import numpy as np
+import pytest
+import torch
+
+from cuda_llm_b200 import ops, workloads as wl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _layer_ops(t, bufs):
+    """The in-scope operators of one Qwen3 decoder layer step, in the reference's order
+    (src/qwen3_layer_cuda.cu:285-325), followed by the final norm and a row argmax."""
+    ops.cuda_rms_norm_out(t["hidden"], t["w_in"], wl.EPS, bufs["normed"])
+    ops.qk_norm_rope_out(t["q"], t["k"], t["w_q"], t["w_k"], t["pos"], wl.EPS, wl.THETA, bufs["q"], bufs["k"])
+    ops.cuda_add_rms_norm_out(t["hidden"], t["o_proj"], t["w_post"], wl.EPS, bufs["residual"], bufs["post"])
+    ops.cuda_swiglu_out(t["gate"], t["up"], bufs["act"])
+    ops.cuda_add_out(bufs["residual"], t["down"], bufs["out"])
+    ops.cuda_rms_norm_out(bufs["out"], t["w_in"], wl.EPS, bufs["final"])
+    ops.argmax_rows_out(t["logits"], bufs["ids"])
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_layer_operator_sequence_replays_from_a_cuda_graph(b2, batch):
+    rng = np.random.default_rng(batch)
+    h = lambda *s: torch.from_numpy(wl.normal(rng, s, dtype=np.float16)).to(DEV)
+    g = lambda n: torch.from_numpy(wl.gamma(rng, n, dtype=np.float16)).to(DEV)
+    t = {"hidden": h(batch, 1024), "o_proj": h(batch, 1024), "down": h(batch, 1024), "q": h(batch, 16, 128),
+         "k": h(batch, 8, 128), "gate": h(batch, 3072), "up": h(batch, 3072), "w_in": g(1024), "w_post": g(1024),
+         "w_q": g(128), "w_k": g(128), "pos": torch.arange(7, 7 + batch, dtype=torch.int32, device=DEV),
+         "logits": torch.from_numpy(wl.normal(rng, (batch, wl.VOCAB), 4.0)).to(DEV)}
+
+    def fresh():
+        e = lambda *s: torch.zeros(*s, dtype=torch.float16, device=DEV)
+        return {"normed": e(batch, 1024), "q": e(batch, 16, 128), "k": e(batch, 8, 128), "residual": e(batch, 1024),
+                "post": e(batch, 1024), "act": e(batch, 3072), "out": e(batch, 1024), "final": e(batch, 1024),
+                "ids": torch.zeros(batch, dtype=torch.int32, device=DEV)}
+
+    eager = fresh()
+    _layer_ops(t, eager)                       # also warms the library's per-device state before capture
+    torch.cuda.synchronize()
+
+    captured = fresh()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            _layer_ops(t, captured)
+    for name, buf in captured.items():         # nothing ran during capture
+        assert int(buf.abs().sum().item()) == 0 or name == "ids"
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for name in eager:
+        assert torch.equal(eager[name], captured[name]), name
+    # new inputs, same graph: the replay reads the tensors in place
+    t["hidden"].copy_(h(batch, 1024))
+    t["logits"][:, 5] = 1e4
+    graph.replay()
+    again = fresh()
+    _layer_ops(t, again)
+    torch.cuda.synchronize()
+    for name in again:
+        assert torch.equal(again[name], captured[name]), name
+    assert captured["ids"].tolist() == [5] * batch
