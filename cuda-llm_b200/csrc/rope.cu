@@ -281,7 +281,7 @@ __device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const ui
 }
 
 template <typename T, bool kNorm, int kHv>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
                         int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
   constexpr int N = Elem<T>::kPerVec;
@@ -316,7 +316,8 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
       bulk_load(dst + q_bytes, static_cast<const unsigned char*>(k.x) + size_t(token) * k_bytes, k_bytes, &bars[stage]);
   };
   if (t < tokens && lane == 0) request(t, 0);
-  int32_t p = t < tokens ? positions[pos_period ? t % pos_period : t] : 0;
+  auto position_of = [&](int64_t token) { return positions[pos_period ? token % pos_period : token]; };
+  int32_t p = t < tokens ? position_of(t) : 0;
 
   for (int it = 0; t < tokens; ++it, t += stride) {
     const int stage = it & 1;
@@ -326,7 +327,7 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
       // the other stage was last read during the previous step; every lane passed the __syncwarp
       // that ends that step after consuming what it read
       if (lane == 0) { fence_before_bulk_copy(); request(t_next, stage ^ 1); }
-      p_next = positions[pos_period ? t_next % pos_period : t_next];
+      p_next = position_of(t_next);
     }
     for (int j = lane; j < half; j += kWarpSize) {
       const float2 cs = rope_cos_sin<false>(p, j, head_dim, theta, freq, half);
@@ -438,7 +439,7 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
   static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
   if (!enabled) return false;
   const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = 2 * stage + size_t(head_dim) * 4;
-  const size_t budget = 110 * 1024;                       // two CTAs per SM (227 KB)
+  const size_t budget = 72 * 1024;                        // three CTAs per SM (227 KB)
   int warps = int(budget / (per_warp + 16));
   if (warps < 1) return false;                            // rows too long for two stages: the register kernel takes over
   if (warps > kWarpsPerCta) warps = kWarpsPerCta;
@@ -451,7 +452,7 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
     cudaGetLastError();
     return false;
   }
-  const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * 2;
+  const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * 3;
   kernel<<<unsigned(ctas < cap ? ctas : cap), warps * kWarpSize, smem, s>>>(q, k, positions, tokens, int(head_dim), hv,
                                                                           hv_shift, pos_period, eps, theta,
                                                                           make_table(head_dim, theta));
