@@ -151,6 +151,85 @@ def cpu_baseline(target_seconds: float, steps: int = 1, warmup: int = 0):
                                      f"CPU operators take; GB/s counts the fp16 workload's algorithmic bytes per row"}
 
 
+def reference_gpu_kernels(L, lib, dev, stream):
+    """The reference's own CUDA operators (src/ops_cuda.cu recompiled for sm_100a, oracle/_ref/libref_cuda.so)
+    timed on this GPU beside ours, same shapes, device-resident tensors, CUDA events.  A reported baseline."""
+    import torch
+    import oracle
+    from cuda_llm_b200 import ops
+    ref = oracle.ref_cuda()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/libref_cuda.so was not built (reference tree absent at build time)"}
+    s = stream.cuda_stream
+    half = torch.float16
+
+    def ours(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    out = {}
+
+    def row(name, ref_ms, our_ms, note=None):
+        out[name] = {"reference_ms": round(ref_ms, 4), "ours_ms": round(our_ms, 4), "speedup": round(ref_ms / our_ms, 1)}
+        if note:
+            out[name]["note"] = note
+
+    rows, hidden = ROWS, HIDDEN
+    x, y = torch.randn(rows, hidden, device=dev).to(half), torch.randn(rows, hidden, device=dev).to(half)
+    g = (torch.rand(hidden, device=dev) + 0.5).to(half)
+    o1, o2 = torch.empty_like(x), torch.empty_like(x)
+    row(f"add_rms_norm {rows}x{hidden} f16", ref.time_add_rms_norm(x, y, g, rows, hidden, 1e-6, 1, 2),
+        ours(lambda: lib.check(L.b2_add_rms_norm(x.data_ptr(), y.data_ptr(), g.data_ptr(), o1.data_ptr(), o2.data_ptr(), rows,
+                                                 hidden, 1e-6, lib.F16, lib.FAST, s))))
+    row(f"rms_norm {rows}x{hidden} f16", ref.time_rms_norm(x, g, rows, hidden, 1e-6, 1, 2),
+        ours(lambda: lib.check(L.b2_rms_norm(x.data_ptr(), g.data_ptr(), o1.data_ptr(), rows, hidden, 1e-6, lib.F16, lib.FAST, s))))
+    n = rows * hidden
+    row(f"add {rows}x{hidden} f16", ref.time_binary(x, y, n, 1, False, 3),
+        ours(lambda: lib.check(L.b2_add(x.data_ptr(), y.data_ptr(), o1.data_ptr(), n, lib.F16, s))))
+    row(f"swiglu {rows}x{hidden} f16", ref.time_binary(x, y, n, 1, True, 3),
+        ours(lambda: lib.check(L.b2_swiglu(x.data_ptr(), y.data_ptr(), o1.data_ptr(), n, lib.F16, lib.FAST, s))))
+    del x, y, o1, o2
+    T = 16384
+    q, k = torch.randn(T, 16, 128, device=dev).to(half), torch.randn(T, 8, 128, device=dev).to(half)
+    g128 = (torch.rand(128, device=dev) + 0.5).to(half)
+    pos = torch.randint(0, 512, (T,), device=dev, dtype=torch.int32)
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    ref_ms = (ref.time_rms_norm(q, g128, T * 16, 128, 1e-6, 1, 3) + ref.time_rms_norm(k, g128, T * 8, 128, 1e-6, 1, 3) +
+              ref.time_rope_token_positions(q, pos, T, 16, 1e6, 3) + ref.time_rope_token_positions(k, pos, T, 8, 1e6, 3))
+    row("qk_norm + rope, T=16384, 16+8 heads x 128 f16", ref_ms,
+        ours(lambda: lib.check(L.b2_qk_norm_rope(q.data_ptr(), k.data_ptr(), g128.data_ptr(), g128.data_ptr(), pos.data_ptr(),
+                                                 qo.data_ptr(), ko.data_ptr(), T, 16, 8, 128, 1e-6, 1e6, lib.F16, s))),
+        note="reference: its four launches (rms_norm x2, rope_token_positions x2); ours: one fused launch")
+    del q, k, qo, ko
+    vocab, tokens = 151936, 262144
+    table = (torch.randn(vocab, 4096, device=dev) * 0.02).to(half)
+    ids = torch.randint(0, vocab, (tokens,), device=dev, dtype=torch.int32)
+    gout = torch.empty(tokens, 4096, device=dev, dtype=half)
+    row(f"embedding gather {tokens} rows x 4096 f16", ref.time_embedding(table, ids, tokens, 4096, vocab, 1, 3),
+        ours(lambda: lib.check(L.b2_embedding_gather(table.data_ptr(), ids.data_ptr(), gout.data_ptr(), tokens, 4096, vocab,
+                                                     lib.F16, None, s))))
+    del table, gout
+    R = 256
+    logits = torch.randn(R, vocab, device=dev) * 4
+    ids_out = torch.empty(R, dtype=torch.int32, device=dev)
+    ws = ops.argmax_workspace(dev, R)
+    row(f"argmax of {R} rows x {vocab} f32", R * ref.time_argmax_last_row(logits, R, vocab, 0, 5),
+        ours(lambda: lib.check(L.b2_argmax_rows(logits.data_ptr(), R, vocab, vocab, lib.F32, ids_out.data_ptr(), ws.data_ptr(), s))),
+        note="reference: one blocking call per row (2 cudaMalloc + 2 cudaFree + a D2H copy each), timed on one row x 256")
+    sws, sout = ops.softmax_workspace(dev, R), torch.empty_like(logits)
+    row(f"softmax {R}x{vocab} f32", ref.time_softmax(logits, R, vocab, 0, 1),
+        ours(lambda: lib.check(L.b2_softmax_rows(logits.data_ptr(), sout.data_ptr(), R, vocab, lib.F32, lib.FAST, sws.data_ptr(), s))))
+    return out
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -282,6 +361,13 @@ def main():
             from cuda_llm_b200 import opbench
             torch.cuda.empty_cache()
             op_table = opbench.run(L, lib, dev, stream, world, rank, barrier, max_over_ranks)
+        ref_gpu = None
+        if world == 1 and not args.no_ops and not args.no_cpu:
+            torch.cuda.empty_cache()
+            try:
+                ref_gpu = reference_gpu_kernels(L, lib, dev, stream)
+            except Exception as exc:      # a reported baseline, never required for our numbers
+                ref_gpu = {"error": str(exc)}
 
     if rank != 0:
         if world > 1:
@@ -309,6 +395,8 @@ def main():
             line["cpu_baseline"] = {"error": str(exc)}
     if op_table is not None:
         line["ops"] = op_table
+    if ref_gpu is not None:
+        line["reference_cuda_kernels_on_this_gpu"] = ref_gpu
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

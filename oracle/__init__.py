@@ -8,6 +8,9 @@ package; the product (the CUDA library and its host side) never does.
              operators (present when oracle/Makefile's ``ref`` target was built
              where the reference tree exists; the binary then travels with the
              snapshot).  ``ref`` is None when that binary is absent.
+``ref_cuda`` -> oracle/_ref/libref_cuda.so, the reference's own CUDA operators
+             recompiled for sm_100a (``refcuda`` target): a second oracle for the
+             deterministic mode and the "reference kernels on the same GPU" timings.
 """
 from __future__ import annotations
 
@@ -23,7 +26,7 @@ F32, F16 = 0, 1  # dtype codes, the same as the product's C ABI
 
 def build(ref: bool = True) -> None:
     """Compile oracle.c (and the reference-backed library when its sources exist)."""
-    subprocess.run(["make", "-C", _HERE, "all"] + (["ref"] if ref else []), check=True,
+    subprocess.run(["make", "-C", _HERE, "all"] + (["ref", "refcuda"] if ref else []), check=True,
                    stdout=subprocess.DEVNULL)
 
 
@@ -293,3 +296,104 @@ def ref():
         path = os.path.join(_HERE, "_ref", "liboracle_ref.so")
         _ref = Ref(path) if os.path.exists(path) else None
     return _ref
+
+
+class RefCuda:
+    """The reference's own CUDA operators (oracle/_ref/libref_cuda.so).  Arguments are device pointers
+    (ints) or anything with ``data_ptr()``; dtype codes as elsewhere (F32 = 0, F16 = 1)."""
+
+    def __init__(self, path: str):
+        self.lib = L = C.CDLL(path)
+        for name in ("refcu_time_add_rms_norm", "refcu_time_rms_norm", "refcu_time_binary", "refcu_time_rope_token_positions",
+                     "refcu_time_embedding", "refcu_time_softmax", "refcu_time_argmax_last_row"):
+            getattr(L, name).restype = C.c_float
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t if isinstance(t, int) else t.data_ptr())
+
+    @staticmethod
+    def _ok(rc, what):
+        if rc:
+            raise RuntimeError(f"reference CUDA operator {what} failed with {rc}")
+
+    def rms_norm(self, x, w, out, rows, hidden, eps, dtype):
+        self._ok(self.lib.refcu_rms_norm(self._p(x), self._p(w), self._p(out), C.c_int64(rows), C.c_int64(hidden),
+                                         C.c_float(eps), C.c_int(dtype)), "rms_norm")
+
+    def add_rms_norm(self, lhs, rhs, w, residual, normalized, rows, hidden, eps, dtype):
+        self._ok(self.lib.refcu_add_rms_norm(self._p(lhs), self._p(rhs), self._p(w), self._p(residual), self._p(normalized),
+                                             C.c_int64(rows), C.c_int64(hidden), C.c_float(eps), C.c_int(dtype)), "add_rms_norm")
+
+    def add(self, a, b, out, n, dtype):
+        self._ok(self.lib.refcu_add(self._p(a), self._p(b), self._p(out), C.c_int64(n), C.c_int(dtype)), "add")
+
+    def swiglu(self, g, u, out, n, dtype):
+        self._ok(self.lib.refcu_swiglu(self._p(g), self._p(u), self._p(out), C.c_int64(n), C.c_int(dtype)), "swiglu")
+
+    def rope(self, x, positions_host, out, tokens, heads, head_dim, theta, dtype):
+        pos = _i32(positions_host)
+        self._ok(self.lib.refcu_rope(self._p(x), _ptr(pos), self._p(out), C.c_int64(tokens), C.c_int64(heads),
+                                     C.c_int64(head_dim), C.c_float(theta), C.c_int(dtype)), "rope")
+
+    def rope_token_positions(self, x, positions_device, out, tokens, heads, theta):
+        self._ok(self.lib.refcu_rope_token_positions(self._p(x), self._p(positions_device), self._p(out), C.c_int64(tokens),
+                                                     C.c_int64(heads), C.c_float(theta)), "rope_token_positions")
+
+    def softmax(self, x, out, rows, width, dtype):
+        self._ok(self.lib.refcu_softmax(self._p(x), self._p(out), C.c_int64(rows), C.c_int64(width), C.c_int(dtype)), "softmax")
+
+    def embedding_lookup(self, table, ids_host, out, hidden, vocab, dtype):
+        ids = _i32(ids_host)
+        self._ok(self.lib.refcu_embedding_lookup(self._p(table), _ptr(ids), self._p(out), C.c_int64(ids.size), C.c_int64(hidden),
+                                                 C.c_int64(vocab), C.c_int(dtype)), "embedding_lookup")
+
+    def argmax_last_row(self, logits, rows, width, dtype) -> int:
+        r = C.c_int32(-1)
+        self._ok(self.lib.refcu_argmax_last_row(self._p(logits), C.c_int64(rows), C.c_int64(width), C.c_int(dtype), C.byref(r)),
+                 "argmax_last_row")
+        return int(r.value)
+
+    # timings: milliseconds per call of the reference operator on device-resident tensors
+    def time_add_rms_norm(self, lhs, rhs, w, rows, hidden, eps, dtype, reps):
+        return float(self.lib.refcu_time_add_rms_norm(self._p(lhs), self._p(rhs), self._p(w), C.c_int64(rows), C.c_int64(hidden),
+                                                      C.c_float(eps), C.c_int(dtype), C.c_int(reps)))
+
+    def time_rms_norm(self, x, w, rows, hidden, eps, dtype, reps):
+        return float(self.lib.refcu_time_rms_norm(self._p(x), self._p(w), C.c_int64(rows), C.c_int64(hidden), C.c_float(eps),
+                                                  C.c_int(dtype), C.c_int(reps)))
+
+    def time_binary(self, a, b, n, dtype, swiglu, reps):
+        return float(self.lib.refcu_time_binary(self._p(a), self._p(b), C.c_int64(n), C.c_int(dtype), C.c_int(int(swiglu)),
+                                                C.c_int(reps)))
+
+    def time_rope_token_positions(self, x, positions_device, tokens, heads, theta, reps):
+        return float(self.lib.refcu_time_rope_token_positions(self._p(x), self._p(positions_device), C.c_int64(tokens),
+                                                              C.c_int64(heads), C.c_float(theta), C.c_int(reps)))
+
+    def time_embedding(self, table, ids_device, count, hidden, vocab, dtype, reps):
+        return float(self.lib.refcu_time_embedding(self._p(table), self._p(ids_device), C.c_int64(count), C.c_int64(hidden),
+                                                   C.c_int64(vocab), C.c_int(dtype), C.c_int(reps)))
+
+    def time_softmax(self, x, rows, width, dtype, reps):
+        return float(self.lib.refcu_time_softmax(self._p(x), C.c_int64(rows), C.c_int64(width), C.c_int(dtype), C.c_int(reps)))
+
+    def time_argmax_last_row(self, logits, rows, width, dtype, reps):
+        return float(self.lib.refcu_time_argmax_last_row(self._p(logits), C.c_int64(rows), C.c_int64(width), C.c_int(dtype),
+                                                         C.c_int(reps)))
+
+
+_ref_cuda = False
+
+
+def ref_cuda():
+    """The reference's CUDA operators recompiled for sm_100a, or None when oracle/_ref/libref_cuda.so is absent."""
+    global _ref_cuda
+    if _ref_cuda is False:
+        path = os.path.join(_HERE, "_ref", "libref_cuda.so")
+        try:
+            _ref_cuda = RefCuda(path) if os.path.exists(path) else None
+        except OSError:
+            _ref_cuda = None
+    return _ref_cuda
+

@@ -1,0 +1,113 @@
+"""Second oracle: the reference's OWN CUDA operators (src/ops_cuda.cu), recompiled for sm_100a into
+oracle/_ref/libref_cuda.so, run on the same GPU and the same device buffers.
+
+Deterministic mode exists so that the reference's bit-level regressions can still be run: where the
+arithmetic is IEEE-exact (RMSNorm family, add, gather, argmax) it must reproduce the reference kernels
+bit for bit.  SwiGLU, RoPE and softmax go through device libm functions compiled from different source
+text, so they are held to an fp32 ulp-level bound instead.  Fast mode is compared at the tolerances the
+reference's own GPU tests use (1e-4 for F32, 5e-3 for F16: tests/test_ops_cuda.cpp:121-151)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from cuda_llm_b200 import lib, ops, workloads as wl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def refcu(b2):
+    r = oracle.ref_cuda()
+    if r is None:
+        pytest.skip("oracle/_ref/libref_cuda.so not built (reference tree absent at build time)")
+    return r
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def code(t):
+    return lib.F32 if t.dtype == torch.float32 else lib.F16
+
+
+def bits(t):
+    return t.view(torch.int32 if t.dtype == torch.float32 else torch.int16)
+
+
+@pytest.mark.parametrize("rows,hidden", [(4, 1024), (65, 2048), (3, 4096), (96, 128), (5, 1000), (512, 4096)])
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_deterministic_norms_equal_reference_kernels_bitwise(refcu, rows, hidden, dtype):
+    rng = np.random.default_rng(rows + hidden)
+    x, r = dev(wl.normal(rng, (rows, hidden), dtype=dtype)), dev(wl.normal(rng, (rows, hidden), dtype=dtype))
+    w = dev(wl.gamma(rng, hidden, dtype=dtype))
+    want = torch.empty_like(x)
+    refcu.rms_norm(x, w, want, rows, hidden, wl.EPS, code(x))
+    got = ops.cuda_rms_norm(x, w, wl.EPS, "deterministic")
+    assert torch.equal(bits(got), bits(want))
+    want_res, want_nrm = torch.empty_like(x), torch.empty_like(x)
+    refcu.add_rms_norm(x, r, w, want_res, want_nrm, rows, hidden, wl.EPS, code(x))
+    res, nrm = torch.empty_like(x), torch.empty_like(x)
+    ops.cuda_add_rms_norm_out(x, r, w, wl.EPS, res, nrm, "deterministic")
+    assert torch.equal(bits(res), bits(want_res)) and torch.equal(bits(nrm), bits(want_nrm))
+    # fast mode: the reference's own GPU-test tolerances
+    tol = 1e-4 if dtype == np.float32 else 5e-3
+    fast_res, fast_nrm = torch.empty_like(x), torch.empty_like(x)
+    ops.cuda_add_rms_norm_out(x, r, w, wl.EPS, fast_res, fast_nrm, "fast")
+    assert torch.equal(bits(fast_res), bits(want_res))
+    scale = max(1.0, float(want_nrm.float().abs().max()))
+    assert float((fast_nrm.float() - want_nrm.float()).abs().max()) <= tol * scale
+    want_add = torch.empty_like(x)
+    refcu.add(x, r, want_add, rows * hidden, code(x))
+    assert torch.equal(bits(ops.cuda_add(x, r)), bits(want_add))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_gather_and_argmax_equal_reference_kernels(refcu, dtype):
+    rng = np.random.default_rng(8)
+    table = dev(wl.normal(rng, (3000, 1024), 0.02, dtype))
+    ids = rng.integers(0, 3000, 257).astype(np.int32)
+    want = torch.empty(257, 1024, dtype=table.dtype, device=DEV)
+    refcu.embedding_lookup(table, ids, want, 1024, 3000, code(table))
+    assert torch.equal(bits(ops.cuda_embedding_lookup(table, ids.tolist())), bits(want))
+    logits = np.round(wl.normal(rng, (3, wl.VOCAB), 4.0) * 2) / 2            # ties
+    logits = dev(logits.astype(dtype))
+    assert ops.cuda_argmax_last_row(logits) == refcu.argmax_last_row(logits, 3, wl.VOCAB, code(logits))
+    each = [refcu.argmax_last_row(logits[r:r + 1].contiguous(), 1, wl.VOCAB, code(logits)) for r in range(3)]
+    assert ops.argmax_rows(logits).tolist() == each
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_deterministic_swiglu_rope_softmax_track_reference_kernels(refcu, dtype):
+    rng = np.random.default_rng(21)
+    tol = 4e-7 if dtype == np.float32 else 0.0     # relative, a few fp32 ulps; fp16 outputs must round identically
+    g, u = dev(wl.normal(rng, 100003, 2.0, dtype)), dev(wl.normal(rng, 100003, 2.0, dtype))
+    want = torch.empty_like(g)
+    refcu.swiglu(g, u, want, g.numel(), code(g))
+    got = ops.cuda_swiglu(g, u, "deterministic")
+    if dtype == np.float16:
+        assert float((bits(got).int() - bits(want).int()).abs().max()) <= 1          # same formula, same rounding: <= 1 ulp
+        assert float((bits(got) != bits(want)).float().mean()) < 1e-3
+    else:
+        assert float(((got - want).abs() / want.abs().clamp_min(1e-30)).max()) <= tol
+    # RoPE: the all-fp32 angle of the reference kernel (src/ops_cuda.cu:133), positions up to a prefill's length
+    x = dev(wl.normal(rng, (300, 16, 128), dtype=dtype))
+    pos = rng.integers(0, 512, 300).astype(np.int32)
+    want = torch.empty_like(x)
+    refcu.rope(x, pos, want, 300, 16, 128, 1e6, code(x))
+    got = ops.cuda_rope(x, pos.tolist(), 1e6, "deterministic")
+    bound = 2e-6 if dtype == np.float32 else 2 ** -9
+    assert float((got.float() - want.float()).abs().max()) <= bound * max(1.0, float(x.float().abs().max()))
+    if dtype == np.float16:
+        tp = torch.empty_like(x)
+        refcu.rope_token_positions(x, dev(pos), tp, 300, 16, 1e6)
+        assert torch.equal(bits(tp), bits(want))             # the reference's two entry points agree with each other
+    # softmax: same order, same fp32 accumulator
+    lg = dev(wl.normal(rng, (4, 8192), 4.0, dtype))
+    want = torch.empty_like(lg)
+    refcu.softmax(lg, want, 4, 8192, code(lg))
+    got = ops.cuda_softmax_last_dim(lg, "deterministic")
+    peak = want.float().max(dim=1, keepdim=True).values
+    assert float(((got.float() - want.float()).abs() / torch.maximum(want.float(), peak)).max()) <= (2e-6 if dtype == np.float32 else 2e-3)
