@@ -26,23 +26,24 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* global_src
                "l"(global_src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
-__device__ __forceinline__ bool mbarrier_done(uint64_t* bar, uint32_t parity) {
+// One hardware-assisted wait: the thread is suspended until the barrier's phase with this parity has
+// completed or about `hint_ns` nanoseconds have passed, whichever comes first; true = completed.
+// (A polling loop around test_wait with a sleep wakes far later than the data arrives.)
+__device__ __forceinline__ bool mbarrier_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t done;
-  asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
                : "=r"(done)
-               : "r"(smem_addr(bar)), "r"(parity)
+               : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns)
                : "memory");
   return done != 0;
 }
-// Bounded wait: about a quarter of a second of polling, then give up (the caller raises a status bit).
+// Bounded wait: at most 2^15 suspensions of ~10 us each (a third of a second), then give up; the caller
+// records the failure and carries on without touching the data.
 __device__ __forceinline__ bool mbarrier_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    if (mbarrier_done(bar, parity)) return true;
-    __nanosleep(32);
-  }
+  for (int attempt = 0; attempt < (1 << 15); ++attempt)
+    if (mbarrier_try_wait(bar, parity, 10000u)) return true;
   return false;
 }
-
 
 // Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy
 // (bulk copy) accesses: needed before a buffer that threads have just read is refilled by a copy.
