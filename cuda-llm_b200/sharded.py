@@ -59,11 +59,15 @@ def allreduce_argmax_keys(keys: torch.Tensor, group=None) -> torch.Tensor:
 
 def allreduce_softmax_stats(row_max: torch.Tensor, row_sum: torch.Tensor,
                             rebase: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None],
-                            group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+                            group=None, global_max: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Turns per-shard (max, sum) into the global (max, sum), in two small all-reduces.
     `rebase(local_max, global_max, local_sum)` multiplies local_sum by exp(local_max - global_max)
-    in place (the b2_softmax_rebase kernel on GPUs).  row_sum is updated in place."""
-    global_max = row_max.clone()
+    in place (the b2_softmax_rebase kernel on GPUs).  row_sum is updated in place.  `global_max` may be a
+    preallocated buffer (nothing is allocated then, which suits CUDA-graph capture)."""
+    if global_max is None:
+        global_max = row_max.clone()
+    else:
+        global_max.copy_(row_max)
     multi = dist.is_initialized() and dist.get_world_size(group) > 1
     if multi:
         dist.all_reduce(global_max, op=dist.ReduceOp.MAX, group=group)
@@ -75,22 +79,27 @@ def allreduce_softmax_stats(row_max: torch.Tensor, row_sum: torch.Tensor,
 
 # ---------------------------------------------------------------- GPU drivers
 
-def argmax_keys(logits_shard: torch.Tensor, index_base: int) -> torch.Tensor:
+def argmax_keys(logits_shard: torch.Tensor, index_base: int, keys: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Packed keys [rows] of this rank's columns (b2_argmax_keys)."""
     _ops._logits_req(logits_shard, "sharded_argmax")
     rows, width = logits_shard.shape
-    keys = torch.empty(rows, dtype=torch.int64, device=logits_shard.device)
+    if keys is None:
+        keys = torch.empty(rows, dtype=torch.int64, device=logits_shard.device)
     ws = _ops.argmax_workspace(logits_shard.device, rows)
     _lib.check(_lib.load().b2_argmax_keys(logits_shard.data_ptr(), rows, width, width, _ops._code(logits_shard),
                                           index_base, keys.data_ptr(), ws.data_ptr(), _ops._stream()))
     return keys
 
 
-def sharded_argmax(logits_shard: torch.Tensor, index_base: int, group=None) -> torch.Tensor:
+def sharded_argmax(logits_shard: torch.Tensor, index_base: int, group=None, keys: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Global row argmax (int32 [rows], on the device) of logits whose columns
-    [index_base, index_base + shard width) live on this rank."""
-    keys = allreduce_argmax_keys(argmax_keys(logits_shard, index_base), group)
-    out = torch.empty(keys.shape[0], dtype=torch.int32, device=keys.device)
+    [index_base, index_base + shard width) live on this rank.  With `keys` (int64 [rows]) and `out`
+    (int32 [rows]) given nothing is allocated, so the call can be recorded into a CUDA graph
+    together with its all-reduce."""
+    keys = allreduce_argmax_keys(argmax_keys(logits_shard, index_base, keys), group)
+    if out is None:
+        out = torch.empty(keys.shape[0], dtype=torch.int32, device=keys.device)
     _lib.check(_lib.load().b2_argmax_decode_keys(keys.data_ptr(), keys.shape[0], out.data_ptr(), _ops._stream()))
     return out
 
@@ -100,17 +109,20 @@ def _rebase_kernel(row_max: torch.Tensor, global_max: torch.Tensor, row_sum: tor
                                              row_sum.shape[0], _ops._stream()))
 
 
-def sharded_softmax(logits_shard: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """This rank's columns of the row softmax taken over ALL ranks' columns."""
+def sharded_softmax(logits_shard: torch.Tensor, group=None, out: Optional[torch.Tensor] = None,
+                    stats: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """This rank's columns of the row softmax taken over ALL ranks' columns.  `stats`: optional float32
+    [3, rows] scratch (local max, local sum, global max); with it and `out` given nothing is allocated."""
     _ops._logits_req(logits_shard, "sharded_softmax")
     rows, width = logits_shard.shape
     L = _lib.load()
-    row_max = torch.empty(rows, dtype=torch.float32, device=logits_shard.device)
-    row_sum = torch.empty_like(row_max)
+    if stats is None:
+        stats = torch.empty(3, rows, dtype=torch.float32, device=logits_shard.device)
+    row_max, row_sum, gmax_buf = stats[0], stats[1], stats[2]
     code = _ops._code(logits_shard)
     _lib.check(L.b2_softmax_stats(logits_shard.data_ptr(), rows, width, code, row_max.data_ptr(), row_sum.data_ptr(),
                                   _ops._stream()))
-    global_max, global_sum = allreduce_softmax_stats(row_max, row_sum, _rebase_kernel, group)
+    global_max, global_sum = allreduce_softmax_stats(row_max, row_sum, _rebase_kernel, group, gmax_buf)
     if out is None:
         out = torch.empty_like(logits_shard)
     _lib.check(L.b2_softmax_apply(logits_shard.data_ptr(), out.data_ptr(), rows, width, code, global_max.data_ptr(),

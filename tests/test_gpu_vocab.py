@@ -191,6 +191,13 @@ def test_vocab_sharded_softmax_single_gpu_emulation(b2, port, world):
         lib.check(L.b2_softmax_apply(t.data_ptr(), o.data_ptr(), 8, t.shape[1], 0, gmax.data_ptr(), gsum.data_ptr(), s))
         outs.append(host(o))
     softmax_check(np.concatenate(outs, axis=1), x, port, "fast", f"sharded softmax world={world}")
+    # preallocated buffers (the form recorded into CUDA graphs together with the all-reduces)
+    keys, ids = torch.empty(8, dtype=torch.int64, device=DEV), torch.empty(8, dtype=torch.int32, device=DEV)
+    stats, out = torch.empty(3, 8, device=DEV), torch.empty(8, wl.VOCAB, device=DEV)
+    assert sharded.sharded_argmax(dev(x), 0, keys=keys, out=ids) is ids
+    assert np.array_equal(host(ids), port.argmax_rows(x))
+    assert sharded.sharded_softmax(dev(x), out=out, stats=stats) is out
+    softmax_check(host(out), x, port, "fast", "sharded softmax, preallocated")
     # the driver function itself, as a world of one (no process group initialised)
     softmax_check(host(sharded.sharded_softmax(dev(x))), x, port, "fast", "sharded softmax, one rank")
     assert np.array_equal(host(sharded.sharded_argmax(dev(x), 0)), port.argmax_rows(x))
