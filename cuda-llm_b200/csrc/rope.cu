@@ -251,16 +251,19 @@ __device__ __forceinline__ void rope_item_from_shared(const uint4* xs, uint4* ou
 }
 
 // All heads of one tensor for one token, from the staged row.  kHv > 0 fixes hv (vectors per half head)
-// at compile time.  The 32 lanes cover 32/hv heads per step, i.e. always 64 vectors: the lane's vector
-// index simply advances by 64 per step, so full steps carry no index arithmetic and no predicates.
-template <typename T, bool kNorm, int kHv>
-__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int heads, int hv_rt,
+// and kHeads > 0 the head count at compile time.  The 32 lanes cover 32/hv heads per step, i.e. always
+// 64 vectors: the lane's vector index simply advances by 64 per step, so full steps carry no index
+// arithmetic and no predicates, and with a fixed head count the steps are unrolled so that the loads,
+// shuffles and stores of different heads overlap.
+template <typename T, bool kNorm, int kHv, int kHeads>
+__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int heads_rt, int hv_rt,
                                                        int hv_shift_rt, int lane,
                                                        const LaneAngles<Elem<T>::kPerVec / 2>& ang, float inv_dim,
                                                        float eps) {
   constexpr int P = Elem<T>::kPerVec / 2;
   const int hv = kHv > 0 ? kHv : hv_rt;
   const int shift = kHv > 0 ? (kHv == 1 ? 0 : kHv == 2 ? 1 : kHv == 4 ? 2 : kHv == 8 ? 3 : kHv == 16 ? 4 : 5) : hv_shift_rt;
+  const int heads = kHeads > 0 ? kHeads : heads_rt;
   const int v = lane & (hv - 1);
   float2 wl[P], wh[P];
   if (kNorm) {
@@ -270,8 +273,15 @@ __device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const ui
   const int items = heads << shift;
   int where = ((lane >> shift) << (shift + 1)) + v;
   const int full = items >> 5;
-  for (int i = 0; i < full; ++i, where += 2 * kWarpSize)
-    rope_item_from_shared<T, kNorm, P>(xs, out, where, hv, true, wl, wh, ang, inv_dim, eps);
+  if (kHeads > 0 && kHv > 0) {
+#pragma unroll
+    for (int i = 0; i < full; ++i)
+      rope_item_from_shared<T, kNorm, P>(xs, out, where + i * 2 * kWarpSize, hv, true, wl, wh, ang, inv_dim, eps);
+    where += full * 2 * kWarpSize;
+  } else {
+    for (int i = 0; i < full; ++i, where += 2 * kWarpSize)
+      rope_item_from_shared<T, kNorm, P>(xs, out, where, hv, true, wl, wh, ang, inv_dim, eps);
+  }
   if (items & 31) {
     // ragged last step: lanes past the end redo the last head (valid memory, converged shuffles) and store nothing
     const bool ok = (full << 5) + lane < items;
@@ -280,29 +290,38 @@ __device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const ui
   }
 }
 
-template <typename T, bool kNorm, int kHv>
-__global__ void __launch_bounds__(kThreads, 3)
+// Shared memory per warp: two stages of (q row + k row), then two cos/sin tables (one per stage).
+// The table of the NEXT token is computed right after its rows have been requested and before the
+// warp waits for the current rows, so the fp64 angle arithmetic runs under the copy's latency.
+constexpr int kBulkWarps = 4, kBulkCtasPerSm = 4;
+constexpr int kBulkFreqPerLane = kMaxTableHalf / kWarpSize;   // head_dim <= 256
+constexpr int kBulkMaxStages = 4;
+
+template <typename T, bool kNorm, int kHv, int kQHeads, int kKHeads>
+__global__ void __launch_bounds__(kBulkWarps * kWarpSize, kBulkCtasPerSm)
 rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
-                        int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
+                        int hv_shift, int64_t pos_period, float eps, float theta, int stages,
+                        const __grid_constant__ InvFreq freq) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int vecs_per_head = 2 * hv;
-  const uint32_t q_bytes = uint32_t(q.heads) * vecs_per_head * 16u, k_bytes = uint32_t(k.heads) * vecs_per_head * 16u;
-  const uint32_t stage_bytes = q_bytes + k_bytes, per_warp = 2u * stage_bytes + uint32_t(head_dim) * 4u;
+  const int q_heads = kQHeads > 0 ? kQHeads : q.heads, k_heads = kQHeads > 0 ? kKHeads : k.heads;
+  const uint32_t q_bytes = uint32_t(q_heads) * vecs_per_head * 16u, k_bytes = uint32_t(k_heads) * vecs_per_head * 16u;
+  const uint32_t stage_bytes = q_bytes + k_bytes, table_bytes = uint32_t(head_dim) * 4u;
+  const uint32_t per_warp = uint32_t(stages) * stage_bytes + 2u * table_bytes;
   unsigned char* mine = bulk_smem + size_t(warp) * per_warp;
-  float* cos_row = reinterpret_cast<float*>(mine + 2u * stage_bytes);
-  float* sin_row = cos_row + half;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem + size_t(warps) * per_warp) + 2 * warp;
+  float* tables = reinterpret_cast<float*>(mine + uint32_t(stages) * stage_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem + size_t(warps) * per_warp) + kBulkMaxStages * warp;
   const float inv_dim = 1.0f / float(head_dim);
-  // kernel parameters used inside the token loop, as plain locals
-  const int q_heads = q.heads, k_heads = k.heads, q_vecs = q.heads * vecs_per_head, k_vecs = k.heads * vecs_per_head;
+  const int q_vecs = q_heads * vecs_per_head, k_vecs = k_heads * vecs_per_head;
   const uint4* q_w = reinterpret_cast<const uint4*>(q.w);
   const uint4* k_w = reinterpret_cast<const uint4*>(k.w);
   uint4* q_out = reinterpret_cast<uint4*>(q.out);
   uint4* k_out = reinterpret_cast<uint4*>(k.out);
 
-  if (lane == 0) { mbarrier_init(&bars[0], 1); mbarrier_init(&bars[1], 1); }
+  if (lane == 0)
+    for (int i = 0; i < stages; ++i) mbarrier_init(&bars[i], 1);
   __syncwarp();
 
   const int64_t stride = int64_t(gridDim.x) * warps;
@@ -315,50 +334,79 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
     if (k_bytes != 0u)
       bulk_load(dst + q_bytes, static_cast<const unsigned char*>(k.x) + size_t(token) * k_bytes, k_bytes, &bars[stage]);
   };
-  if (t < tokens && lane == 0) request(t, 0);
-  auto position_of = [&](int64_t token) { return positions[pos_period ? token % pos_period : token]; };
-  int32_t p = t < tokens ? position_of(t) : 0;
+  // A lane always computes the same frequencies (lane, lane + 32, ...): their inverse wavelengths are read
+  // from the parameter table once and kept in registers (a per-lane index into kernel parameters is a
+  // divergent constant load, far too slow to repeat for every token).
+  double lane_freq[kBulkFreqPerLane];
+#pragma unroll
+  for (int i = 0; i < kBulkFreqPerLane; ++i) lane_freq[i] = lane + i * kWarpSize < half ? freq.v[lane + i * kWarpSize] : 0.0;
+  // every lane: cos/sin of one token's frequencies into one of the two tables
+  auto fill_table = [&](int32_t p, int which) {
+    float* cos_row = tables + which * head_dim;
+    const double two_pi_hi = 6.283185307179586232e+00, two_pi_lo = 2.449293598294706414e-16;
+#pragma unroll
+    for (int i = 0; i < kBulkFreqPerLane; ++i) {
+      const int j = lane + i * kWarpSize;
+      if (j < half) {
+        // as rope_cos_sin<false>: fp64 angle, fp64 reduction to [-pi, pi], hardware sine/cosine
+        const double angle = double(p) * lane_freq[i];
+        const double turns = rint(angle * 1.591549430918953456e-01);
+        const float rf = float(fma(-turns, two_pi_lo, fma(-turns, two_pi_hi, angle)));
+        cos_row[j] = __cosf(rf);
+        cos_row[half + j] = __sinf(rf);
+      }
+    }
+  };
+  auto position_of = [&](int64_t token) { return token < tokens ? positions[pos_period ? token % pos_period : token] : 0; };
+  // positions are fetched two tokens ahead of their use, so that no step waits for that load
+  int32_t p_next = position_of(t + stride);
+  if (t < tokens) {
+    if (lane == 0)
+      for (int i = 0; i < stages - 1 && t + i * stride < tokens; ++i) request(t + i * stride, i);
+    fill_table(position_of(t), 0);
+  }
 
+  int stage = 0;        // it % stages
+  uint32_t round = 0;   // it / stages
   for (int it = 0; t < tokens; ++it, t += stride) {
-    const int stage = it & 1;
-    const int64_t t_next = t + stride;
-    int32_t p_next = 0;
-    if (t_next < tokens) {
-      // the other stage was last read during the previous step; every lane passed the __syncwarp
-      // that ends that step after consuming what it read
-      if (lane == 0) { fence_before_bulk_copy(); request(t_next, stage ^ 1); }
-      p_next = position_of(t_next);
+    const int64_t t_next = t + stride, t_ahead = t + (stages - 1) * stride;
+    const int32_t p_after = position_of(t_next + stride);
+    // the stage that the previous step read is free: every lane passed the __syncwarp that ends that step
+    // after consuming what it read
+    if (lane == 0 && t_ahead < tokens) {
+      fence_before_bulk_copy();
+      request(t_ahead, stage == 0 ? stages - 1 : stage - 1);
     }
-    for (int j = lane; j < half; j += kWarpSize) {
-      const float2 cs = rope_cos_sin<false>(p, j, head_dim, theta, freq, half);
-      cos_row[j] = cs.x;
-      sin_row[j] = cs.y;
-    }
-    __syncwarp();
+    if (t_next < tokens) fill_table(p_next, (it + 1) & 1);
+    p_next = p_after;
+    __syncwarp();   // this step's table (written one step ago, or before the loop) is visible to every lane
     LaneAngles<N / 2> ang;
+    const float* cos_row = tables + (it & 1) * head_dim;
     const int first = (lane & (hv - 1)) * N;
 #pragma unroll
     for (int e = 0; e < N / 2; ++e) {
       ang.c[e] = *reinterpret_cast<const float2*>(cos_row + first + 2 * e);
-      ang.s[e] = *reinterpret_cast<const float2*>(sin_row + first + 2 * e);
+      ang.s[e] = *reinterpret_cast<const float2*>(cos_row + half + first + 2 * e);
       ang.neg_s[e] = make_float2(-ang.s[e].x, -ang.s[e].y);
     }
 
-    const uint32_t parity = uint32_t(it >> 1) & 1u;
-    if (!mbarrier_wait_bounded(&bars[stage], parity)) {
-      // never expected: record it, give both stages' copies one more bounded chance to land, and stop
+    if (!mbarrier_wait_bounded(&bars[stage], round & 1u)) {
+      // never expected: record it, give every stage's copy one more bounded chance to land, and stop
       if (lane == 0) atomicAdd(&g_rope_bulk_timeouts, 1u);
-      mbarrier_wait_bounded(&bars[stage], parity);
-      if (t_next < tokens) mbarrier_wait_bounded(&bars[stage ^ 1], uint32_t((it + 1) >> 1) & 1u);
+      for (int i = 0; i < stages && t + i * stride < tokens; ++i) {   // copies in flight: tokens t .. t_ahead
+        const bool wrapped = stage + i >= stages;
+        mbarrier_wait_bounded(&bars[wrapped ? stage + i - stages : stage + i], (wrapped ? round + 1u : round) & 1u);
+      }
       break;
     }
     const uint4* xs = reinterpret_cast<const uint4*>(mine + uint32_t(stage) * stage_bytes);
-    rope_heads_from_shared<T, kNorm, kHv>(xs, q_w, q_out + size_t(t) * q_vecs, q_heads, hv, hv_shift, lane, ang, inv_dim, eps);
+    rope_heads_from_shared<T, kNorm, kHv, kQHeads>(xs, q_w, q_out + size_t(t) * q_vecs, q_heads, hv, hv_shift, lane, ang,
+                                                   inv_dim, eps);
     if (k_heads > 0)
-      rope_heads_from_shared<T, kNorm, kHv>(xs + q_vecs, k_w, k_out + size_t(t) * k_vecs, k_heads, hv, hv_shift, lane, ang,
-                                            inv_dim, eps);
+      rope_heads_from_shared<T, kNorm, kHv, kKHeads>(xs + q_vecs, k_w, k_out + size_t(t) * k_vecs, k_heads, hv, hv_shift,
+                                                     lane, ang, inv_dim, eps);
     __syncwarp();   // stage and table are free again
-    p = p_next;
+    if (++stage == stages) { stage = 0; ++round; }
   }
 }
 
@@ -438,23 +486,26 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
                  int64_t pos_period, float eps, float theta, cudaStream_t s) {
   static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
   if (!enabled) return false;
-  const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = 2 * stage + size_t(head_dim) * 4;
-  const size_t budget = 72 * 1024;                        // three CTAs per SM (227 KB)
-  int warps = int(budget / (per_warp + 16));
-  if (warps < 1) return false;                            // rows too long for two stages: the register kernel takes over
-  if (warps > kWarpsPerCta) warps = kWarpsPerCta;
+  constexpr int stages = 2, max_warps = kBulkWarps;   // deeper prefetch and other warp counts measured no faster
+  const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = stages * stage + 2 * size_t(head_dim) * 4;
+  const size_t bar_bytes = size_t(kBulkMaxStages) * 8;
+  const size_t budget = (227 * 1024) / kBulkCtasPerSm - 1024;   // kBulkCtasPerSm CTAs share one SM's shared memory
+  int warps = int(budget / (per_warp + bar_bytes));
+  if (warps < 1 || head_dim / 2 > kMaxTableHalf) return false;   // rows too long for the stages: the register kernel takes over
+  if (warps > max_warps) warps = max_warps;
   if (int64_t(warps) > tokens) warps = int(tokens);
-  const size_t smem = size_t(warps) * per_warp + size_t(warps) * 16;
-  // the two head sizes of the model family get hv fixed at compile time (head_dim 128: 8 vectors of fp16, 16 of fp32)
-  auto kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16>
-                                                                         : rope_tokens_bulk_kernel<T, kNorm, 0>;
+  const size_t smem = size_t(warps) * (per_warp + bar_bytes);
+  // the head size of the model family gets hv fixed at compile time (head_dim 128: 8 vectors of fp16, 16 of fp32
+  // per half head); fixing the head counts as well measured no faster
+  auto kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8, 0, 0> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16, 0, 0>
+                                                                               : rope_tokens_bulk_kernel<T, kNorm, 0, 0, 0>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
     cudaGetLastError();
     return false;
   }
-  const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * 3;
+  const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * kBulkCtasPerSm;
   kernel<<<unsigned(ctas < cap ? ctas : cap), warps * kWarpSize, smem, s>>>(q, k, positions, tokens, int(head_dim), hv,
-                                                                          hv_shift, pos_period, eps, theta,
+                                                                          hv_shift, pos_period, eps, theta, stages,
                                                                           make_table(head_dim, theta));
   return true;
 }

@@ -178,6 +178,7 @@ __device__ __forceinline__ void online_update(float& m, float& m2, float& s, con
 // nothing reads a neighbour's memory after the last barrier and CTAs retire independently.
 // `status` (may be null): bit 0 is raised if the bulk-copy wait ran out; outputs are then invalid.
 constexpr int kMaxClusterRanks = 16;
+constexpr int kDeviceSlots = 64;
 constexpr uint32_t kBulkChunk = 16 * 1024;
 
 template <typename T, bool kVec, bool kBulk>
@@ -300,6 +301,8 @@ softmax_cluster_kernel(const T* x, T* out, int64_t width, int64_t slice, int* st
 // are in flight at once (K per thread), nothing passes through shared memory, and the loops are
 // fully unrolled: ~6 instructions per element.  Used whenever the slice fits K <= 12 vectors
 // per thread; the shared-memory kernel above takes the rest.
+// Every CTA exponentiates against its OWN slice maximum and the slices are merged afterwards
+// (out = e * 2^(m_slice - m_row) / sum), so one exchange and one cluster barrier carry both statistics.
 template <typename T, int K>
 __global__ void __launch_bounds__(kSoftThreads, 2)
 softmax_cluster_reg_kernel(const T* x, T* out, int64_t width, int64_t slice) {
@@ -338,11 +341,8 @@ softmax_cluster_reg_kernel(const T* x, T* out, int64_t width, int64_t slice) {
     for (int q = 0; q < N; q += 2) { m0 = fmaxf(m0, e[k][q]); m1 = fmaxf(m1, e[k][q + 1]); }
   }
   const float slice_max = block_max(fmaxf(m0, m1), scratch);
-  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_max[rank], tid) = slice_max;
-  cluster.sync();
-  float row_max = -INFINITY;
-  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, peer_max[r]);
-  const float neg_m2 = -row_max * kLog2e;
+  // an all -inf slice exponentiates against 0 (every e becomes 0) and is left out of the merge
+  const float neg_m2 = slice_max == -INFINITY ? 0.0f : -slice_max * kLog2e;
 
   float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
@@ -356,21 +356,196 @@ softmax_cluster_reg_kernel(const T* x, T* out, int64_t width, int64_t slice) {
     }
   }
   const float slice_sum = block_sum(s0 + s1, scratch);
-  if (tid < int(ranks)) *cluster.map_shared_rank(&peer_sum[rank], tid) = slice_sum;
+  if (tid < int(ranks)) {
+    *cluster.map_shared_rank(&peer_max[rank], tid) = slice_max;
+    *cluster.map_shared_rank(&peer_sum[rank], tid) = slice_sum;
+  }
   cluster.sync();
-  float row_sum = 0.0f;
-  for (unsigned r = 0; r < ranks; ++r) row_sum += peer_sum[r];   // rank order: the same sum on every CTA of the row
-  const float inv_sum = 1.0f / row_sum;
-
+  float row_max = -INFINITY;
+  for (unsigned r = 0; r < ranks; ++r) row_max = fmaxf(row_max, peer_max[r]);
+  const float row_m2 = row_max * kLog2e;
+  float row_sum = 0.0f;                                           // rank order: the same sum on every CTA of the row
+  for (unsigned r = 0; r < ranks; ++r)
+    if (peer_max[r] != -INFINITY) row_sum += peer_sum[r] * fast_exp2(fmaf(peer_max[r], kLog2e, -row_m2));
+  // a row of nothing but -inf divides 0 by 0, as the reference does
+  const float scale = slice_max == -INFINITY ? (row_max == -INFINITY ? __int_as_float(0x7fc00000) : 0.0f)
+                                             : fast_exp2(fmaf(slice_max, kLog2e, -row_m2)) / row_sum;
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int v = tid + k * kSoftThreads;
     if (v < nvec) {
 #pragma unroll
-      for (int q = 0; q < N; ++q) e[k][q] *= inv_sum;
+      for (int q = 0; q < N; ++q) e[k][q] *= scale;
       st_stream(dst + v, Elem<T>::pack(e[k]));
     }
   }
+}
+
+// ---- fast mode, streaming form of the register kernel.  The register kernel alone leaves HBM idle
+// while a cluster is between its read burst and its write burst, and its cluster barriers carry a
+// memory fence that waits for the stores in flight.  Here the grid is persistent (as many clusters as
+// fit the GPU at once, each walking rows c, c + clusters, ...), and per row a CTA does:
+//   wait for its stage (filled by the copy engine while the previous row was being finished)
+//   -> registers -> per-warp max, exp against the warp's own max, per-warp sum
+//   -> ONE __syncthreads (stage free: request the next row; warp statistics visible)
+//   -> threads 0..ranks-1 fold the warps' statistics and send them to every CTA of the cluster with an
+//      asynchronous remote store that completes a transaction count on the receiver's mbarrier
+//   -> wait for the own mbarrier (all slices' statistics have landed) -> scale, store.
+// No cluster barrier and no fence inside the loop, so stores of one row drain under the next row's work.
+// Statistic buffers and their mbarriers alternate with the row's parity: a fast CTA may send row r+1
+// while a slow one still reads row r, and cannot get further ahead (it needs the slow CTA's row r+1).
+// `status`: bit 0 is raised if a bounded wait ran out; the outputs of that call are invalid.
+__device__ __forceinline__ uint32_t cluster_address_of(const void* local_shared, uint32_t target_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local_shared)), "r"(target_rank));
+  return remote;
+}
+// 8-byte store into another CTA's shared memory that also counts 8 bytes on that CTA's mbarrier
+__device__ __forceinline__ void remote_store_and_signal(uint32_t remote_data, uint64_t value, uint32_t remote_barrier) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];" ::"r"(remote_data), "l"(value),
+               "r"(remote_barrier)
+               : "memory");
+}
+// as mbarrier_wait_bounded, for data that other CTAs of the cluster wrote (acquire at cluster scope)
+__device__ __forceinline__ bool mbarrier_wait_bounded_cluster(uint64_t* bar, uint32_t parity) {
+  for (int attempt = 0; attempt < (1 << 15); ++attempt) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(10000u)
+        : "memory");
+    if (done != 0) return true;
+  }
+  return false;
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(kSoftThreads, 2)
+softmax_cluster_stream_kernel(const T* x, T* out, int64_t rows, int64_t width, int64_t slice, int* status) {
+  constexpr int N = Elem<T>::kPerVec;
+  constexpr int kWarps = kSoftThreads / kWarpSize;
+  extern __shared__ __align__(128) unsigned char stage_bytes_[];
+  __shared__ float2 warp_stats[2][kWarps];                        // (max, sum) of each warp's elements
+  __shared__ __align__(8) float2 peer_stats[2][kMaxClusterRanks];   // (max, sum) of each slice; written by the other CTAs
+  __shared__ __align__(8) uint64_t stage_barrier, stats_barrier[2];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank(), ranks = cluster.num_blocks();
+  const int64_t clusters = gridDim.x / ranks;
+  const int64_t lo = int64_t(rank) * slice;
+  const int nvec = int(lo >= width ? 0 : (width - lo < slice ? width - lo : slice)) / N;
+  const uint32_t bytes = uint32_t(nvec) * 16u;
+  const uint4* stage = reinterpret_cast<const uint4*>(stage_bytes_);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  auto request = [&](int64_t row) {   // thread 0 only
+    mbarrier_expect_bytes(&stage_barrier, bytes);
+    const char* src = reinterpret_cast<const char*>(x + row * width + lo);
+    for (uint32_t off = 0; off < bytes; off += kBulkChunk)
+      bulk_load(stage_bytes_ + off, src + off, bytes - off < kBulkChunk ? bytes - off : kBulkChunk, &stage_barrier);
+  };
+
+  int64_t row = blockIdx.x / ranks;
+  if (tid == 0) {
+    mbarrier_init(&stage_barrier, 1);
+    mbarrier_init(&stats_barrier[0], 1);
+    mbarrier_init(&stats_barrier[1], 1);
+    mbarrier_expect_bytes(&stats_barrier[0], ranks * 8u);   // the first row's statistics: 8 bytes from each CTA
+    if (row < rows && bytes != 0u) request(row);
+  }
+  __syncthreads();
+  cluster.sync();   // every CTA's barriers exist before anyone stores into a neighbour's shared memory
+
+  bool healthy = true;
+  for (int it = 0; row < rows; ++it, row += clusters) {
+    const int par = it & 1;
+    if (bytes != 0u && !mbarrier_wait_bounded(&stage_barrier, uint32_t(par))) { healthy = false; break; }
+    uint4 raw[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int v = tid + k * kSoftThreads;
+      if (v < nvec) raw[k] = stage[v];
+    }
+    float e[K][N];
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (tid + k * kSoftThreads < nvec) {
+        Elem<T>::unpack(raw[k], e[k]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < N; ++q) e[k][q] = -INFINITY;   // contributes exp(-inf) = 0
+      }
+#pragma unroll
+      for (int q = 0; q < N; q += 2) { m0 = fmaxf(m0, e[k][q]); m1 = fmaxf(m1, e[k][q + 1]); }
+    }
+    const float warp_m = warp_max(fmaxf(m0, m1));
+    // a warp of nothing but -inf exponentiates against 0 (every e becomes 0) and is left out of the merges
+    const float neg_m2 = warp_m == -INFINITY ? 0.0f : -warp_m * kLog2e;
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+#pragma unroll
+      for (int q = 0; q < N; q += 2) {
+        e[k][q] = fast_exp2(fmaf(e[k][q], kLog2e, neg_m2));
+        e[k][q + 1] = fast_exp2(fmaf(e[k][q + 1], kLog2e, neg_m2));
+        s0 += e[k][q];
+        s1 += e[k][q + 1];
+      }
+    }
+    const float warp_s = warp_sum(s0 + s1);
+    if (lane == 0) warp_stats[par][warp] = make_float2(warp_m, warp_s);
+    __syncthreads();   // the stage has been read by everyone; the warps' statistics are visible
+
+    const int64_t next = row + clusters;
+    if (tid == 0 && next < rows) {
+      if (bytes != 0u) { fence_before_bulk_copy(); request(next); }
+      // the next row's statistics: that barrier's previous phase was consumed by every thread before the
+      // __syncthreads above
+      mbarrier_expect_bytes(&stats_barrier[par ^ 1], ranks * 8u);
+    }
+    if (tid < int(ranks)) {
+      float slice_m = -INFINITY;
+      for (int w = 0; w < kWarps; ++w) slice_m = fmaxf(slice_m, warp_stats[par][w].x);
+      const float slice_m2 = slice_m * kLog2e;
+      float slice_s = 0.0f;                                    // warp order: the same sum whoever computes it
+      for (int w = 0; w < kWarps; ++w)
+        if (warp_stats[par][w].x != -INFINITY) slice_s += warp_stats[par][w].y * fast_exp2(fmaf(warp_stats[par][w].x, kLog2e, -slice_m2));
+      const uint64_t packed = (uint64_t(__float_as_uint(slice_s)) << 32) | uint64_t(__float_as_uint(slice_m));
+      remote_store_and_signal(cluster_address_of(&peer_stats[par][rank], unsigned(tid)), packed,
+                              cluster_address_of(&stats_barrier[par], unsigned(tid)));
+    }
+    if (!mbarrier_wait_bounded_cluster(&stats_barrier[par], uint32_t(it >> 1) & 1u)) { healthy = false; break; }
+    float row_m = -INFINITY;
+    for (unsigned r = 0; r < ranks; ++r) row_m = fmaxf(row_m, peer_stats[par][r].x);
+    const float row_m2 = row_m * kLog2e;
+    float row_sum = 0.0f;                                      // rank order: the same sum on every CTA of the row
+    for (unsigned r = 0; r < ranks; ++r)
+      if (peer_stats[par][r].x != -INFINITY) row_sum += peer_stats[par][r].y * fast_exp2(fmaf(peer_stats[par][r].x, kLog2e, -row_m2));
+    // a row of nothing but -inf divides 0 by 0, as the reference does
+    const float scale = warp_m == -INFINITY ? (row_m == -INFINITY ? __int_as_float(0x7fc00000) : 0.0f)
+                                            : fast_exp2(fmaf(warp_m, kLog2e, -row_m2)) / row_sum;
+    uint4* dst = reinterpret_cast<uint4*>(out + row * width + lo);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int v = tid + k * kSoftThreads;
+      if (v < nvec) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) e[k][q] *= scale;
+        st_stream(dst + v, Elem<T>::pack(e[k]));
+      }
+    }
+  }
+  if (!healthy) {
+    // never expected: a bounded wait ran out.  Flag it, give a copy that may still be in flight one more
+    // bounded chance to land (it must not outlive this CTA's shared memory), and meet the other CTAs below.
+    if (tid == 0 && status != nullptr) atomicOr(status, 1);
+    if (bytes != 0u) { mbarrier_wait_bounded(&stage_barrier, 0u); mbarrier_wait_bounded(&stage_barrier, 1u); }
+  }
+  // nobody leaves while a neighbour may still store into its shared memory (only matters after a failure:
+  // in a healthy run every CTA has received all statistics of its last row by now)
+  cluster.sync();
 }
 
 // ---- row statistics (max, sum of exp(x - max)), one CTA per row, one pass, online rescaling
@@ -582,23 +757,83 @@ int launch_softmax_reg(const T* x, T* out, int64_t rows, int64_t width, int rank
   return B2_OK;
 }
 
+// Persistent launch of the streaming kernel: as many clusters as the GPU holds at once (asked of the
+// occupancy calculator once per device and cluster size), each walking several rows.
+template <typename T, int K>
+int launch_softmax_stream(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, int* status,
+                          cudaStream_t s) {
+  auto kernel = softmax_cluster_stream_kernel<T, K>;
+  const size_t smem = size_t(K) * kSoftThreads * 16;
+  static std::mutex mutex;
+  static int resident[kDeviceSlots][kMaxClusterRanks + 1] = {};   // 0 = not asked yet, -1 = cannot launch
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kDeviceSlots) { cudaGetLastError(); return B2_ERR_UNSUPPORTED; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kSoftThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(ranks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (resident[device][ranks] == 0) {
+      int n = 0;
+      cfg.gridDim = dim3(unsigned(ranks) * 64u);
+      const bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) == cudaSuccess &&
+                      (ranks <= 8 || cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) &&
+                      cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0;
+      if (!ok) cudaGetLastError();
+      resident[device][ranks] = ok ? n : -1;
+    }
+    clusters = resident[device][ranks];
+  }
+  if (clusters <= 0) return B2_ERR_UNSUPPORTED;
+  if (int64_t(clusters) > rows) clusters = int(rows);
+  cfg.gridDim = dim3(unsigned(clusters) * unsigned(ranks));
+  if (cudaLaunchKernelEx(&cfg, kernel, x, out, rows, width, slice, status) != cudaSuccess) {
+    cudaGetLastError();
+    return B2_ERR_UNSUPPORTED;
+  }
+  return B2_OK;
+}
+
 // K vectors of N elements per thread stay in registers: at most 48 floats (64 registers at two CTAs per SM).
 template <typename T, int K>
-int launch_softmax_reg_if_fits(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
-  if constexpr (K * Elem<T>::kPerVec <= 48) return launch_softmax_reg<T, K>(x, out, rows, width, ranks, slice, s);
-  else return B2_ERR_UNSUPPORTED;
+int launch_softmax_reg_if_fits(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, int* status,
+                               cudaStream_t s) {
+  if constexpr (K * Elem<T>::kPerVec <= 48) {
+    // several rows per cluster: stream them; otherwise one cluster per row is all there is to do
+    if (rows * ranks > int64_t(sm_count()) * 2 &&
+        launch_softmax_stream<T, K>(x, out, rows, width, ranks, slice, status, s) == B2_OK)
+      return B2_OK;
+    return launch_softmax_reg<T, K>(x, out, rows, width, ranks, slice, s);
+  } else {
+    return B2_ERR_UNSUPPORTED;
+  }
 }
 
 template <typename T>
-int launch_softmax_reg_any(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, cudaStream_t s) {
+int launch_softmax_reg_any(const T* x, T* out, int64_t rows, int64_t width, int ranks, int64_t slice, int* status,
+                           cudaStream_t s) {
   const int64_t vecs = slice / Elem<T>::kPerVec, per_thread = (vecs + kSoftThreads - 1) / kSoftThreads;
-  if (per_thread <= 1) return launch_softmax_reg_if_fits<T, 1>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 2) return launch_softmax_reg_if_fits<T, 2>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 4) return launch_softmax_reg_if_fits<T, 4>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 6) return launch_softmax_reg_if_fits<T, 6>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 8) return launch_softmax_reg_if_fits<T, 8>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 10) return launch_softmax_reg_if_fits<T, 10>(x, out, rows, width, ranks, slice, s);
-  if (per_thread <= 12) return launch_softmax_reg_if_fits<T, 12>(x, out, rows, width, ranks, slice, s);
+  if (per_thread <= 1) return launch_softmax_reg_if_fits<T, 1>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 2) return launch_softmax_reg_if_fits<T, 2>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 3) return launch_softmax_reg_if_fits<T, 3>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 4) return launch_softmax_reg_if_fits<T, 4>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 5) return launch_softmax_reg_if_fits<T, 5>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 6) return launch_softmax_reg_if_fits<T, 6>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 7) return launch_softmax_reg_if_fits<T, 7>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 8) return launch_softmax_reg_if_fits<T, 8>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 9) return launch_softmax_reg_if_fits<T, 9>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 10) return launch_softmax_reg_if_fits<T, 10>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 11) return launch_softmax_reg_if_fits<T, 11>(x, out, rows, width, ranks, slice, status, s);
+  if (per_thread <= 12) return launch_softmax_reg_if_fits<T, 12>(x, out, rows, width, ranks, slice, status, s);
   return B2_ERR_UNSUPPORTED;
 }
 
@@ -641,15 +876,10 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
     return launch_status("softmax (deterministic)");
   }
   // smallest cluster whose slices fit, then widened (up to 8) while rows alone cannot fill the SMs
-  static const int max_ranks = [] {                 // tuning aid: B2_SOFTMAX_CLUSTER=16 opts in to the
-    const char* v = std::getenv("B2_SOFTMAX_CLUSTER");   // non-portable cluster size
-    const int n = v ? std::atoi(v) : 8;
-    return n == 16 || n == 4 || n == 2 || n == 1 ? n : 8;
-  }();
+  constexpr int max_ranks = 8;   // the portable cluster size; 9 measured 2 % faster and 10 or more far slower
   int ranks = 1;
   while (ranks < max_ranks && size_t((width + ranks - 1) / ranks) * sizeof(float) > kClusterSliceBytes) ranks <<= 1;
   while (ranks < max_ranks && rows * ranks < int64_t(sm_count()) * 2 && width / (ranks * 2) >= 1024) ranks <<= 1;
-  if (max_ranks == 16 && width / 16 >= 1024) ranks = 16;
   int64_t slice = (width + ranks - 1) / ranks;
   slice = (slice + N - 1) / N * N;
   if (size_t(slice) * sizeof(float) <= kClusterSliceBytes) {
@@ -658,7 +888,7 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
     int* status = reinterpret_cast<int*>(static_cast<char*>(workspace) + softmax_workspace_bytes(rows) - 16);
     int rc;
     static const bool reg_path = [] { const char* v = std::getenv("B2_SOFTMAX_REG"); return !v || std::atoi(v) != 0; }();
-    if (vec && reg_path && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, s) == B2_OK) return B2_OK;
+    if (vec && reg_path && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, status, s) == B2_OK) return B2_OK;
     if (vec && sizeof(T) == 4 && slice % 4 == 0)   // fp32 rows: shared memory holds the input's own bytes -> bulk copy
       rc = launch_softmax_cluster<T, true, true>(x, out, rows, width, ranks, slice, status, s);
     else

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from cuda_llm_b200 import ops, sharded, workloads as wl
-from util import f16_bits
+from util import assert_within_1ulp_f16, f16_bits
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -137,6 +137,31 @@ def test_softmax_f32(b2, port, rows, width, mode):
     got = host(ops.cuda_softmax_last_dim(dev(x), mode))
     softmax_check(got, x, port, mode, f"softmax {mode} {rows}x{width}")
     assert ops.softmax_status(DEV, rows) == 0          # no bounded wait ran out
+
+
+@pytest.mark.parametrize("rows,width,dtype", [(80, 151936, np.float32), (100, 60004, np.float32), (333, 30000, np.float32),
+                                              (600, 4096, np.float16), (90, 151936, np.float16), (2000, 1000, np.float32)])
+def test_softmax_many_rows_streaming_clusters(b2, port, rows, width, dtype):
+    """More rows than clusters fit the GPU at once: the persistent kernel walks several rows per cluster
+    (copy engine one row ahead, statistics exchanged through remote shared-memory stores).  Includes
+    ragged last slices, slices and warps that are entirely masked (-inf), and one fully masked row."""
+    rng = np.random.default_rng(rows * 7 + width)
+    x = wl.normal(rng, (rows, width), 4.0).astype(dtype)
+    x[1, : width // 2] = -np.inf            # whole slices of a row masked
+    x[2, width // 3:] = -np.inf
+    x[3, 5:] = -np.inf                      # nearly everything masked
+    x[rows - 1, :] = -np.inf                # nothing left: 0/0 like the reference
+    got = host(ops.cuda_softmax_last_dim(dev(x), "fast"))
+    assert ops.softmax_status(DEV, rows) == 0
+    assert np.isnan(got[rows - 1].astype(np.float32)).all()
+    live = np.arange(rows) != rows - 1
+    xf = x[live].astype(np.float32)
+    if dtype == np.float32:
+        softmax_check(got[live], xf, port, "fast", f"streaming softmax {rows}x{width}")
+    else:
+        assert_within_1ulp_f16(got[live], port.softmax_f64(xf), f"streaming softmax f16 {rows}x{width}")
+    again = host(ops.cuda_softmax_last_dim(dev(x), "fast"))
+    assert np.array_equal(got.view(np.uint8), again.view(np.uint8))     # run-to-run bit-identical
 
 
 def test_softmax_reference_test_literals(b2, port):
