@@ -3,10 +3,12 @@
 // except b2_alloc / b2_free.
 #include "b2ops.h"
 #include "common.cuh"
+#include "exchange.cuh"
 #include "kernels.h"
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -264,6 +266,92 @@ int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int 
   B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width), op, "rows must be >= 0 and width > 0");
   B2_REQUIRE(rows == 0 || (x && out && row_max && row_sum), op, "null pointer");
   return launch_softmax_apply(x, out, rows, width, dtype, row_max, row_sum, as_stream(stream));
+}
+
+size_t b2_p2p_exchange_bytes(int world, int64_t max_rows) {
+  return world >= 1 && world <= B2_P2P_MAX_WORLD && max_rows > 0 && max_rows < (1 << 24) ? exchange_bytes(world, max_rows) : 0;
+}
+
+int b2_p2p_exchange_init(void* buffer, int world, int64_t max_rows, b2_stream stream) {
+  const char* op = "b2_p2p_exchange_init";
+  B2_REQUIRE(buffer != nullptr, op, "null pointer");
+  B2_REQUIRE(b2_p2p_exchange_bytes(world, max_rows) != 0, op, "need 1 <= world <= B2_P2P_MAX_WORLD and 0 < max_rows < 2^24");
+  if (cudaMemsetAsync(buffer, 0, exchange_bytes(world, max_rows), as_stream(stream)) != cudaSuccess) return launch_status(op);
+  return B2_OK;
+}
+
+int b2_ipc_export(const void* device_ptr, unsigned char handle[64]) {
+  const char* op = "b2_ipc_export";
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI carries IPC handles as 64 bytes");
+  B2_REQUIRE(device_ptr != nullptr && handle != nullptr, op, "null pointer");
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(device_ptr));
+  if (e != cudaSuccess) { set_error("%s: CUDA error: %s", op, cudaGetErrorString(e)); cudaGetLastError(); return B2_ERR_CUDA; }
+  memcpy(handle, &h, 64);
+  return B2_OK;
+}
+
+int b2_ipc_open(const unsigned char handle[64], void** device_ptr) {
+  const char* op = "b2_ipc_open";
+  B2_REQUIRE(handle != nullptr && device_ptr != nullptr, op, "null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { set_error("%s: CUDA error: %s", op, cudaGetErrorString(e)); cudaGetLastError(); return B2_ERR_CUDA; }
+  *device_ptr = p;
+  return B2_OK;
+}
+
+int b2_ipc_close(void* device_ptr) {
+  if (device_ptr == nullptr) return B2_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(device_ptr);
+  if (e != cudaSuccess) { set_error("b2_ipc_close: CUDA error: %s", cudaGetErrorString(e)); cudaGetLastError(); return B2_ERR_CUDA; }
+  return B2_OK;
+}
+
+static int exchange_checks(const char* op, const b2_p2p_exchange* x, int64_t rows, int32_t* status, ExchangeArgs* out) {
+  B2_REQUIRE(x != nullptr, op, "null exchange descriptor");
+  B2_REQUIRE(x->world >= 1 && x->world <= B2_P2P_MAX_WORLD && x->rank >= 0 && x->rank < x->world, op,
+             "need 1 <= world <= B2_P2P_MAX_WORLD and 0 <= rank < world");
+  B2_REQUIRE(x->max_rows > 0 && x->max_rows < (1 << 24), op, "max_rows out of range");
+  if (rows > x->max_rows) { set_error("%s: %lld rows exceed the exchange buffer's max_rows %lld", op, (long long)rows, (long long)x->max_rows); return B2_ERR_TOO_LARGE; }
+  for (int g = 0; g < x->world; ++g) {
+    B2_REQUIRE(x->buffers[g] != nullptr, op, "null exchange buffer");
+    out->buf[g] = static_cast<unsigned char*>(x->buffers[g]);
+  }
+  for (int g = x->world; g < kMaxWorld; ++g) out->buf[g] = nullptr;
+  out->world = x->world;
+  out->rank = x->rank;
+  out->max_rows = x->max_rows;
+  out->timeout_ns = static_cast<unsigned long long>(x->timeout_ms ? x->timeout_ms : 2000u) * 1000000ull;
+  out->status = status;
+  return B2_OK;
+}
+
+int b2_argmax_rows_sharded(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                           int64_t index_base, int32_t* out_ids, void* workspace, const b2_p2p_exchange* exchange,
+                           int32_t* status, b2_stream stream) {
+  const char* op = "b2_argmax_rows_sharded";
+  int rc = argmax_checks(op, logits, rows, width, row_stride, dtype, index_base, out_ids, workspace);
+  if (rc != B2_OK) return rc;
+  B2_REQUIRE(width <= 0x7fffffffll, op, "width must fit int32");
+  ExchangeArgs xa;
+  rc = exchange_checks(op, exchange, rows, status, &xa);
+  if (rc != B2_OK) return rc;
+  return launch_argmax_exchange(logits, rows, width, row_stride, dtype, index_base, out_ids, workspace, xa, as_stream(stream));
+}
+
+int b2_softmax_stats_sharded(const void* x, int64_t rows, int64_t width, int dtype, float* global_max, float* global_sum,
+                             const b2_p2p_exchange* exchange, int32_t* status, b2_stream stream) {
+  const char* op = "b2_softmax_stats_sharded";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width) && rows < (1 << 24), op, "rows must be >= 0 and width > 0");
+  B2_REQUIRE(rows == 0 || (x && global_max && global_sum), op, "null pointer");
+  ExchangeArgs xa;
+  const int rc = exchange_checks(op, exchange, rows, status, &xa);
+  if (rc != B2_OK) return rc;
+  return launch_softmax_stats_exchange(x, rows, width, dtype, global_max, global_sum, xa, as_stream(stream));
 }
 
 void* b2_alloc(size_t bytes) {

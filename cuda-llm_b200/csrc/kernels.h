@@ -40,4 +40,11 @@ int launch_softmax_rebase(const float* row_max, const float* global_max, float* 
 int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
                          const float* row_sum, cudaStream_t s);
 
+// vocab.cu, vocabulary-sharded forms with the inter-GPU exchange fused into the kernel (exchange.cuh)
+struct ExchangeArgs;
+int launch_argmax_exchange(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                           int64_t index_base, int32_t* out_ids, void* workspace, const ExchangeArgs& xa, cudaStream_t s);
+int launch_softmax_stats_exchange(const void* x, int64_t rows, int64_t width, int dtype, float* global_max,
+                                  float* global_sum, const ExchangeArgs& xa, cudaStream_t s);
+
 }  // namespace b2

@@ -17,6 +17,7 @@
 // (src/ops_cuda.cu:132: one thread per row, strided access).
 #include "common.cuh"
 #include "bulk_copy.cuh"
+#include "exchange.cuh"
 #include "kernels.h"
 #include "b2ops.h"
 
@@ -123,6 +124,67 @@ argmax_rows_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t c
   }
   if (out_keys != nullptr) out_keys[row] = static_cast<int64_t>(key ^ kSignBit);
   if (out_ids != nullptr) out_ids[row] = key == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(key & 0xffffffffull));
+}
+
+// Vocabulary-sharded form with the exchange fused into the kernel's tail: the same fold of this
+// GPU's columns to one key per row, then the CTA that finishes the last row pushes the keys to
+// every peer, waits (bounded) for theirs and writes the global winners' indices.
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kArgThreads)
+argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_t row_stride, int64_t chunk, int chunks,
+                            int64_t index_base, int32_t* out_ids, unsigned long long* keys, unsigned int* tickets,
+                            const __grid_constant__ ExchangeArgs xa) {
+  __shared__ float warp_v[kArgThreads / kWarpSize];
+  __shared__ int warp_i[kArgThreads / kWarpSize];
+  __shared__ int run_tail;
+  const int64_t row = blockIdx.x / chunks;
+  const int c = int(blockIdx.x - row * chunks);
+  const int64_t lo = int64_t(c) * chunk;
+  const int64_t n = width - lo < chunk ? width - lo : chunk;
+
+  float bv = -FLT_MAX;
+  int bi = kNoIndex;
+  scan_range<T, kVec>(logits + row * row_stride + lo, n, [&](float v, int64_t i) {
+    if (v > bv) { bv = v; bi = int(lo + i); }
+  });
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_down_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_down_sync(0xffffffffu, bi, offset);
+    if (beats(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { warp_v[warp] = bv; warp_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < kArgThreads / kWarpSize; ++k)
+      if (beats(warp_v[k], warp_i[k], bv, bi)) { bv = warp_v[k]; bi = warp_i[k]; }
+    unsigned long long key = bi == kNoIndex ? 0ull : pack_key(bv, uint32_t(index_base + bi));
+    bool row_finished = true;
+    if (chunks > 1) {
+      if (key != 0ull) atomicMax(keys + row, key);
+      __threadfence();
+      row_finished = atomicAdd(tickets + row, 1u) == unsigned(chunks - 1);
+      if (row_finished) {
+        __threadfence();
+        key = atomicExch(keys + row, 0ull);  // read the merged key and leave the scratch zeroed
+        tickets[row] = 0u;
+      }
+    }
+    int tail = 0;
+    if (row_finished) {
+      exchange_own_slot(xa)[row] = key;
+      tail = exchange_row_done(xa, rows) ? 1 : 0;
+    }
+    run_tail = tail;
+  }
+  __syncthreads();
+  if (!run_tail) return;
+  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
+    unsigned long long best = 0ull;               // 0 = no shard saw a candidate: index 0, like the reference
+    for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
+    out_ids[r] = best == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(best & 0xffffffffull));
+  });
 }
 
 __global__ void argmax_decode_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids) {
@@ -584,6 +646,64 @@ softmax_stats_kernel(const T* x, int64_t width, float* row_max, float* row_sum) 
   if (threadIdx.x == 0) { row_max[row] = big; row_sum[row] = s; }
 }
 
+// Vocabulary-sharded row statistics with the exchange fused into the tail: (max, sum) of this GPU's
+// columns per row, pushed to every peer; the CTA that finishes the last row waits (bounded) for the
+// peers' pairs and writes the statistics of the WHOLE row, ready for softmax_apply_kernel.
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kSoftThreads)
+softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* global_max, float* global_sum,
+                              const __grid_constant__ ExchangeArgs xa) {
+  constexpr int N = Elem<T>::kPerVec;
+  __shared__ float scratch[32];
+  __shared__ int run_tail;
+  const int64_t row = blockIdx.x;
+  const T* src = x + row * width;
+  const int64_t step = blockDim.x;
+  float m = -INFINITY, m2 = -INFINITY, s = 0.0f;
+  if (kVec) {
+    const int64_t nvec = width / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += step * 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (v0 + k * step < nvec) r[k] = ld_stream(vp + v0 + k * step);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (v0 + k * step < nvec) {
+          float e[N];
+          Elem<T>::unpack(r[k], e);
+          online_update<N>(m, m2, s, e);
+        }
+      }
+    }
+    for (int64_t i = nvec * N + threadIdx.x; i < width; i += step) { const float e = Elem<T>::load(src + i); online_update<1>(m, m2, s, &e); }
+  } else {
+    for (int64_t i = threadIdx.x; i < width; i += step) { const float e = Elem<T>::load(src + i); online_update<1>(m, m2, s, &e); }
+  }
+  const float big = block_max(m, scratch);
+  s = m2 == -INFINITY ? 0.0f : s * fast_exp2(m2 - big * kLog2e);
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) {
+    exchange_own_slot(xa)[row] = (static_cast<unsigned long long>(__float_as_uint(s)) << 32) | __float_as_uint(big);
+    run_tail = exchange_row_done(xa, rows) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!run_tail) return;
+  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
+    float top = -INFINITY;
+    for (int g = 0; g < xa.world; ++g) top = fmaxf(top, __uint_as_float(uint32_t(partial_of(g))));
+    const float top2 = top * kLog2e;
+    float total = 0.0f;                             // rank order: the same sum on every GPU
+    for (int g = 0; g < xa.world; ++g) {
+      const unsigned long long p = partial_of(g);
+      const float pm = __uint_as_float(uint32_t(p)), ps = __uint_as_float(uint32_t(p >> 32));
+      if (pm != -INFINITY) total += ps * fast_exp2(fmaf(pm, kLog2e, -top2));
+    }
+    global_max[r] = top;
+    global_sum[r] = total;
+  });
+}
+
 __global__ void softmax_rebase_kernel(const float* row_max, const float* global_max, float* row_sum, int64_t rows) {
   const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   // the same 2^(m*log2e - M*log2e) form as the kernels on either side of the exchange
@@ -903,6 +1023,43 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
   return launch_apply_typed<T>(x, out, rows, width, row_max, row_sum, s);
 }
 
+template <typename T>
+int launch_argmax_exchange_typed(const void* logits_, int64_t rows, int64_t width, int64_t row_stride, int64_t index_base,
+                                 int32_t* out_ids, void* workspace, const ExchangeArgs& xa, cudaStream_t s) {
+  const T* logits = static_cast<const T*>(logits_);
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t target = int64_t(sm_count()) * 8;
+  int64_t chunks = target / rows;
+  const int64_t most = (width + kMinChunk - 1) / kMinChunk;
+  if (chunks > most) chunks = most;
+  if (chunks < 1) chunks = 1;
+  int64_t chunk = (width + chunks - 1) / chunks;
+  chunk = (chunk + 4 * N - 1) / (4 * N) * (4 * N);  // chunk starts stay 16-byte aligned
+  chunks = (width + chunk - 1) / chunk;
+  auto* keys = static_cast<unsigned long long*>(workspace);
+  auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
+  const unsigned grid = unsigned(rows * chunks);
+  if (rows_vector_ok<T>(logits, row_stride))
+    argmax_rows_exchange_kernel<T, true><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk, int(chunks),
+                                                                     index_base, out_ids, keys, tickets, xa);
+  else
+    argmax_rows_exchange_kernel<T, false><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk, int(chunks),
+                                                                      index_base, out_ids, keys, tickets, xa);
+  return launch_status("argmax_rows_sharded");
+}
+
+template <typename T>
+int launch_stats_exchange_typed(const void* x, int64_t rows, int64_t width, float* global_max, float* global_sum,
+                                const ExchangeArgs& xa, cudaStream_t s) {
+  if (rows_vector_ok<T>(x, width))
+    softmax_stats_exchange_kernel<T, true><<<unsigned(rows), kSoftThreads, 0, s>>>(static_cast<const T*>(x), rows, width,
+                                                                                  global_max, global_sum, xa);
+  else
+    softmax_stats_exchange_kernel<T, false><<<unsigned(rows), kSoftThreads, 0, s>>>(static_cast<const T*>(x), rows, width,
+                                                                                   global_max, global_sum, xa);
+  return launch_status("softmax_stats_sharded");
+}
+
 }  // namespace
 
 size_t argmax_workspace_bytes(int64_t rows) {
@@ -948,6 +1105,21 @@ int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, 
                          const float* row_sum, cudaStream_t s) {
   return dtype == B2_F32 ? launch_apply_typed<float>(x, out, rows, width, row_max, row_sum, s)
                          : launch_apply_typed<__half>(x, out, rows, width, row_max, row_sum, s);
+}
+
+int launch_argmax_exchange(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                           int64_t index_base, int32_t* out_ids, void* workspace, const ExchangeArgs& xa, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  return dtype == B2_F32
+             ? launch_argmax_exchange_typed<float>(logits, rows, width, row_stride, index_base, out_ids, workspace, xa, s)
+             : launch_argmax_exchange_typed<__half>(logits, rows, width, row_stride, index_base, out_ids, workspace, xa, s);
+}
+
+int launch_softmax_stats_exchange(const void* x, int64_t rows, int64_t width, int dtype, float* global_max,
+                                  float* global_sum, const ExchangeArgs& xa, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  return dtype == B2_F32 ? launch_stats_exchange_typed<float>(x, rows, width, global_max, global_sum, xa, s)
+                         : launch_stats_exchange_typed<__half>(x, rows, width, global_max, global_sum, xa, s);
 }
 
 }  // namespace b2

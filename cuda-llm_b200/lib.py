@@ -35,6 +35,15 @@ class AllocStats(C.Structure):
                                           "freed_bytes_total", "live_bytes", "peak_live_bytes")]
 
 
+P2P_MAX_WORLD = 16
+
+
+class P2PExchange(C.Structure):
+    """b2_p2p_exchange of include/b2ops.h."""
+    _fields_ = [("buffers", C.c_void_p * P2P_MAX_WORLD), ("world", C.c_int32), ("rank", C.c_int32),
+                ("max_rows", C.c_int64), ("timeout_ms", C.c_uint32)]
+
+
 def declared_symbols(header: str = HEADER):
     """Names of every B2_API function the header declares."""
     text = open(header).read()
@@ -67,6 +76,13 @@ _SIGNATURES = {
     "b2_softmax_stats": (_i, [_p, _i64, _i64, _i, _p, _p, _p]),
     "b2_softmax_rebase": (_i, [_p, _p, _p, _i64, _p]),
     "b2_softmax_apply": (_i, [_p, _p, _i64, _i64, _i, _p, _p, _p]),
+    "b2_p2p_exchange_bytes": (_sz, [_i, _i64]),
+    "b2_p2p_exchange_init": (_i, [_p, _i, _i64, _p]),
+    "b2_ipc_export": (_i, [_p, _p]),
+    "b2_ipc_open": (_i, [_p, C.POINTER(C.c_void_p)]),
+    "b2_ipc_close": (_i, [_p]),
+    "b2_argmax_rows_sharded": (_i, [_p, _i64, _i64, _i64, _i, _i64, _p, _p, _p, _p, _p]),
+    "b2_softmax_stats_sharded": (_i, [_p, _i64, _i64, _i, _p, _p, _p, _p, _p]),
     "b2_alloc": (_p, [_sz]),
     "b2_free": (_i, [_p]),
     "b2_get_alloc_stats": (None, [C.POINTER(AllocStats)]),

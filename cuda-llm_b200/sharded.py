@@ -128,3 +128,123 @@ def sharded_softmax(logits_shard: torch.Tensor, group=None, out: Optional[torch.
     _lib.check(L.b2_softmax_apply(logits_shard.data_ptr(), out.data_ptr(), rows, width, code, global_max.data_ptr(),
                                   global_sum.data_ptr(), _ops._stream()))
     return out
+
+
+# ---------------------------------------------------------------- exchange fused into the kernels
+
+class PeerExchange:
+    """Exchange buffers of a group of GPUs on one NVLink node, for the fused forms below.
+
+    Every rank allocates one buffer, exports it as a CUDA IPC handle, gathers the handles over the
+    process group (host side, once) and maps its peers' buffers.  After that a fused call is ONE kernel
+    launch per GPU: the reduction kernel's last thread block stores this GPU's per-row partials into
+    every peer's buffer through NVLink, publishes them with a release flag, waits (bounded by
+    `timeout_ms`) for the peers' flags and finishes the rows (include/b2ops.h, b2_p2p_exchange).
+    All ranks must make the same sequence of fused calls.  `status` is a device int32 that a kernel
+    ORs 2 into when its wait ran out (the results of that call are invalid; call reset() on every rank).
+    """
+
+    def __init__(self, max_rows: int, group=None, device=None, timeout_ms: int = 2000):
+        import ctypes as C
+        self._C = C
+        self.group = group
+        multi = dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
+        if self.world > _lib.P2P_MAX_WORLD:
+            raise ValueError(f"PeerExchange: at most {_lib.P2P_MAX_WORLD} ranks")
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.max_rows = int(max_rows)
+        L = _lib.load()
+        self._L = L
+        with torch.cuda.device(self.device):
+            size = L.b2_p2p_exchange_bytes(self.world, self.max_rows)
+            if size == 0:
+                raise ValueError("PeerExchange: max_rows out of range")
+            self.buffer = L.b2_alloc(size)
+            if not self.buffer:
+                _lib.check(-2)      # B2_ERR_CUDA, with the library's message
+            self._opened = []
+            self.reset(_barrier=False)
+            pointers = [None] * self.world
+            pointers[self.rank] = self.buffer
+            if multi:
+                handle = (C.c_ubyte * 64)()
+                _lib.check(L.b2_ipc_export(self.buffer, handle))
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle), group=group)
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        continue
+                    p = C.c_void_p()
+                    _lib.check(L.b2_ipc_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(p)))
+                    pointers[r] = p.value
+                    self._opened.append(p.value)
+                dist.barrier(group=group)      # every buffer is initialised and mapped before the first call
+        self.desc = _lib.P2PExchange()
+        for r, p in enumerate(pointers):
+            self.desc.buffers[r] = p
+        self.desc.world, self.desc.rank = self.world, self.rank
+        self.desc.max_rows, self.desc.timeout_ms = self.max_rows, int(timeout_ms)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def reset(self, _barrier: bool = True) -> None:
+        """Zero this rank's buffer (epochs, flags, slots).  After a timeout every rank calls this."""
+        torch.cuda.synchronize(self.device)
+        _lib.check(self._L.b2_p2p_exchange_init(self.buffer, self.world, self.max_rows, _ops._stream()))
+        torch.cuda.synchronize(self.device)
+        if _barrier and self.world > 1:
+            dist.barrier(group=self.group)
+
+    def timed_out(self) -> bool:
+        """Blocking read of the status word: True when some fused call's wait for its peers ran out."""
+        return bool(int(self.status.item()) & 2)
+
+    def close(self) -> None:
+        if getattr(self, "buffer", None):
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)     # nobody unmaps while a peer may still store into it
+            for p in self._opened:
+                self._L.b2_ipc_close(p)
+            self._opened = []
+            self._L.b2_free(self.buffer)
+            self.buffer = None
+
+
+def sharded_argmax_fused(logits_shard: torch.Tensor, index_base: int, exchange: PeerExchange,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sharded_argmax as ONE kernel per GPU (b2_argmax_rows_sharded): the keys cross NVLink as plain
+    stores from the reduction kernel itself; no collective library call, no second kernel."""
+    _ops._logits_req(logits_shard, "sharded_argmax_fused")
+    rows, width = logits_shard.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits_shard.device)
+    ws = _ops.argmax_workspace(logits_shard.device, rows)
+    import ctypes as C
+    _lib.check(_lib.load().b2_argmax_rows_sharded(logits_shard.data_ptr(), rows, width, width, _ops._code(logits_shard),
+                                                  index_base, out.data_ptr(), ws.data_ptr(), C.byref(exchange.desc),
+                                                  exchange.status.data_ptr(), _ops._stream()))
+    return out
+
+
+def sharded_softmax_fused(logits_shard: torch.Tensor, exchange: PeerExchange, out: Optional[torch.Tensor] = None,
+                          stats: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sharded_softmax as two kernels per GPU and no collective library call: the statistics kernel
+    exchanges (max, sum) pairs itself (b2_softmax_stats_sharded), then b2_softmax_apply scales this
+    rank's columns.  `stats`: optional float32 [2, rows] scratch."""
+    _ops._logits_req(logits_shard, "sharded_softmax_fused")
+    rows, width = logits_shard.shape
+    L = _lib.load()
+    if stats is None:
+        stats = torch.empty(2, rows, dtype=torch.float32, device=logits_shard.device)
+    if out is None:
+        out = torch.empty_like(logits_shard)
+    code = _ops._code(logits_shard)
+    import ctypes as C
+    _lib.check(L.b2_softmax_stats_sharded(logits_shard.data_ptr(), rows, width, code, stats[0].data_ptr(),
+                                          stats[1].data_ptr(), C.byref(exchange.desc), exchange.status.data_ptr(),
+                                          _ops._stream()))
+    _lib.check(L.b2_softmax_apply(logits_shard.data_ptr(), out.data_ptr(), rows, width, code, stats[0].data_ptr(),
+                                  stats[1].data_ptr(), _ops._stream()))
+    return out

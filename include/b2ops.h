@@ -219,6 +219,57 @@ B2_API int b2_softmax_rebase(const float* row_max, const float* global_max, floa
 B2_API int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype,
                             const float* row_max, const float* row_sum, b2_stream stream);
 
+/* ---- vocabulary-sharded reductions with the exchange fused into the kernel ------ */
+
+/* One process per GPU, all GPUs on one NVLink node.  Instead of reduce kernel -> collective
+ * library -> finishing kernel, the reduction kernel's last thread block stores this GPU's
+ * per-row partial results straight into every peer's exchange buffer (peer-mapped device
+ * memory), publishes them with a release flag, waits -- bounded -- for the peers' flags in
+ * its own buffer and finishes the row results there.  One launch per GPU and no host
+ * round trip.  No reference counterpart: the reference is single-GPU.
+ *
+ * Set-up, once per group of GPUs:
+ *   1. every process: buffer = b2_alloc(b2_p2p_exchange_bytes(world, max_rows));
+ *      b2_p2p_exchange_init(buffer, world, max_rows, stream)
+ *   2. b2_ipc_export(buffer, handle): 64 bytes to hand to the other processes by any host
+ *      channel (the Python side uses torch.distributed.all_gather_object)
+ *   3. b2_ipc_open(peer_handle, &peer_pointer) for every other rank; fill b2_p2p_exchange with
+ *      buffers[r] = rank r's buffer as addressable from THIS process (own pointer at [rank])
+ *   4. a host barrier, so that every buffer is initialised before the first call.
+ * Every rank must then make the same sequence of fused calls (they are collectives); calls
+ * on one buffer must not overlap on a GPU.  timeout_ms bounds the wait for the peers (0 means
+ * 2000): when it runs out the kernel still ends normally, ORs 2 into *status, and the results
+ * of that call are invalid; every rank then re-initialises its buffer before further use.
+ * Tear-down: b2_ipc_close(peer_pointer) for each opened handle, then b2_free(buffer). */
+#define B2_P2P_MAX_WORLD 16
+typedef struct {
+  void* buffers[B2_P2P_MAX_WORLD];
+  int32_t world, rank;
+  int64_t max_rows;
+  uint32_t timeout_ms;
+} b2_p2p_exchange;
+B2_API size_t b2_p2p_exchange_bytes(int world, int64_t max_rows);
+B2_API int b2_p2p_exchange_init(void* buffer, int world, int64_t max_rows, b2_stream stream);
+B2_API int b2_ipc_export(const void* device_ptr, unsigned char handle[64]);
+B2_API int b2_ipc_open(const unsigned char handle[64], void** device_ptr);
+B2_API int b2_ipc_close(void* device_ptr);
+
+/* Global row argmax of logits whose columns [index_base, index_base + width) live on this
+ * GPU: out_ids[r] on EVERY rank = index of the largest value of row r over all ranks' columns,
+ * ties to the lowest index (the rule of b2_argmax_rows).  workspace as for b2_argmax_rows;
+ * status: device int32 or NULL.  Replaces b2_argmax_keys + ncclAllReduce + b2_argmax_decode_keys. */
+B2_API int b2_argmax_rows_sharded(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                                  int64_t index_base, int32_t* out_ids, void* workspace,
+                                  const b2_p2p_exchange* exchange, int32_t* status, b2_stream stream);
+
+/* Row statistics of the WHOLE row from this GPU's columns: global_max[r] = max over all ranks,
+ * global_sum[r] = sum over all ranks of exp(x - global_max[r]); follow with
+ * b2_softmax_apply(x, out, rows, width, dtype, global_max, global_sum).
+ * Replaces b2_softmax_stats + two all-reduces + b2_softmax_rebase. */
+B2_API int b2_softmax_stats_sharded(const void* x, int64_t rows, int64_t width, int dtype, float* global_max,
+                                    float* global_sum, const b2_p2p_exchange* exchange, int32_t* status,
+                                    b2_stream stream);
+
 /* ---- device memory with the reference's allocation counters ----------------- */
 
 /* cudaMalloc / cudaFree plus the counters of the reference's CudaAllocationStats
