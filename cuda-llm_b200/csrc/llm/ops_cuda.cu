@@ -3,6 +3,7 @@
 // of its reference counterpart (src/ops_cuda.cu, lines cited per function) and throws the same
 // exception types; no arithmetic happens here.
 #include "llm/ops_cuda.h"
+#include "llm/ops_cuda_b200.h"
 #include "llm/cuda_check.h"
 #include "b2ops.h"
 

@@ -208,6 +208,47 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
         record("softmax (vocab-sharded + all-reduce MAX, SUM), eager launches", f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R,
                sharded_over=world)
         table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+        # the exchange fused into the reduction kernel: peer stores over NVLink, no collective call
+        ex = sharded.PeerExchange(max_rows=R)
+        try:
+            ids_f = torch.empty(R, dtype=torch.int32, device=dev)
+            stats_f = torch.empty(2, R, dtype=torch.float32, device=dev)
+            calls = [(lambda x=x: sharded.sharded_argmax_fused(x, c_lo, ex, out=ids_f)) for x in logits]
+            ms = timed(calls, nreps(40))
+            record("argmax (vocab-sharded, exchange fused into the kernel), eager launch", f"{R}x{VOCAB}/{world} f32",
+                   per_set + 4 * R, ms, R, sharded_over=world, note="one launch per GPU; keys cross NVLink as peer stores")
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            calls = [(lambda x=x, i=i: sharded.sharded_softmax_fused(x, ex, out=outs[i % len(outs)], stats=stats_f))
+                     for i, x in enumerate(logits)]
+            ms = timed(calls, nreps(40))
+            record("softmax (vocab-sharded, exchange fused into the statistics kernel), eager launches",
+                   f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            stream = torch.cuda.current_stream()
+            graphs_a, graphs_s = [], []
+            for i, x in enumerate(logits):
+                ga = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(ga, stream=stream):
+                    sharded.sharded_argmax_fused(x, c_lo, ex, out=ids_f)
+                graphs_a.append(ga)
+                gs = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gs, stream=stream):
+                    sharded.sharded_softmax_fused(x, ex, out=outs[i % len(outs)], stats=stats_f)
+                graphs_s.append(gs)
+            ms = timed([g.replay for g in graphs_a], nreps(40))
+            record("argmax (vocab-sharded, exchange fused into the kernel), CUDA-graph replay", f"{R}x{VOCAB}/{world} f32",
+                   per_set + 4 * R, ms, R, sharded_over=world)
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            ms = timed([g.replay for g in graphs_s], nreps(40))
+            record("softmax (vocab-sharded, exchange fused into the statistics kernel), CUDA-graph replay",
+                   f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            if ex.timed_out():
+                table.append({"op": "vocab-sharded reductions, fused exchange", "error": "a bounded wait for a peer ran out"})
+        except Exception as exc:
+            table.append({"op": "vocab-sharded reductions, fused exchange", "error": str(exc)[:200]})
+        finally:
+            ex.close()
         # the same calls recorded once into CUDA graphs (kernels + NCCL all-reduces) and replayed
         try:
             stream = torch.cuda.current_stream()

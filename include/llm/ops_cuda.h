@@ -18,22 +18,6 @@
 
 namespace llm {
 
-// Fast: parallel fp32 partial sums.  Deterministic: the summation order of the reference's
-// kernels (fp64 index-order sum for the RMSNorm family, fp32 index-order sum for softmax,
-// all-fp32 RoPE angles), for bit-level regressions.  Thread-local, set through the RAII guard,
-// in the idiom of the reference's CudaLinearModeGuard (:18-38).
-enum class CudaReductionMode { kFast, kDeterministic };
-class CudaReductionModeGuard {
- public:
-  explicit CudaReductionModeGuard(CudaReductionMode mode);
-  ~CudaReductionModeGuard();
-  CudaReductionModeGuard(const CudaReductionModeGuard&) = delete;
-  CudaReductionModeGuard& operator=(const CudaReductionModeGuard&) = delete;
- private:
-  CudaReductionMode previous_;
-};
-CudaReductionMode cuda_reduction_mode();
-
 // ---- allocating forms (:77-82)
 Tensor cuda_rms_norm(const Tensor& input, const Tensor& weight, float eps);
 Tensor cuda_add(const Tensor& lhs, const Tensor& rhs);
@@ -69,15 +53,7 @@ void cuda_embedding_lookup_device_ids_out(const Tensor& embedding_weight, const 
 int32_t cuda_argmax_last_row(const Tensor& logits_cuda);
 Tensor cuda_embedding_lookup(const Tensor& embedding_weight_cuda, const std::vector<int32_t>& token_ids);
 
-// ---- additions of this library (no reference counterpart)
-// Row-wise argmax of [R,V] logits into a CUDA/I32 [R] tensor, on `stream`, with no host round trip.
-// (The reference reaches rows other than the last only through CudaSampler::sample_row, one blocking
-// call per row, src/ops_cuda.cu:961-971.)
-void cuda_argmax_rows_out(const Tensor& logits_cuda, Tensor& ids_i32, cudaStream_t stream = 0);
-// Fused per-head RMSNorm + RoPE of q [T,Hq,D] and k [T,Hk,D] with one CUDA/I32 position per token:
-// one launch for the four the reference's layer makes (src/qwen3_layer_cuda.cu:289-292).
-void cuda_qk_norm_rope_out(const Tensor& q, const Tensor& k, const Tensor& q_weight, const Tensor& k_weight,
-                           const Tensor& positions_device, float eps, float theta, Tensor& q_out, Tensor& k_out,
-                           cudaStream_t stream = 0);
-
 }  // namespace llm
+
+// the additions of this library (reduction-mode switch, row-wise argmax, fused QK-norm + RoPE)
+#include "ops_cuda_b200.h"

@@ -26,7 +26,7 @@ F32, F16 = 0, 1  # dtype codes, the same as the product's C ABI
 
 def build(ref: bool = True) -> None:
     """Compile oracle.c (and the reference-backed library when its sources exist)."""
-    subprocess.run(["make", "-C", _HERE, "all"] + (["ref", "refcuda"] if ref else []), check=True,
+    subprocess.run(["make", "-C", _HERE, "all"] + (["ref", "refcuda", "layer"] if ref else []), check=True,
                    stdout=subprocess.DEVNULL)
 
 
@@ -397,3 +397,57 @@ def ref_cuda():
             _ref_cuda = None
     return _ref_cuda
 
+
+
+# ---------------------------------------------------------------------------------------------
+# The reference's own decoder-layer code, twice: with the reference's operators and with the in-scope
+# operators replaced by this repository's (oracle/Makefile, target `layer`).
+# ---------------------------------------------------------------------------------------------
+
+LAYER_NODES = ("input_norm", "q_linear", "k_linear", "v_linear", "q_norm_output", "k_norm_output", "q_rope", "k_rope",
+               "attention_output", "o_proj_output", "attention_residual", "post_attention_norm", "gate_proj_output",
+               "up_proj_output", "swiglu_output", "down_proj_output", "layer_output")
+LAYER_WEIGHTS = (("input_norm", (1024,)), ("q_proj", (2048, 1024)), ("k_proj", (1024, 1024)), ("v_proj", (1024, 1024)),
+                 ("q_norm", (128,)), ("k_norm", (128,)), ("o_proj", (1024, 2048)), ("post_attention_norm", (1024,)),
+                 ("gate_proj", (3072, 1024)), ("up_proj", (3072, 1024)), ("down_proj", (1024, 3072)))
+
+
+class LayerLib:
+    """qwen3_decoder_layer_cuda_trace / _trace_fp16 of the reference (src/qwen3_layer_cuda.cu:99-160) behind
+    oracle/layer_wrapper.cu.  `replaced` tells whether RMSNorm, RoPE, add and SwiGLU are this repository's."""
+
+    def __init__(self, path: str):
+        self.lib = C.CDLL(path)
+        self.lib.layer_trace.restype = C.c_int
+        self.lib.layer_select_reductions.restype = C.c_int
+        self.replaced = bool(self.lib.layer_select_reductions(0))
+
+    def select_reductions(self, deterministic: bool) -> None:
+        self.lib.layer_select_reductions(1 if deterministic else 0)
+
+    def trace(self, hidden: np.ndarray, positions, weights: dict, eps: float, theta: float, half: bool) -> dict:
+        seq = hidden.shape[0]
+        x = _f32(hidden)
+        pos = _i32(positions)
+        ws = [_f32(weights[name]).reshape(shape) for name, shape in LAYER_WEIGHTS]
+        wptr = (C.c_void_p * len(ws))(*[w.ctypes.data for w in ws])
+        shapes = {"input_norm": 1024, "q_linear": 2048, "k_linear": 1024, "v_linear": 1024, "q_norm_output": 2048,
+                  "k_norm_output": 1024, "q_rope": 2048, "k_rope": 1024, "attention_output": 2048, "o_proj_output": 1024,
+                  "attention_residual": 1024, "post_attention_norm": 1024, "gate_proj_output": 3072, "up_proj_output": 3072,
+                  "swiglu_output": 3072, "down_proj_output": 1024, "layer_output": 1024}
+        outs = {n: np.empty((seq, shapes[n]), np.float32) for n in LAYER_NODES}
+        optr = (C.c_void_p * len(LAYER_NODES))(*[outs[n].ctypes.data for n in LAYER_NODES])
+        err = C.create_string_buffer(512)
+        rc = self.lib.layer_trace(C.c_int(1 if half else 0), _ptr(x), C.c_int(seq), _ptr(pos), wptr, C.c_float(eps),
+                                  C.c_float(theta), optr, err, C.c_int(512))
+        if rc != 0:
+            raise RuntimeError(err.value.decode(errors="replace"))
+        return outs
+
+
+def layer_libs():
+    """(all-reference library, drop-in library), or None when they were not built."""
+    paths = [os.path.join(_HERE, "_ref", n) for n in ("liblayer_ref.so", "liblayer_dropin.so")]
+    if not all(os.path.exists(p) for p in paths):
+        return None
+    return LayerLib(paths[0]), LayerLib(paths[1])
