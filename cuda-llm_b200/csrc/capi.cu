@@ -6,6 +6,7 @@
 #include "exchange.cuh"
 #include "kernels.h"
 
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -266,6 +267,89 @@ int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int 
   B2_REQUIRE(rows >= 0 && width > 0 && fits(rows, width), op, "rows must be >= 0 and width > 0");
   B2_REQUIRE(rows == 0 || (x && out && row_max && row_sum), op, "null pointer");
   return launch_softmax_apply(x, out, rows, width, dtype, row_max, row_sum, as_stream(stream));
+}
+
+static int pool_checks(const char* op, const void* key, const void* value, const void* storage, const int32_t* table,
+                       const int32_t* positions, int64_t tokens, int64_t max_blocks, int64_t layer, int64_t layers,
+                       int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim, int dtype) {
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(tokens >= 0 && max_blocks > 0 && layers > 0 && total_blocks > 0 && block_size > 0 && kv_heads > 0 && head_dim > 0,
+             op, "sizes must be positive");
+  B2_REQUIRE(layer >= 0 && layer < layers, op, "layer out of range");
+  B2_REQUIRE(fits(kv_heads, head_dim) && fits(tokens, kv_heads * head_dim) && fits(layers * total_blocks * 2, block_size) &&
+                 fits(layers * total_blocks * 2 * block_size, kv_heads * head_dim),
+             op, "sizes out of range");
+  B2_REQUIRE(tokens == 0 || (key && value && storage && table && positions), op, "null pointer");
+  return B2_OK;
+}
+
+int b2_paged_kv_write_decode_batch(const void* key, const void* value, void* storage, const int32_t* block_tables,
+                                   const int32_t* positions, int64_t batch, int64_t max_blocks, int64_t layer, int64_t layers,
+                                   int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim, int dtype,
+                                   int32_t* status, b2_stream stream) {
+  const int rc = pool_checks("b2_paged_kv_write_decode_batch", key, value, storage, block_tables, positions, batch, max_blocks,
+                             layer, layers, total_blocks, block_size, kv_heads, head_dim, dtype);
+  if (rc != B2_OK) return rc;
+  return launch_paged_kv_write(0, key, value, storage, block_tables, positions, batch, max_blocks, layer, total_blocks,
+                               block_size, kv_heads * head_dim * (dtype == B2_F32 ? 4 : 2), status, as_stream(stream));
+}
+
+int b2_paged_kv_write_decode(const void* key, const void* value, void* storage, const int32_t* block_table,
+                             const int32_t* cache_length, int64_t max_blocks, int64_t layer, int64_t layers,
+                             int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim, int dtype,
+                             int32_t* status, b2_stream stream) {
+  const int rc = pool_checks("b2_paged_kv_write_decode", key, value, storage, block_table, cache_length, 1, max_blocks, layer,
+                             layers, total_blocks, block_size, kv_heads, head_dim, dtype);
+  if (rc != B2_OK) return rc;
+  return launch_paged_kv_write(2, key, value, storage, block_table, cache_length, 1, max_blocks, layer, total_blocks, block_size,
+                               kv_heads * head_dim * (dtype == B2_F32 ? 4 : 2), status, as_stream(stream));
+}
+
+int b2_paged_kv_prefill_copy(const void* key, const void* value, void* storage, const int32_t* block_table, int64_t tokens,
+                             int64_t max_blocks, int64_t layer, int64_t layers, int64_t total_blocks, int64_t block_size,
+                             int64_t kv_heads, int64_t head_dim, int dtype, int32_t* status, b2_stream stream) {
+  const int rc = pool_checks("b2_paged_kv_prefill_copy", key, value, storage, block_table, block_table, tokens, max_blocks, layer,
+                             layers, total_blocks, block_size, kv_heads, head_dim, dtype);
+  if (rc != B2_OK) return rc;
+  return launch_paged_kv_write(1, key, value, storage, block_table, nullptr, tokens, max_blocks, layer, total_blocks, block_size,
+                               kv_heads * head_dim * (dtype == B2_F32 ? 4 : 2), status, as_stream(stream));
+}
+
+int b2_select_last_valid_rows(const void* padded, const int32_t* valid_lengths, void* out, int64_t batch, int64_t seq,
+                              int64_t width, int dtype, int32_t* status, b2_stream stream) {
+  const char* op = "b2_select_last_valid_rows";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(batch >= 0 && seq > 0 && width > 0 && fits(batch, seq) && fits(batch * seq, width), op,
+             "batch must be >= 0, seq and width > 0");
+  B2_REQUIRE(batch == 0 || (padded && valid_lengths && out), op, "null pointer");
+  return launch_select_last_valid(padded, valid_lengths, out, batch, seq, width * (dtype == B2_F32 ? 4 : 2), status,
+                                  as_stream(stream));
+}
+
+size_t b2_sampler_workspace_bytes(int64_t rows, int64_t width) {
+  if (rows <= 0 || width <= 0 || width > 0x7fffffffll) return 0;
+  const size_t sampling = sampler_workspace_bytes(rows, width), greedy = argmax_workspace_bytes(rows);
+  return sampling > greedy ? sampling : greedy;
+}
+
+int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, float temperature,
+                   int32_t top_k, float top_p, uint64_t seed, const uint64_t* draw_offsets, int32_t* out_ids,
+                   void* workspace, b2_stream stream) {
+  const char* op = "b2_sample_rows";
+  const int rc = argmax_checks(op, logits, rows, width, row_stride, dtype, 0, out_ids, workspace);
+  if (rc != B2_OK) return rc;
+  B2_REQUIRE(width <= 0x7fffffffll, op, "width must fit int32");
+  B2_REQUIRE(std::isfinite(temperature) && temperature >= 0.0f, op, "temperature must be finite and >= 0");
+  if (rows == 0) return B2_OK;
+  if (temperature == 0.0f) {
+    // greedy: the argmax kernel, whose scratch must start zeroed
+    if (cudaMemsetAsync(workspace, 0, argmax_workspace_bytes(rows), as_stream(stream)) != cudaSuccess) return launch_status(op);
+    return launch_argmax(logits, rows, width, row_stride, dtype, 0, out_ids, nullptr, workspace, as_stream(stream));
+  }
+  B2_REQUIRE(top_k >= 0 && int64_t(top_k) <= width, op, "top_k must be in [0, width]");
+  B2_REQUIRE(std::isfinite(top_p) && top_p > 0.0f && top_p <= 1.0f, op, "top_p must be finite in (0, 1]");
+  return launch_sample_rows(logits, rows, width, row_stride, dtype, temperature, top_k, top_p, seed,
+                            reinterpret_cast<const unsigned long long*>(draw_offsets), out_ids, workspace, as_stream(stream));
 }
 
 size_t b2_p2p_exchange_bytes(int world, int64_t max_rows) {

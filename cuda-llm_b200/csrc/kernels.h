@@ -40,6 +40,18 @@ int launch_softmax_rebase(const float* row_max, const float* global_max, float* 
 int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
                          const float* row_sum, cudaStream_t s);
 
+// kvmove.cu: mode 0 = decode batch (one block table and one position per token), 1 = packed prefill (token t at
+// slot t of one block table), 2 = single decode (*positions is the cache length after the append)
+int launch_paged_kv_write(int mode, const void* key, const void* value, void* storage, const int32_t* block_tables,
+                          const int32_t* positions, int64_t tokens, int64_t max_blocks, int64_t layer, int64_t total_blocks,
+                          int64_t block_size, int64_t row_bytes, int32_t* status, cudaStream_t s);
+int launch_select_last_valid(const void* padded, const int32_t* valid_lengths, void* out, int64_t batch, int64_t seq,
+                             int64_t row_bytes, int32_t* status, cudaStream_t s);
+// sampler.cu
+size_t sampler_workspace_bytes(int64_t rows, int64_t width);
+int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, float temperature,
+                       int top_k, float top_p, unsigned long long seed, const unsigned long long* draw_offsets,
+                       int32_t* out_ids, void* workspace, cudaStream_t s);
 // vocab.cu, vocabulary-sharded forms with the inter-GPU exchange fused into the kernel (exchange.cuh)
 struct ExchangeArgs;
 int launch_argmax_exchange(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,

@@ -356,4 +356,74 @@ void cuda_argmax_rows_out(const Tensor& logits, Tensor& ids, cudaStream_t stream
   check(b2_argmax_rows(logits.data(), rows, width, width, dtype_code(logits), static_cast<int32_t*>(ids.data()), ws, stream));
 }
 
+// ---------------------------------------------------------------- sampler
+
+// reference src/ops_cuda.cu:886-890.  The workspace (keys, running sums, one result slot, one draw offset)
+// is a plain device allocation made once, like the reference's SamplerWorkspace buffers.
+CudaSampler::CudaSampler(size_t max_vocab) : max_vocab_(max_vocab) {
+  if (max_vocab == 0) throw std::invalid_argument("CudaSampler: max_vocab must be > 0");
+  const size_t bytes = b2_sampler_workspace_bytes(1, int64_t(max_vocab));
+  if (bytes == 0) throw std::invalid_argument("CudaSampler: max_vocab out of range");
+  CUDA_CHECK(cudaMalloc(&workspace_, bytes + 16));
+}
+CudaSampler::~CudaSampler() { cudaFree(workspace_); }
+
+// reference src/ops_cuda.cu:891-937
+int32_t CudaSampler::sample_row_offset(const Tensor& logits, size_t row_offset, const SamplingConfig& config,
+                                       uint64_t draw_offset) {
+  const char* op = "CudaSampler::sample_last_row";
+  if (logits.device() != DeviceType::CUDA || !logits.is_contiguous()) reject(op, "requires contiguous CUDA tensor");
+  if (logits.dtype() != DType::F32 && logits.dtype() != DType::F16) reject(op, "supports F32/F16 only");
+  if ((logits.shape().size() != 2 && logits.shape().size() != 3) || logits.shape().back() == 0)
+    reject(op, "requires non-empty rank-2 or rank-3 logits");
+  const size_t vocab = static_cast<size_t>(logits.shape().back());
+  if (vocab > max_vocab_) reject(op, "vocab exceeds sampler capacity");
+  if (!std::isfinite(config.temperature) || config.temperature < 0.0f) reject(op, "temperature must be finite and >= 0");
+  if (config.temperature != 0.0f) {
+    if (config.top_k < 0 || static_cast<size_t>(config.top_k) > vocab) reject(op, "top_k must be in [0,vocab]");
+    if (!std::isfinite(config.top_p) || config.top_p <= 0.0f || config.top_p > 1.0f) reject(op, "top_p must be finite in (0,1]");
+  }
+  const size_t bytes = b2_sampler_workspace_bytes(1, int64_t(max_vocab_));
+  char* tail = static_cast<char*>(workspace_) + bytes;                 // [0,8): the draw offset, [8,12): the result
+  uint64_t* offset_device = reinterpret_cast<uint64_t*>(tail);
+  int32_t* result_device = reinterpret_cast<int32_t*>(tail + 8);
+  CUDA_CHECK(cudaMemcpyAsync(offset_device, &draw_offset, sizeof(draw_offset), cudaMemcpyHostToDevice, 0));
+  const char* row = static_cast<const char*>(logits.data()) + row_offset * dtype_size(logits.dtype());
+  check(b2_sample_rows(row, 1, int64_t(vocab), int64_t(vocab), dtype_code(logits), config.temperature, config.top_k,
+                       config.temperature != 0.0f ? config.top_p : 1.0f, config.seed, offset_device, result_device,
+                       workspace_, 0));
+  int32_t host = 0;
+  CUDA_CHECK(cudaMemcpyAsync(&host, result_device, sizeof(host), cudaMemcpyDeviceToHost, 0));
+  CUDA_CHECK(cudaStreamSynchronize(0));
+  return host;
+}
+
+// reference src/ops_cuda.cu:938-944
+int32_t CudaSampler::sample_last_row(const Tensor& logits, const SamplingConfig& config, uint64_t draw_offset) {
+  if (logits.shape().size() != 2 || logits.shape()[0] == 0)
+    reject("CudaSampler::sample_last_row", "requires non-empty rank-2 logits");
+  return sample_row_offset(logits, (static_cast<size_t>(logits.shape()[0]) - 1) * static_cast<size_t>(logits.shape()[1]),
+                           config, draw_offset);
+}
+
+// reference src/ops_cuda.cu:945-960
+int32_t CudaSampler::sample_last_token_of_batch(const Tensor& logits, size_t batch_index, const SamplingConfig& config,
+                                                uint64_t draw_offset) {
+  const char* op = "CudaSampler::sample_last_token_of_batch";
+  if (logits.device() != DeviceType::CUDA || !logits.is_contiguous()) reject(op, "requires contiguous CUDA tensor");
+  if (logits.dtype() != DType::F32 && logits.dtype() != DType::F16) reject(op, "supports F32/F16 only");
+  if (logits.shape().size() != 3 || logits.numel() == 0) reject(op, "requires non-empty rank-3 logits");
+  if (batch_index >= static_cast<size_t>(logits.shape()[0])) throw std::out_of_range(std::string(op) + ": batch_index out of range");
+  const size_t seq = static_cast<size_t>(logits.shape()[1]), vocab = static_cast<size_t>(logits.shape()[2]);
+  return sample_row_offset(logits, (batch_index * seq + seq - 1) * vocab, config, draw_offset);
+}
+
+// reference src/ops_cuda.cu:961-971
+int32_t CudaSampler::sample_row(const Tensor& logits, size_t batch_index, const SamplingConfig& config, uint64_t draw_offset) {
+  const char* op = "CudaSampler::sample_row";
+  if (logits.shape().size() != 2 || logits.numel() == 0) reject(op, "requires non-empty rank-2 logits");
+  if (batch_index >= static_cast<size_t>(logits.shape()[0])) throw std::out_of_range(std::string(op) + ": batch_index out of range");
+  return sample_row_offset(logits, batch_index * static_cast<size_t>(logits.shape()[1]), config, draw_offset);
+}
+
 }  // namespace llm

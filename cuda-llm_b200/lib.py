@@ -76,6 +76,12 @@ _SIGNATURES = {
     "b2_softmax_stats": (_i, [_p, _i64, _i64, _i, _p, _p, _p]),
     "b2_softmax_rebase": (_i, [_p, _p, _p, _i64, _p]),
     "b2_softmax_apply": (_i, [_p, _p, _i64, _i64, _i, _p, _p, _p]),
+    "b2_paged_kv_write_decode_batch": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
+    "b2_paged_kv_write_decode": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
+    "b2_paged_kv_prefill_copy": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
+    "b2_select_last_valid_rows": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p, _p]),
+    "b2_sampler_workspace_bytes": (_sz, [_i64, _i64]),
+    "b2_sample_rows": (_i, [_p, _i64, _i64, _i64, _i, _f, C.c_int32, _f, C.c_uint64, _p, _p, _p, _p]),
     "b2_p2p_exchange_bytes": (_sz, [_i, _i64]),
     "b2_p2p_exchange_init": (_i, [_p, _i, _i64, _p]),
     "b2_ipc_export": (_i, [_p, _p]),

@@ -411,3 +411,184 @@ def cuda_softmax_last_dim(x, mode: Optional[str] = None):
     ws = softmax_workspace(x.device, rows)
     _lib.check(_lib.load().b2_softmax_rows(_ptr(x), _ptr(out), rows, width, _code(x), m, _ptr(ws), _stream()))
     return out
+
+
+# ---------------------------------------------------------------- sampling
+
+import dataclasses
+import math
+
+
+@dataclasses.dataclass
+class SamplingConfig:
+    """include/llm/ops_cuda.h:46-51."""
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+
+
+def sample_rows_out(logits, config: SamplingConfig, draw_offsets, out_ids, workspace=None) -> None:
+    """One token per row of [R,V] logits into int32[R] on the device, all rows in one call and no host
+    round trip (b2_sample_rows).  draw_offsets: CUDA int64 [R] (the bits are read as uint64), or None."""
+    op = "sample_rows"
+    _logits_req(logits, op)
+    rows, width = logits.shape
+    if not out_ids.is_cuda or out_ids.dtype != torch.int32 or tuple(out_ids.shape) != (rows,):
+        raise ValueError(f"{op}: output must be CUDA int32 [rows]")
+    if draw_offsets is not None and (not draw_offsets.is_cuda or draw_offsets.dtype != torch.int64
+                                     or tuple(draw_offsets.shape) != (rows,)):
+        raise ValueError(f"{op}: draw_offsets must be CUDA int64 [rows]")
+    L = _lib.load()
+    need = L.b2_sampler_workspace_bytes(rows, width)
+    if workspace is None:
+        key = (torch.device(logits.device).index, "sampler")
+        workspace = _workspaces.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=logits.device)
+            _workspaces[key] = workspace
+    elif workspace.numel() < need:
+        raise ValueError(f"{op}: workspace too small")
+    _lib.check(L.b2_sample_rows(_ptr(logits), rows, width, width, _code(logits), float(config.temperature),
+                                int(config.top_k), float(config.top_p), int(config.seed) & 0xFFFFFFFFFFFFFFFF,
+                                _ptr(draw_offsets), _ptr(out_ids), _ptr(workspace), _stream()))
+
+
+class CudaSampler:
+    """include/llm/ops_cuda.h:53-74: the reference's sampler interface, one token per blocking call,
+    with its argument rules (src/ops_cuda.cu:886-971)."""
+
+    def __init__(self, max_vocab: int):
+        if max_vocab <= 0:
+            raise ValueError("CudaSampler: max_vocab must be > 0")
+        self.max_vocab = int(max_vocab)
+
+    def _sample(self, row, config: SamplingConfig, draw_offset: int, op: str) -> int:
+        vocab = row.shape[-1]
+        if vocab > self.max_vocab:
+            raise ValueError(f"{op}: vocab exceeds sampler capacity")
+        if not math.isfinite(config.temperature) or config.temperature < 0:
+            raise ValueError(f"{op}: temperature must be finite and >= 0")
+        if config.temperature > 0:
+            if config.top_k < 0 or config.top_k > vocab:
+                raise ValueError(f"{op}: top_k must be in [0,vocab]")
+            if not math.isfinite(config.top_p) or config.top_p <= 0 or config.top_p > 1:
+                raise ValueError(f"{op}: top_p must be finite in (0,1]")
+        out = torch.empty(1, dtype=torch.int32, device=row.device)
+        offsets = torch.tensor([draw_offset & 0x7FFFFFFFFFFFFFFF if draw_offset < (1 << 63) else draw_offset - (1 << 64)],
+                               dtype=torch.int64, device=row.device)
+        sample_rows_out(row, config, offsets, out)
+        return int(out.item())
+
+    @staticmethod
+    def _check(logits, op, ranks):
+        if not isinstance(logits, torch.Tensor) or not logits.is_cuda or not logits.is_contiguous():
+            raise ValueError(f"{op}: requires contiguous CUDA tensor")
+        if logits.dtype not in (torch.float32, torch.float16):
+            raise ValueError(f"{op}: supports F32/F16 only")
+        if logits.dim() not in ranks or logits.numel() == 0:
+            raise ValueError(f"{op}: requires non-empty rank-{'/'.join(map(str, ranks))} logits")
+
+    def sample_last_row(self, logits, config: SamplingConfig, draw_offset: int) -> int:
+        op = "CudaSampler::sample_last_row"
+        self._check(logits, op, (2,))
+        return self._sample(logits[-1:], config, draw_offset, op)
+
+    def sample_row(self, logits_bv, batch_index: int, config: SamplingConfig, draw_offset: int) -> int:
+        op = "CudaSampler::sample_row"
+        self._check(logits_bv, op, (2,))
+        if not 0 <= batch_index < logits_bv.shape[0]:
+            raise IndexError(f"{op}: batch_index out of range")
+        return self._sample(logits_bv[batch_index:batch_index + 1], config, draw_offset, op)
+
+    def sample_last_token_of_batch(self, logits_bsv, batch_index: int, config: SamplingConfig, draw_offset: int) -> int:
+        op = "CudaSampler::sample_last_token_of_batch"
+        self._check(logits_bsv, op, (3,))
+        if not 0 <= batch_index < logits_bsv.shape[0]:
+            raise IndexError(f"{op}: batch_index out of range")
+        return self._sample(logits_bsv[batch_index, -1:], config, draw_offset, op)
+
+
+# ---------------------------------------------------------------- paged KV cache writes, last-valid-row gather
+
+def _pool_args(storage, key, value, op):
+    for t in (storage, key, value):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{op}: requires contiguous CUDA tensors")
+    if storage.dim() != 6 or storage.shape[2] != 2:
+        raise ValueError(f"{op}: storage must be [layers, total_blocks, 2, block_size, kv_heads, head_dim]")
+    if key.dtype != storage.dtype or value.dtype != storage.dtype or key.dtype not in (torch.float16, torch.float32):
+        raise ValueError(f"{op}: key, value and storage must share one dtype, F16 or F32")
+    if key.shape != value.shape or key.dim() != 3 or tuple(key.shape[1:]) != tuple(storage.shape[4:]):
+        raise ValueError(f"{op}: key/value must be [tokens, kv_heads, head_dim] of the pool")
+    return tuple(int(d) for d in storage.shape)
+
+
+def _i32_device(t, shape, op, what):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.int32 or not t.is_contiguous() \
+            or (shape is not None and tuple(t.shape) != tuple(shape)):
+        raise ValueError(f"{op}: {what} must be CUDA/I32/contiguous" + (f" {list(shape)}" if shape else ""))
+
+
+def paged_kv_write_decode_batch(key_bhd, value_bhd, storage, layer: int, block_tables_bm, positions_b, status=None) -> None:
+    """cuda_paged_kv_write_decode_batch (include/llm/ops_cuda.h:183-186) on the pool's storage tensor."""
+    op = "paged_kv_write_decode_batch"
+    layers, total_blocks, _, block_size, kv_heads, head_dim = _pool_args(storage, key_bhd, value_bhd, op)
+    batch = key_bhd.shape[0]
+    if block_tables_bm.dim() != 2:
+        raise ValueError(f"{op}: block tables must be CUDA/I32/contiguous [B,max_blocks]")
+    _i32_device(block_tables_bm, (batch, block_tables_bm.shape[1]), op, "block tables")
+    _i32_device(positions_b, (batch,), op, "positions")
+    if not 0 <= layer < layers:
+        raise ValueError(f"{op}: invalid KV cache dimensions")
+    _lib.check(_lib.load().b2_paged_kv_write_decode_batch(_ptr(key_bhd), _ptr(value_bhd), _ptr(storage), _ptr(block_tables_bm),
+                                                          _ptr(positions_b), batch, block_tables_bm.shape[1], layer, layers,
+                                                          total_blocks, block_size, kv_heads, head_dim, _code(key_bhd),
+                                                          _ptr(status), _stream()))
+
+
+def paged_kv_write_decode(key_hd, value_hd, storage, layer: int, block_table, cache_length, status=None) -> None:
+    """cuda_paged_kv_write_decode (include/llm/ops_cuda.h:178-182): one token at position *cache_length - 1."""
+    op = "paged_kv_write_decode"
+    layers, total_blocks, _, block_size, kv_heads, head_dim = _pool_args(storage, key_hd[None], value_hd[None], op)
+    _i32_device(block_table, None, op, "device block table")
+    _i32_device(cache_length, (1,), op, "device cache length")
+    if block_table.dim() != 1 or block_table.numel() == 0 or not 0 <= layer < layers:
+        raise ValueError(f"{op}: invalid block table or layer")
+    _lib.check(_lib.load().b2_paged_kv_write_decode(_ptr(key_hd), _ptr(value_hd), _ptr(storage), _ptr(block_table),
+                                                    _ptr(cache_length), block_table.numel(), layer, layers, total_blocks,
+                                                    block_size, kv_heads, head_dim, _code(key_hd), _ptr(status), _stream()))
+
+
+def paged_kv_prefill_copy_packed(key_thd, value_thd, storage, block_table, layer: int, status=None) -> None:
+    """cuda_paged_kv_prefill_copy_packed (reference src/ops_cuda.cu:1123-1160): token t to slot t of one block table."""
+    op = "paged_kv_prefill_copy_packed"
+    layers, total_blocks, _, block_size, kv_heads, head_dim = _pool_args(storage, key_thd, value_thd, op)
+    tokens = key_thd.shape[0]
+    _i32_device(block_table, None, op, "block table")
+    if tokens == 0 or block_table.numel() < (tokens + block_size - 1) // block_size or not 0 <= layer < layers:
+        raise ValueError(f"{op}: invalid CUDA/F16 packed KV or pool metadata")
+    _lib.check(_lib.load().b2_paged_kv_prefill_copy(_ptr(key_thd), _ptr(value_thd), _ptr(storage), _ptr(block_table), tokens,
+                                                    block_table.numel(), layer, layers, total_blocks, block_size, kv_heads,
+                                                    head_dim, _code(key_thd), _ptr(status), _stream()))
+
+
+def select_last_valid_logits(padded_logits, valid_lengths: Sequence[int]):
+    """select_last_valid_logits (include/llm/qwen3_padded_prefill.h:43; src/qwen3_padded_prefill.cpp:118-148), CUDA
+    branch: [B,S,V] -> [B,V], the row of each prompt's last real token, in one launch."""
+    op = "select_last_valid_logits"
+    if not isinstance(padded_logits, torch.Tensor) or not padded_logits.is_cuda or not padded_logits.is_contiguous() \
+            or padded_logits.dim() != 3:
+        raise ValueError(f"{op}: padded logits must be contiguous rank-3 [B,S,V]")
+    if padded_logits.dtype not in (torch.float32, torch.float16):
+        raise ValueError(f"{op}: supports only F32/F16")
+    batch, seq, vocab = padded_logits.shape
+    if batch == 0 or seq == 0 or vocab == 0 or len(valid_lengths) != batch:
+        raise ValueError(f"{op}: invalid padded logits shape or valid_lengths size")
+    if any(n <= 0 or n > seq for n in valid_lengths):
+        raise ValueError(f"{op}: valid length is outside padded logits sequence")
+    lengths = torch.tensor(list(valid_lengths), dtype=torch.int32).to(padded_logits.device, non_blocking=True)
+    out = torch.empty(batch, vocab, dtype=padded_logits.dtype, device=padded_logits.device)
+    _lib.check(_lib.load().b2_select_last_valid_rows(_ptr(padded_logits), _ptr(lengths), _ptr(out), batch, seq, vocab,
+                                                     _code(padded_logits), None, _stream()))
+    return out

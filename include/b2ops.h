@@ -219,6 +219,63 @@ B2_API int b2_softmax_rebase(const float* row_max, const float* global_max, floa
 B2_API int b2_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype,
                             const float* row_max, const float* row_sum, b2_stream stream);
 
+/* ---- row moves around the paged KV cache and the padded-prefill logits ------------- */
+
+/* The KV pool is the reference's PagedKvCachePool storage: [layers, total_blocks, 2, block_size,
+ * kv_heads, head_dim], plane 0 = keys, plane 1 = values (include/llm/paged_kv_cache_pool.h).
+ * key, value: [tokens, kv_heads, head_dim]; every token's key row and value row are copied, bit for
+ * bit, to the slot its position selects through a block table:
+ *   b2_paged_kv_write_decode_batch  token b -> position positions[b] of block_tables[b, 0..max_blocks)
+ *   b2_paged_kv_write_decode        the one token -> position *cache_length - 1 of block_table
+ *                                   (nothing is written when *cache_length == 0)
+ *   b2_paged_kv_prefill_copy        token t -> position t of block_table
+ * A block id outside [0, total_blocks), a negative position or one past the table never reaches
+ * memory: that row is skipped and bit 0 of *status (device int32, may be NULL) is raised.
+ * Replace cuda_paged_kv_write_decode_batch / cuda_paged_kv_write_decode (include/llm/ops_cuda.h:178-186;
+ * src/paged_attention_cuda.cu:219-262,639-716) and cuda_paged_kv_prefill_copy_packed
+ * (src/ops_cuda.cu:1104-1160), after their checks of the pool object. */
+B2_API int b2_paged_kv_write_decode_batch(const void* key, const void* value, void* storage,
+                                          const int32_t* block_tables, const int32_t* positions, int64_t batch,
+                                          int64_t max_blocks, int64_t layer, int64_t layers, int64_t total_blocks,
+                                          int64_t block_size, int64_t kv_heads, int64_t head_dim, int dtype,
+                                          int32_t* status, b2_stream stream);
+B2_API int b2_paged_kv_write_decode(const void* key, const void* value, void* storage, const int32_t* block_table,
+                                    const int32_t* cache_length, int64_t max_blocks, int64_t layer, int64_t layers,
+                                    int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim,
+                                    int dtype, int32_t* status, b2_stream stream);
+B2_API int b2_paged_kv_prefill_copy(const void* key, const void* value, void* storage, const int32_t* block_table,
+                                    int64_t tokens, int64_t max_blocks, int64_t layer, int64_t layers,
+                                    int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim,
+                                    int dtype, int32_t* status, b2_stream stream);
+
+/* out[b, :] = padded[b, valid_lengths[b] - 1, :] for padded [batch, seq, width]: the logits of each
+ * prompt's last real token, gathered in one launch.  valid_lengths: device int32[batch]; a length outside
+ * [1, seq] zero-fills that row and raises bit 0 of *status (device int32, may be NULL).
+ * Replaces the CUDA branch of select_last_valid_logits (src/qwen3_padded_prefill.cpp:118-148: one blocking
+ * device-to-device copy per prompt), after its host-side checks. */
+B2_API int b2_select_last_valid_rows(const void* padded, const int32_t* valid_lengths, void* out, int64_t batch,
+                                     int64_t seq, int64_t width, int dtype, int32_t* status, b2_stream stream);
+
+/* ---- temperature / top-k / top-p sampling ------------------------------------------ */
+
+/* One token per row of logits [rows, width] (rows `row_stride` elements apart), chosen exactly as the
+ * reference's CudaSampler chooses it: scores = logits / temperature; tokens ordered by score descending,
+ * equal scores by ascending id; the first top_k of them (all when top_k == 0); of those the shortest
+ * prefix whose softmax mass reaches top_p (all when top_p == 1); then one draw u(seed, draw_offsets[r]) in
+ * (0,1) picks by cumulative mass.  Sums are fp32 and added in that order, so the token is the reference's
+ * bit for bit.  temperature == 0 is the row argmax (top_k, top_p and the draw are ignored).
+ * temperature must be finite and >= 0; with temperature > 0: 0 <= top_k <= width and 0 < top_p <= 1.
+ * draw_offsets: device uint64[rows], or NULL for offset 0 on every row.
+ * workspace: b2_sampler_workspace_bytes(rows, width) bytes of scratch, no initialisation needed; calls
+ * that share it must not overlap on the device.
+ * Replaces CudaSampler::sample_row / sample_last_row / sample_last_token_of_batch, kernels sampler_fill and
+ * sampler_select and the library sort between them (include/llm/ops_cuda.h:46-74;
+ * src/ops_cuda.cu:575-617,886-971), which handle one row per blocking call. */
+B2_API size_t b2_sampler_workspace_bytes(int64_t rows, int64_t width);
+B2_API int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
+                          float temperature, int32_t top_k, float top_p, uint64_t seed, const uint64_t* draw_offsets,
+                          int32_t* out_ids, void* workspace, b2_stream stream);
+
 /* ---- vocabulary-sharded reductions with the exchange fused into the kernel ------ */
 
 /* One process per GPU, all GPUs on one NVLink node.  Instead of reduce kernel -> collective

@@ -18,6 +18,32 @@
 
 namespace llm {
 
+// ---- sampling (:46-74).  temperature == 0 is greedy; otherwise scores = logits / temperature, the top_k
+// highest (all when 0), of those the shortest prefix with softmax mass >= top_p, one seeded draw.  Every
+// call returns one token to the host (blocking), like the reference; the token is the reference's.
+struct SamplingConfig {
+  float temperature = 0.0f;
+  int32_t top_k = 0;
+  float top_p = 1.0f;
+  uint64_t seed = 0;
+};
+
+class CudaSampler {
+ public:
+  explicit CudaSampler(size_t max_vocab);
+  ~CudaSampler();
+  CudaSampler(const CudaSampler&) = delete;
+  CudaSampler& operator=(const CudaSampler&) = delete;
+  int32_t sample_last_row(const Tensor& logits_cuda, const SamplingConfig& config, uint64_t draw_offset);
+  int32_t sample_row(const Tensor& logits_bv, size_t batch_index, const SamplingConfig& config, uint64_t draw_offset);
+  int32_t sample_last_token_of_batch(const Tensor& logits_bsv, size_t batch_index, const SamplingConfig& config,
+                                     uint64_t draw_offset);
+ private:
+  int32_t sample_row_offset(const Tensor& logits, size_t row_offset, const SamplingConfig& config, uint64_t draw_offset);
+  void* workspace_ = nullptr;   // device scratch for one row of max_vocab_ logits, allocated once
+  size_t max_vocab_ = 0;
+};
+
 // ---- allocating forms (:77-82)
 Tensor cuda_rms_norm(const Tensor& input, const Tensor& weight, float eps);
 Tensor cuda_add(const Tensor& lhs, const Tensor& rhs);

@@ -152,6 +152,35 @@ class Port:
                 out[r] = self.lib.orc_argmax_row_f32(_ptr(row), C.c_int64(w))
         return out
 
+    def sample_row(self, logits_row, temperature, top_k, top_p, seed, offset):
+        """(token id, decision margin) of the reference's sampling rule for one row of float32 logits."""
+        row = _f32(logits_row).ravel()
+        self.lib.orc_sample_row.restype = C.c_int32
+        margin = C.c_double(0)
+        token = self.lib.orc_sample_row(_ptr(row), C.c_int64(row.size), C.c_float(temperature), C.c_int32(top_k),
+                                        C.c_float(top_p), C.c_uint64(seed), C.c_uint64(offset), C.byref(margin))
+        return int(token), float(margin.value)
+
+    def paged_kv_write(self, mode, key, value, storage, block_tables, positions, layer, total_blocks, block_size):
+        """In-place on `storage` [layers, total_blocks, 2, block_size, kv_heads, head_dim] (any 2- or 4-byte dtype)."""
+        key, value = np.ascontiguousarray(key), np.ascontiguousarray(value)
+        tables, pos = _i32(block_tables), _i32(positions)
+        tokens, kv_heads, head_dim = key.shape
+        max_blocks = tables.shape[-1]
+        assert storage.flags["C_CONTIGUOUS"] and storage.dtype == key.dtype
+        self.lib.orc_paged_kv_write(C.c_int(mode), _ptr(key), _ptr(value), _ptr(storage), _ptr(tables), _ptr(pos),
+                                    C.c_int64(tokens), C.c_int64(max_blocks), C.c_int64(layer), C.c_int64(total_blocks),
+                                    C.c_int64(block_size), C.c_int64(kv_heads), C.c_int64(head_dim), C.c_int64(key.itemsize))
+
+    def select_last_valid(self, padded, valid_lengths):
+        padded = np.ascontiguousarray(padded)
+        batch, seq, width = padded.shape
+        out = np.empty((batch, width), padded.dtype)
+        lengths = _i32(valid_lengths)
+        self.lib.orc_select_last_valid(_ptr(padded), _ptr(lengths), _ptr(out), C.c_int64(batch), C.c_int64(seq),
+                                       C.c_int64(width * padded.itemsize))
+        return out
+
     def argmax_key(self, value: float, index: int) -> int:
         return int(self.lib.orc_argmax_key(C.c_float(value), C.c_int64(index)))
 
@@ -305,7 +334,7 @@ class RefCuda:
     def __init__(self, path: str):
         self.lib = L = C.CDLL(path)
         for name in ("refcu_time_add_rms_norm", "refcu_time_rms_norm", "refcu_time_binary", "refcu_time_rope_token_positions",
-                     "refcu_time_embedding", "refcu_time_softmax", "refcu_time_argmax_last_row"):
+                     "refcu_time_embedding", "refcu_time_softmax", "refcu_time_argmax_last_row", "refcu_time_sample_row"):
             getattr(L, name).restype = C.c_float
 
     @staticmethod
@@ -353,6 +382,18 @@ class RefCuda:
         self._ok(self.lib.refcu_argmax_last_row(self._p(logits), C.c_int64(rows), C.c_int64(width), C.c_int(dtype), C.byref(r)),
                  "argmax_last_row")
         return int(r.value)
+
+    def sample_row(self, logits, rows, vocab, dtype, row, temperature, top_k, top_p, seed, draw_offset) -> int:
+        """CudaSampler::sample_row of the reference: one token, one blocking call."""
+        r = C.c_int32(-1)
+        self._ok(self.lib.refcu_sample_row(self._p(logits), C.c_int64(rows), C.c_int64(vocab), C.c_int(dtype), C.c_int64(row),
+                                           C.c_float(temperature), C.c_int32(top_k), C.c_float(top_p), C.c_uint64(seed),
+                                           C.c_uint64(draw_offset), C.byref(r)), "sample_row")
+        return int(r.value)
+
+    def time_sample_row(self, logits, rows, vocab, dtype, temperature, top_k, top_p, reps):
+        return float(self.lib.refcu_time_sample_row(self._p(logits), C.c_int64(rows), C.c_int64(vocab), C.c_int(dtype),
+                                                    C.c_float(temperature), C.c_int32(top_k), C.c_float(top_p), C.c_int(reps)))
 
     # timings: milliseconds per call of the reference operator on device-resident tensors
     def time_add_rms_norm(self, lhs, rhs, w, rows, hidden, eps, dtype, reps):

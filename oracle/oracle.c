@@ -22,6 +22,7 @@
  * against the reference's own compiled ops_cpu.
  */
 #include <math.h>
+#include <stdlib.h>
 #include <stdint.h>
 #include <string.h>
 #include <float.h>
@@ -293,4 +294,101 @@ ORC_API void orc_cpu_add_rms_norm(const float* lhs, const float* rhs, const floa
                                   int64_t rows, int64_t hidden, float* residual, float* normalized) {
   orc_cpu_add(lhs, rhs, rows * hidden, residual);
   orc_cpu_rms_norm(residual, w, eps, rows, hidden, normalized);
+}
+
+/* Temperature / top-k / top-p sampling of one row, following the reference's CudaSampler
+ * (src/ops_cuda.cu:575-617: sampler_fill, a stable descending sort of the scores, sampler_select;
+ * hash and uniform draw :581-586,606-608).  The reference has no CPU sampler; this restates its
+ * device algorithm with libm's expf, so a decision that hangs on the last bits of a running sum can
+ * differ from the device.  `margin` (may be NULL) receives the smallest relative gap of any
+ * comparison that decided the result: when it is well above 1e-6 the token is unambiguous. */
+typedef struct { uint32_t ordered; int32_t id; float score; } orc_sample_item;
+static int orc_sample_cmp(const void* a, const void* b) {
+  const orc_sample_item* x = (const orc_sample_item*)a;
+  const orc_sample_item* y = (const orc_sample_item*)b;
+  if (x->ordered != y->ordered) return x->ordered > y->ordered ? -1 : 1;   /* higher score first */
+  return x->id < y->id ? -1 : (x->id > y->id ? 1 : 0);                      /* stable: lower id first */
+}
+static uint64_t orc_sample_mix(uint64_t x) {
+  x += 0x9e3779b97f4a7c15ULL;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ULL;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebULL;
+  return x ^ (x >> 31);
+}
+ORC_API int32_t orc_sample_row(const float* logits, int64_t n, float temperature, int32_t top_k, float top_p, uint64_t seed,
+                               uint64_t offset, double* margin) {
+  orc_sample_item* items = (orc_sample_item*)malloc((size_t)n * sizeof(orc_sample_item));
+  double gap = 1.0;
+  for (int64_t i = 0; i < n; ++i) {
+    const float s = logits[i] / temperature;
+    uint32_t b;
+    memcpy(&b, &s, 4);
+    items[i].ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);   /* the order of a radix sort on floats */
+    items[i].id = (int32_t)i;
+    items[i].score = s;
+  }
+  qsort(items, (size_t)n, sizeof(orc_sample_item), orc_sample_cmp);
+  const int64_t limit = top_k == 0 ? n : (top_k < n ? top_k : n);
+  const float maximum = items[0].score;
+  float total = 0.0f;
+  for (int64_t i = 0; i < limit; ++i) total += expf(items[i].score - maximum);
+  int64_t prefix = limit;
+  if (top_p < 1.0f) {
+    float cumulative = 0.0f;
+    for (int64_t i = 0; i < limit; ++i) {
+      cumulative += expf(items[i].score - maximum) / total;
+      const double g = fabs((double)cumulative - (double)top_p);
+      if (g < gap) gap = g;
+      if (cumulative >= top_p) { prefix = i + 1; break; }
+    }
+  }
+  float prefix_total = 0.0f;
+  for (int64_t i = 0; i < prefix; ++i) prefix_total += expf(items[i].score - maximum);
+  const uint64_t bits = orc_sample_mix(seed ^ (offset * 0xd1342543de82ef95ULL));
+  const float u = ((float)((bits >> 11) & 0x1fffffffffffffULL) + 0.5f) / 9007199254740992.0f;
+  const float target = u * prefix_total;
+  float cumulative = 0.0f;
+  int32_t selected = items[prefix - 1].id;
+  for (int64_t i = 0; i < prefix; ++i) {
+    cumulative += expf(items[i].score - maximum);
+    const double g = fabs((double)target - (double)cumulative) / (double)prefix_total;
+    if (g < gap) gap = g;
+    if (target < cumulative) { selected = items[i].id; break; }
+  }
+  if (margin) *margin = gap;
+  free(items);
+  return selected;
+}
+
+/* Row moves around the paged KV cache: the index arithmetic of paged_kv_write_decode_batch_kernel
+ * (src/paged_attention_cuda.cu:241-262), paged_kv_write_decode_kernel (:219-239) and
+ * packed_kv_prefill_copy_kernel (src/ops_cuda.cu:1104-1121), element by element as the reference
+ * writes it, on byte-sized elements of `esize` bytes.  mode 0: batch decode, 1: packed prefill,
+ * 2: single decode with *positions = cache length. */
+ORC_API void orc_paged_kv_write(int mode, const unsigned char* key, const unsigned char* value, unsigned char* storage,
+                                const int32_t* block_tables, const int32_t* positions, int64_t tokens, int64_t max_blocks,
+                                int64_t layer, int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim,
+                                int64_t esize) {
+  const int64_t per_row = kv_heads * head_dim, plane_elements = block_size * per_row;
+  for (int64_t t = 0; t < tokens; ++t) {
+    int64_t token;
+    const int32_t* table;
+    if (mode == 0) { token = (int64_t)positions[t] + 1 - 1; table = block_tables + t * max_blocks; }
+    else if (mode == 1) { token = t; table = block_tables; }
+    else { if (positions[0] == 0) return; token = (int64_t)positions[0] - 1; table = block_tables; }
+    const int64_t block = table[token / block_size], offset = token % block_size;
+    const int64_t layer_block = (layer * total_blocks + block) * 2;
+    for (int64_t e = 0; e < per_row; ++e) {
+      memcpy(storage + (layer_block * plane_elements + offset * per_row + e) * esize, key + (t * per_row + e) * esize, (size_t)esize);
+      memcpy(storage + ((layer_block + 1) * plane_elements + offset * per_row + e) * esize, value + (t * per_row + e) * esize,
+             (size_t)esize);
+    }
+  }
+}
+
+/* select_last_valid_logits (src/qwen3_padded_prefill.cpp:118-148): row valid_lengths[b] - 1 of every prompt. */
+ORC_API void orc_select_last_valid(const unsigned char* padded, const int32_t* valid_lengths, unsigned char* out, int64_t batch,
+                                   int64_t seq, int64_t row_bytes) {
+  for (int64_t b = 0; b < batch; ++b)
+    memcpy(out + b * row_bytes, padded + (b * seq + (int64_t)valid_lengths[b] - 1) * row_bytes, (size_t)row_bytes);
 }

@@ -186,3 +186,39 @@ REFCU_API float refcu_time_argmax_last_row(const void* logits, int64_t rows, int
   });
   return ms;
 }
+
+// ---- the reference's CudaSampler (include/llm/ops_cuda.h:53-74): one token per call, blocking
+REFCU_API int refcu_sample_row(const void* logits, int64_t rows, int64_t vocab, int dtype, int64_t row, float temperature,
+                               int32_t top_k, float top_p, uint64_t seed, uint64_t draw_offset, int32_t* result) {
+  return guarded([&] {
+    static llm::CudaSampler* sampler = nullptr;     // one workspace for the process, sized for the largest vocabulary seen
+    static size_t capacity = 0;
+    if (sampler == nullptr || size_t(vocab) > capacity) {
+      delete sampler;
+      capacity = size_t(vocab) < 151936 ? 151936 : size_t(vocab);
+      sampler = new llm::CudaSampler(capacity);
+    }
+    llm::SamplingConfig config;
+    config.temperature = temperature;
+    config.top_k = top_k;
+    config.top_p = top_p;
+    config.seed = seed;
+    *result = sampler->sample_row(from_device(logits, dtype_of(dtype), {rows, vocab}), size_t(row), config, draw_offset);
+  });
+}
+
+// milliseconds per sampled row (the reference samples one row per blocking call)
+REFCU_API float refcu_time_sample_row(const void* logits, int64_t rows, int64_t vocab, int dtype, float temperature, int32_t top_k,
+                                      float top_p, int reps) {
+  try {
+    llm::CudaSampler sampler{static_cast<size_t>(vocab)};
+    llm::SamplingConfig config;
+    config.temperature = temperature;
+    config.top_k = top_k;
+    config.top_p = top_p;
+    config.seed = 1;
+    Tensor t = from_device(logits, dtype_of(dtype), {rows, vocab});
+    uint64_t draw = 0;
+    return timed([&] { sampler.sample_row(t, size_t(draw % uint64_t(rows)), config, draw); ++draw; }, reps);
+  } catch (const std::exception&) { return -1.0f; }
+}

@@ -44,3 +44,8 @@ def test_tensor_host_program():
 def test_ops_cuda_program():
     out = _run(_build("test_ops_cuda_b200"))
     assert "test_ops_cuda_b200 passed" in out and "bit-exact" in out
+
+
+@pytest.mark.gpu
+def test_sampling_program():
+    assert "test_sampling_b200 passed" in _run(_build("test_sampling_b200"))
