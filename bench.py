@@ -227,6 +227,18 @@ def reference_gpu_kernels(L, lib, dev, stream):
     sws, sout = ops.softmax_workspace(dev, R), torch.empty_like(logits)
     row(f"softmax {R}x{vocab} f32", ref.time_softmax(logits, R, vocab, 0, 1),
         ours(lambda: lib.check(L.b2_softmax_rows(logits.data_ptr(), sout.data_ptr(), R, vocab, lib.F32, lib.FAST, sws.data_ptr(), s))))
+    # sampling: the reference draws one token per blocking call; ours draws all rows in one call
+    sampler_ws = torch.empty(L.b2_sampler_workspace_bytes(R, vocab), dtype=torch.uint8, device=dev)
+    offs = torch.arange(R, dtype=torch.int64, device=dev)
+    for label, temp, top_k, top_p, ref_reps in (("top_k=50 top_p=0.95", 0.8, 50, 0.95, 3), ("top_k=0 top_p=0.9", 1.0, 0, 0.9, 2)):
+        per_row = ref.time_sample_row(logits, R, vocab, 0, temp, top_k, top_p, ref_reps)
+        if per_row < 0:
+            continue
+        row(f"sample {R} rows x {vocab} f32, {label}", R * per_row,
+            ours(lambda: lib.check(L.b2_sample_rows(logits.data_ptr(), R, vocab, vocab, lib.F32, temp, top_k, top_p, 7,
+                                                    offs.data_ptr(), ids_out.data_ptr(), sampler_ws.data_ptr(), s)), reps=3),
+            note="reference: one blocking CudaSampler::sample_row call per row (full-vocabulary sort + single-thread scans), "
+                 "timed per row x 256")
     return out
 
 

@@ -101,7 +101,61 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
         _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, nreps)
     if want("argmax") or want("softmax"):
         _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table)
+    if world == 1 and (want("sampler") or want("kvmove")):
+        _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
     return table
+
+
+def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
+    """The callers either side of the path: sampling over the LM-head logits, paged-KV row writes, last-valid-row gather."""
+    F16, F32 = lib.F16, lib.F32
+    if want("sampler"):
+        R = 256
+        logits = [randn(R, VOCAB, sigma=4.0, dtype=torch.float32) for _ in range(2)]
+        ids = torch.empty(R, dtype=torch.int32, device=dev)
+        offs = torch.arange(R, dtype=torch.int64, device=dev)
+        ws = torch.empty(L.b2_sampler_workspace_bytes(R, VOCAB), dtype=torch.uint8, device=dev)
+        for label, temp, top_k, top_p in (("top_k=50 top_p=0.95 (radix select)", 0.8, 50, 0.95),
+                                          ("top_k=0 top_p=0.9 (whole-vocabulary sort)", 1.0, 0, 0.9)):
+            calls = [(lambda x=x: lib.check(L.b2_sample_rows(x.data_ptr(), R, VOCAB, VOCAB, F32, temp, top_k, top_p, 7,
+                                                             offs.data_ptr(), ids.data_ptr(), ws.data_ptr(), s))) for x in logits]
+            ms = timed(calls, nreps(6), warm=2)
+            record(f"sample_rows {label}", f"{R}x{VOCAB} f32", R * VOCAB * 4 + 12 * R, ms, R,
+                   note="bytes = the logits read once; the ordered fp32 sums (one thread per row) set the time, not HBM")
+        del logits, ws
+    if want("kvmove"):
+        half = torch.float16
+        layers, block_size, kv_heads, head_dim = 2, 16, 8, 128
+        row_bytes = kv_heads * head_dim * 2
+        T = 16384
+        total_blocks = T // block_size + 8
+        storage = torch.zeros(layers, total_blocks, 2, block_size, kv_heads, head_dim, device=dev, dtype=half)
+        table = torch.randperm(total_blocks, device=dev)[: T // block_size].to(torch.int32)
+        sets = [(randn(T, kv_heads, head_dim), randn(T, kv_heads, head_dim)) for _ in range(4)]
+        calls = [(lambda b=b: lib.check(L.b2_paged_kv_prefill_copy(b[0].data_ptr(), b[1].data_ptr(), storage.data_ptr(),
+                                                                   table.data_ptr(), T, table.numel(), 1, layers, total_blocks,
+                                                                   block_size, kv_heads, head_dim, F16, None, s))) for b in sets]
+        ms = timed(calls, nreps(40))
+        record("paged_kv_prefill_copy", f"T={T}, {kv_heads} heads x {head_dim} f16", 4 * T * row_bytes + 4 * table.numel(), ms, T)
+        B = 256
+        tables = torch.randperm(total_blocks, device=dev)[:B * 4].reshape(B, 4).to(torch.int32).contiguous()
+        pos = torch.randint(0, 4 * block_size, (B,), device=dev, dtype=torch.int32)
+        k1, v1 = randn(B, kv_heads, head_dim), randn(B, kv_heads, head_dim)
+        calls = [lambda: lib.check(L.b2_paged_kv_write_decode_batch(k1.data_ptr(), v1.data_ptr(), storage.data_ptr(),
+                                                                    tables.data_ptr(), pos.data_ptr(), B, 4, 0, layers,
+                                                                    total_blocks, block_size, kv_heads, head_dim, F16, None, s))]
+        ms = timed(calls, nreps(100))
+        record("paged_kv_write_decode_batch", f"B={B}, {kv_heads} heads x {head_dim} f16", 4 * B * row_bytes + 20 * B, ms, B,
+               note="latency-bound: 2 MB moved")
+        del storage, sets
+        Bp, S = 64, 16
+        padded = [randn(Bp, S, VOCAB, dtype=torch.float32) for _ in range(2)]
+        lengths = torch.randint(1, S + 1, (Bp,), device=dev, dtype=torch.int32)
+        out = torch.empty(Bp, VOCAB, device=dev)
+        calls = [(lambda x=x: lib.check(L.b2_select_last_valid_rows(x.data_ptr(), lengths.data_ptr(), out.data_ptr(), Bp, S, VOCAB,
+                                                                    F32, None, s))) for x in padded]
+        ms = timed(calls, nreps(40))
+        record("select_last_valid_rows", f"[{Bp},{S},{VOCAB}] f32 -> [{Bp},{VOCAB}]", 2 * Bp * VOCAB * 4 + 4 * Bp, ms, Bp)
 
 
 def _headline_shape_ops(L, lib, dev, s, timed, record, randn, nreps):
