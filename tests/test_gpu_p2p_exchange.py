@@ -149,10 +149,12 @@ def test_world_of_one_through_the_python_drivers(b2, port):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_processes_two_gpus(b2):
-    """Two ranks over NVLink peer mappings: fused results equal the NCCL-exchange results and the oracle's."""
+def test_one_process_per_gpu_over_nvlink(b2):
+    """One rank per GPU of the box (2, 4 or 8) over NVLink peer mappings: fused results equal the NCCL-exchange
+    results and the oracle's, call after call."""
+    ranks = 8 if torch.cuda.device_count() >= 8 else 4 if torch.cuda.device_count() >= 4 else 2
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT + os.pathsep + os.path.join(ROOT, "tests"))
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr", "127.0.0.1",
            "--master-port", "29641", os.path.join(ROOT, "tests", "p2p_exchange_worker.py")]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
