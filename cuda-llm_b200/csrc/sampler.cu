@@ -9,10 +9,11 @@
 // What changes is how the order and the sums are produced:
 //   keys     one 64-bit key per token, (order-preserving bits of the score) << 32 | ~index, so one
 //            unsigned sort gives the reference's order including its tie rule
-//   sort     when 0 < top_k <= 2048 only the k largest keys matter: a radix select over the L2-resident
-//            keys finds the k-th largest key, a compaction gathers the survivors and one thread block
-//            sorts them in shared memory; otherwise a bitonic network sorts the whole row (4096-key
-//            tiles in shared memory, wider steps in global memory), all rows at once
+//   sort     when 0 < top_k <= 2048 only the k largest keys matter: one pass over the logits histograms
+//            the top bits of the scores, a second pass gathers the few hundred tokens at or above the bin
+//            that holds the k-th largest, and one thread block sorts those in shared memory (rows with too
+//            many near-equal scores fall back to a radix select over all 64 key bits); otherwise a bitonic
+//            network sorts the whole row (4096-key tiles in shared memory, wider steps in global memory)
 //   select   one thread block per row: the exponentials of a 2048-token chunk are computed in
 //            parallel, one thread adds them in order (the only serial part left) and records the
 //            running sums; the top-p cut walks the same way and stops at the crossing; the final pick
@@ -47,7 +48,8 @@ __device__ __forceinline__ int32_t key_index(unsigned long long key) { return in
 template <typename T>
 __global__ void __launch_bounds__(256)
 sampler_keys_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature,
-                    unsigned long long* keys) {
+                    unsigned long long* keys, const int* only_if) {
+  if (only_if != nullptr && *only_if == 0) return;   // a stage of the exact fallback that this call does not need
   const int64_t row = blockIdx.y;
   const T* src = logits + row * row_stride;
   unsigned long long* dst = keys + row * padded;
@@ -112,7 +114,8 @@ struct SelectState {                 // per row, in the workspace
   unsigned int taken;                // compaction cursor
 };
 
-__global__ void select_init_kernel(SelectState* state, int64_t rows, unsigned int k) {
+__global__ void select_init_kernel(SelectState* state, int64_t rows, unsigned int k, const int* only_if) {
+  if (only_if != nullptr && *only_if == 0) return;
   const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (r < rows) { state[r].prefix = 0ull; state[r].remaining = k; state[r].taken = 0u; }
 }
@@ -120,8 +123,10 @@ __global__ void select_init_kernel(SelectState* state, int64_t rows, unsigned in
 // Histogram of one digit over the keys whose higher digits equal the prefix found so far.
 __global__ void __launch_bounds__(256)
 select_histogram_kernel(const unsigned long long* keys, int64_t width, int64_t padded, int shift, int bits,
-                        unsigned long long mask_above, const SelectState* state, unsigned int* histograms) {
+                        unsigned long long mask_above, const SelectState* state, unsigned int* histograms,
+                        const int* only_if) {
   __shared__ unsigned int local[kSelectBins];
+  if (only_if != nullptr && *only_if == 0) return;
   const int64_t row = blockIdx.y;
   const int bins = 1 << bits;
   for (int b = threadIdx.x; b < bins; b += blockDim.x) local[b] = 0u;
@@ -141,8 +146,9 @@ select_histogram_kernel(const unsigned long long* keys, int64_t width, int64_t p
 // Walks the histogram from the top bin down until the wanted count is covered: fixes the next digit of the
 // prefix, updates what is still wanted from inside that bin, and clears the histogram for the next round.
 __global__ void __launch_bounds__(256)
-select_scan_kernel(int shift, int bits, SelectState* state, unsigned int* histograms) {
+select_scan_kernel(int shift, int bits, SelectState* state, unsigned int* histograms, const int* only_if) {
   __shared__ unsigned int counts[kSelectBins];
+  if (only_if != nullptr && *only_if == 0) return;
   const int64_t row = blockIdx.x;
   const int bins = 1 << bits;
   unsigned int* hist = histograms + row * kSelectBins;
@@ -163,7 +169,8 @@ select_scan_kernel(int shift, int bits, SelectState* state, unsigned int* histog
 // After the last round state.prefix IS the k-th largest key: gather every key >= it (exactly k of them).
 __global__ void __launch_bounds__(256)
 select_compact_kernel(const unsigned long long* keys, int64_t width, int64_t padded, SelectState* state,
-                      unsigned long long* survivors) {
+                      unsigned long long* survivors, const int* only_if) {
+  if (only_if != nullptr && *only_if == 0) return;
   const int64_t row = blockIdx.y;
   const unsigned long long* src = keys + row * padded;
   const unsigned long long cut = state[row].prefix;
@@ -179,13 +186,142 @@ select_compact_kernel(const unsigned long long* keys, int64_t width, int64_t pad
 
 // Sorts one row's survivors in shared memory, descending, into the front of the row's key area.
 __global__ void __launch_bounds__(kSortThreads)
-select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const unsigned long long* survivors) {
+select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const unsigned long long* survivors,
+                     const int* only_if) {
   __shared__ unsigned long long buf[kMaxSelectK];
+  if (only_if != nullptr && *only_if == 0) return;
   const int64_t row = blockIdx.x;
   const unsigned long long* in = survivors + row * int64_t(kMaxSelectK);
   int n = 1;
   while (n < top_k) n <<= 1;
   for (int i = threadIdx.x; i < n; i += kSortThreads) buf[i] = i < top_k ? in[i] : 0ull;
+  __syncthreads();
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int p = threadIdx.x; p < n / 2; p += kSortThreads) {
+        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+        compare_exchange(buf[i], buf[i | j], (i & k) == 0);
+      }
+      __syncthreads();
+    }
+  }
+  unsigned long long* dst = keys + row * padded;
+  for (int i = threadIdx.x; i < top_k; i += kSortThreads) dst[i] = buf[i];
+}
+
+// ---- small top_k, the usual case: two passes over the LOGITS and no key array at all.
+//   pass 1  histogram of the top 11 bits of every token's order-preserving score bits
+//   cut     the highest bin b with (tokens in bins >= b) >= top_k
+//   pass 2  the keys of all tokens in bins >= b are gathered (a few hundred for a vocabulary of 150k)
+//   finish  one thread block sorts the candidates and keeps the top_k largest
+// Exact whenever the candidates fit kCandidates; a row whose cut bin is too crowded (long runs of equal or
+// nearly equal scores) raises a flag, and the radix select over all 64 key bits above then redoes the
+// call (every stage of it is launched in any case and returns at once when the flag is down).
+constexpr int kCandidates = 4096;
+
+struct CutState {            // per row
+  unsigned int cut_bin;      // candidates are the tokens whose bin is >= this
+  unsigned int taken;        // compaction cursor
+};
+
+__device__ __forceinline__ unsigned int score_bin(float score) {
+  const uint32_t b = __float_as_uint(score);
+  return ((b & 0x80000000u) ? ~b : (b | 0x80000000u)) >> 21;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+topk_histogram_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, unsigned int* histograms) {
+  __shared__ unsigned int local[kSelectBins];
+  const int64_t row = blockIdx.y;
+  for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x) local[b] = 0u;
+  __syncthreads();
+  const T* src = logits + row * row_stride;
+  const int lane = threadIdx.x & 31;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
+    const unsigned int bin = score_bin(__fdiv_rn(Elem<T>::load(src + i), temperature));
+    // scores crowd into a few dozen bins: lanes with the same bin add once, through their lowest lane
+    const unsigned int same = __match_any_sync(__activemask(), bin);
+    if (lane == __ffs(int(same)) - 1) atomicAdd(&local[bin], unsigned(__popc(same)));
+  }
+  __syncthreads();
+  unsigned int* out = histograms + row * kSelectBins;
+  for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x)
+    if (local[b] != 0u) atomicAdd(&out[b], local[b]);
+}
+
+// one thread block per row: suffix counts from the top bin down, 8 bins per thread
+__global__ void __launch_bounds__(256)
+topk_cut_kernel(unsigned int top_k, CutState* cut, unsigned int* histograms) {
+  __shared__ unsigned int counts[kSelectBins];
+  __shared__ unsigned int group_sum[256], above_group[256];
+  const int64_t row = blockIdx.x;
+  unsigned int* hist = histograms + row * kSelectBins;
+  const int t = threadIdx.x;
+  for (int b = t; b < kSelectBins; b += 256) { counts[b] = hist[b]; hist[b] = 0u; }   // left cleared for the next user
+  __syncthreads();
+  unsigned int sum = 0;
+  for (int b = 0; b < 8; ++b) sum += counts[t * 8 + b];
+  group_sum[t] = sum;
+  // above_group[t] = tokens in the groups above t: suffix sums inside each warp by shuffles, then the warps above
+  unsigned int suffix = sum;                       // inclusive, over lanes >= this one
+  const int lane = t & 31, warp = t >> 5;
+#pragma unroll
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const unsigned int other = __shfl_down_sync(0xffffffffu, suffix, offset);
+    if (lane + offset < 32) suffix += other;
+  }
+  __shared__ unsigned int warp_total[8];
+  if (lane == 0) warp_total[warp] = suffix;
+  __syncthreads();
+  unsigned int higher = 0;
+  for (int w = warp + 1; w < 8; ++w) higher += warp_total[w];
+  above_group[t] = higher + suffix - sum;
+  __syncthreads();
+  // exactly one thread owns the bin where the count from the top first reaches top_k
+  unsigned int above = above_group[t];
+  if (above < top_k && above + group_sum[t] >= top_k) {
+    for (int b = 7; b >= 0; --b) {
+      above += counts[t * 8 + b];
+      if (above >= top_k) { cut[row].cut_bin = unsigned(t * 8 + b); break; }
+    }
+  }
+  if (t == 0) cut[row].taken = 0u;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, CutState* cut,
+                   unsigned long long* candidates) {
+  const int64_t row = blockIdx.y;
+  const T* src = logits + row * row_stride;
+  const unsigned int cut_bin = cut[row].cut_bin;
+  unsigned long long* out = candidates + row * int64_t(kCandidates);
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
+    const float score = __fdiv_rn(Elem<T>::load(src + i), temperature);
+    if (score_bin(score) >= cut_bin) {
+      const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
+      if (slot < unsigned(kCandidates)) out[slot] = sample_key(score, uint32_t(i));
+    }
+  }
+}
+
+// Sorts one row's candidates in shared memory, descending, and leaves the top_k largest at the front of the
+// row's key area; more candidates than fit raise *overflow (the exact fallback then overwrites every row).
+__global__ void __launch_bounds__(kSortThreads)
+topk_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const CutState* cut,
+                   const unsigned long long* candidates, int* overflow) {
+  __shared__ unsigned long long buf[kCandidates];
+  const int64_t row = blockIdx.x;
+  const unsigned int count = cut[row].taken;
+  if (count > unsigned(kCandidates)) {
+    if (threadIdx.x == 0) atomicExch(overflow, 1);
+    return;
+  }
+  const unsigned long long* in = candidates + row * int64_t(kCandidates);
+  int n = 2;
+  while (n < int(count)) n <<= 1;
+  for (int i = threadIdx.x; i < n; i += kSortThreads) buf[i] = unsigned(i) < count ? in[i] : 0ull;
   __syncthreads();
   for (int k = 2; k <= n; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
@@ -288,12 +424,13 @@ int64_t padded_width(int64_t width) {
 
 }  // namespace
 
-// per row: padded keys (8 B each), padded running sums (4 B each), the survivors of the top-k select,
-// a histogram and a select state
+// per row: padded keys (8 B each), padded running sums (4 B each), the candidates / survivors of the top-k
+// paths, a histogram and the two small state records; one flag for the whole call
 size_t sampler_workspace_bytes(int64_t rows, int64_t width) {
   const int64_t padded = padded_width(width);
-  const size_t per_row = size_t(padded) * 12 + size_t(kMaxSelectK) * 8 + size_t(kSelectBins) * 4 + sizeof(SelectState);
-  return (size_t(rows) * per_row + 255) / 256 * 256;
+  const size_t per_row = size_t(padded) * 12 + size_t(kCandidates) * 8 + size_t(kSelectBins) * 4 + sizeof(SelectState) +
+                         sizeof(CutState);
+  return (size_t(rows) * per_row + 16 + 255) / 256 * 256;
 }
 
 int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, float temperature,
@@ -302,41 +439,70 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
   if (rows == 0) return B2_OK;
   const int64_t padded = padded_width(width);
   auto* keys = static_cast<unsigned long long*>(workspace);
-  auto* survivors = keys + rows * padded;
-  auto* state = reinterpret_cast<SelectState*>(survivors + rows * int64_t(kMaxSelectK));
+  auto* candidates = keys + rows * padded;                                   // kCandidates per row (>= kMaxSelectK)
+  auto* state = reinterpret_cast<SelectState*>(candidates + rows * int64_t(kCandidates));
   auto* running = reinterpret_cast<float*>(state + rows);
   auto* histograms = reinterpret_cast<unsigned int*>(running + rows * padded);
+  auto* cut = reinterpret_cast<CutState*>(histograms + rows * int64_t(kSelectBins));
+  int* overflow = reinterpret_cast<int*>(cut + rows);
 
-  const unsigned spread = unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256));
+  // thread blocks per row for the passes over a row: enough to fill the GPU over all rows and no more (each block
+  // of the histogram passes clears and flushes a 2048-bin histogram, and an unneeded stage of the fallback should
+  // cost one short wave of empty blocks)
+  int64_t spread64 = (int64_t(sm_count()) * 8 + rows - 1) / rows;
+  if (spread64 > padded / 1024) spread64 = padded / 1024;
+  if (spread64 < 1) spread64 = 1;
+  const unsigned spread = unsigned(spread64);
   const dim3 row_grid(spread, unsigned(rows));
-  if (dtype == B2_F32)
-    sampler_keys_kernel<float><<<row_grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
-                                                       temperature, keys);
-  else
-    sampler_keys_kernel<__half><<<row_grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
-                                                        temperature, keys);
+  // the whole-row sort has no empty stages and little per-block overhead: more, smaller blocks
+  const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), unsigned(rows));
+  auto make_keys = [&](const int* only_if) {
+    const dim3 grid = only_if != nullptr ? row_grid : wide_grid;
+    if (dtype == B2_F32)
+      sampler_keys_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
+                                                         temperature, keys, only_if);
+    else
+      sampler_keys_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
+                                                      temperature, keys, only_if);
+  };
 
   if (top_k > 0 && top_k <= kMaxSelectK && width > kTile) {
-    // only the k largest keys matter: find the k-th largest, gather the survivors, sort those
-    if (cudaMemsetAsync(histograms, 0, size_t(rows) * kSelectBins * 4, s) != cudaSuccess) return launch_status("sample_rows");
-    select_init_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(state, rows, unsigned(top_k));
+    // only the k largest keys matter.  Two passes over the logits find them ...
+    if (cudaMemsetAsync(histograms, 0, size_t(rows) * (size_t(kSelectBins) * 4 + sizeof(CutState)) + 16, s) != cudaSuccess)
+      return launch_status("sample_rows");
+    if (dtype == B2_F32) {
+      const float* x = static_cast<const float*>(logits);
+      topk_histogram_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, histograms);
+      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), cut, histograms);
+      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
+    } else {
+      const __half* x = static_cast<const __half*>(logits);
+      topk_histogram_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, histograms);
+      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), cut, histograms);
+      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
+    }
+    topk_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, cut, candidates, overflow);
+    // ... unless a row's cut bin was too crowded: then (and only then) the radix select over all 64 key bits runs
+    make_keys(overflow);
+    select_init_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(state, rows, unsigned(top_k), overflow);
     const int shifts[kSelectRounds] = {53, 42, 31, 20, 9, 0}, widths[kSelectRounds] = {11, 11, 11, 11, 11, 9};
     unsigned long long mask_above = 0ull;
     for (int round = 0; round < kSelectRounds; ++round) {
       select_histogram_kernel<<<row_grid, 256, 0, s>>>(keys, width, padded, shifts[round], widths[round], mask_above, state,
-                                                      histograms);
-      select_scan_kernel<<<unsigned(rows), 256, 0, s>>>(shifts[round], widths[round], state, histograms);
+                                                      histograms, overflow);
+      select_scan_kernel<<<unsigned(rows), 256, 0, s>>>(shifts[round], widths[round], state, histograms, overflow);
       mask_above |= ((1ull << widths[round]) - 1ull) << shifts[round];
     }
-    select_compact_kernel<<<row_grid, 256, 0, s>>>(keys, width, padded, state, survivors);
-    select_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, survivors);
+    select_compact_kernel<<<row_grid, 256, 0, s>>>(keys, width, padded, state, candidates, overflow);
+    select_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, candidates, overflow);
   } else {
+    make_keys(nullptr);
     const int tile = int(padded < kTile ? padded : kTile);
     const dim3 tile_grid(unsigned(padded / tile), unsigned(rows));
     const size_t smem = size_t(tile) * 8;
     bitonic_tile_kernel<<<tile_grid, kSortThreads, smem, s>>>(keys, padded, tile, 2, tile);
     for (int64_t k = int64_t(tile) * 2; k <= padded; k <<= 1) {
-      for (int64_t j = k >> 1; j >= tile; j >>= 1) bitonic_wide_kernel<<<row_grid, 256, 0, s>>>(keys, padded, k, j);
+      for (int64_t j = k >> 1; j >= tile; j >>= 1) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);
       bitonic_tile_kernel<<<tile_grid, kSortThreads, smem, s>>>(keys, padded, tile, k, k);
     }
   }

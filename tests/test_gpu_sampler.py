@@ -67,22 +67,30 @@ CONFIGS = [SamplingConfig(1.0, 0, 1.0, 11), SamplingConfig(0.7, 50, 1.0, 12), Sa
            SamplingConfig(1.0, 1, 1.0, 17), SamplingConfig(0.5, 0, 0.3, 18)]
 
 
-def rows_for(width, rows, seed, dtype):
+def rows_for(width, rows, seed, dtype, kind="ties"):
     rng = np.random.default_rng(seed)
     x = wl.normal(rng, (rows, width), 4.0)
-    x[1, : width // 2] = x[1, 0]                # a long run of equal scores: the tie rule decides
-    x[2, :] = 0.0                               # every score equal
-    if width > 100:
-        x[3, 7], x[3, 99] = 30.0, 30.0          # two equal maxima
+    if kind == "ties":
+        x[1, : width // 2] = x[1, 0]                # a long run of equal scores: the tie rule decides
+        x[2, :] = 0.0                               # every score equal
+        if width > 100:
+            x[3, 7], x[3, 99] = 30.0, 30.0          # two equal maxima
+    elif kind == "narrow":
+        x = 16.0 + rng.random((rows, width), dtype=np.float32)   # every score in one binade: the coarse cut cannot separate them
     return x.astype(dtype)
 
 
-@pytest.mark.parametrize("width,dtype", [(6, np.float32), (1000, np.float32), (4096, np.float16), (5000, np.float32),
-                                         (151936, np.float32), (151936, np.float16)])
-def test_every_row_equals_the_references_own_sampler_and_the_restatement(b2, port, width, dtype):
+@pytest.mark.parametrize("width,dtype,kind", [(6, np.float32, "ties"), (1000, np.float32, "ties"), (4096, np.float16, "ties"),
+                                              (5000, np.float32, "ties"), (151936, np.float32, "ties"),
+                                              (151936, np.float16, "ties"), (151936, np.float32, "plain"),
+                                              (151936, np.float16, "plain"), (40000, np.float32, "plain"),
+                                              (151936, np.float32, "narrow")])
+def test_every_row_equals_the_references_own_sampler_and_the_restatement(b2, port, width, dtype, kind):
+    """"plain" rows take the two-pass top-k path alone; "ties" and "narrow" rows crowd the cut bin and send the
+    call through the exact radix select; top_k == 0 and top_k > 2048 sort the whole row."""
     refcu = oracle.ref_cuda()
     rows = 8
-    x = rows_for(width, rows, width, dtype)
+    x = rows_for(width, rows, width, dtype, kind)
     t = dev(x)
     xf = x.astype(np.float32)
     out = torch.empty(rows, dtype=torch.int32, device=DEV)
