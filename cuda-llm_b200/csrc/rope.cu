@@ -390,7 +390,8 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
       ang.neg_s[e] = make_float2(-ang.s[e].x, -ang.s[e].y);
     }
 
-    if (!mbarrier_wait_bounded(&bars[stage], round & 1u)) {
+    // the whole warp takes one decision (a lane whose wait succeeded at the last moment must not part from the rest)
+    if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(&bars[stage], round & 1u))) {
       // never expected: record it, give every stage's copy one more bounded chance to land, and stop
       if (lane == 0) atomicAdd(&g_rope_bulk_timeouts, 1u);
       for (int i = 0; i < stages && t + i * stride < tokens; ++i) {   // copies in flight: tokens t .. t_ahead

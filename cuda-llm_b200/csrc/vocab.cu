@@ -522,7 +522,10 @@ softmax_cluster_stream_kernel(const T* x, T* out, int64_t rows, int64_t width, i
   bool healthy = true;
   for (int it = 0; row < rows; ++it, row += clusters) {
     const int par = it & 1;
-    if (bytes != 0u && !mbarrier_wait_bounded(&stage_barrier, uint32_t(par))) { healthy = false; break; }
+    // A wait that runs out (never expected) makes this thread stop waiting for anything: it finishes the loop on
+    // whatever is in memory, in step with the others (every barrier and shuffle below is still reached by all),
+    // and the status word says that this call's outputs are invalid.
+    if (healthy && bytes != 0u && !mbarrier_wait_bounded(&stage_barrier, uint32_t(par))) healthy = false;
     uint4 raw[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) {
@@ -562,29 +565,28 @@ softmax_cluster_stream_kernel(const T* x, T* out, int64_t rows, int64_t width, i
 
     const int64_t next = row + clusters;
     if (tid == 0 && next < rows) {
-      if (bytes != 0u) { fence_before_bulk_copy(); request(next); }
+      if (bytes != 0u && healthy) { fence_before_bulk_copy(); request(next); }
       // the next row's statistics: that barrier's previous phase was consumed by every thread before the
       // __syncthreads above
       mbarrier_expect_bytes(&stats_barrier[par ^ 1], ranks * 8u);
     }
+    // Every warp folds the warps' statistics, one per lane, with shuffle trees (fixed order: the same bits in
+    // every warp); a serial walk by a few threads would sit on the critical path of the whole cluster.
+    const float2 mine = lane < kWarps ? warp_stats[par][lane] : make_float2(-INFINITY, 0.0f);
+    const float slice_m = warp_max(mine.x);
+    const float slice_s =
+        warp_sum(mine.x == -INFINITY ? 0.0f : mine.y * fast_exp2(fmaf(mine.x, kLog2e, -slice_m * kLog2e)));
     if (tid < int(ranks)) {
-      float slice_m = -INFINITY;
-      for (int w = 0; w < kWarps; ++w) slice_m = fmaxf(slice_m, warp_stats[par][w].x);
-      const float slice_m2 = slice_m * kLog2e;
-      float slice_s = 0.0f;                                    // warp order: the same sum whoever computes it
-      for (int w = 0; w < kWarps; ++w)
-        if (warp_stats[par][w].x != -INFINITY) slice_s += warp_stats[par][w].y * fast_exp2(fmaf(warp_stats[par][w].x, kLog2e, -slice_m2));
       const uint64_t packed = (uint64_t(__float_as_uint(slice_s)) << 32) | uint64_t(__float_as_uint(slice_m));
       remote_store_and_signal(cluster_address_of(&peer_stats[par][rank], unsigned(tid)), packed,
                               cluster_address_of(&stats_barrier[par], unsigned(tid)));
     }
-    if (!mbarrier_wait_bounded_cluster(&stats_barrier[par], uint32_t(it >> 1) & 1u)) { healthy = false; break; }
-    float row_m = -INFINITY;
-    for (unsigned r = 0; r < ranks; ++r) row_m = fmaxf(row_m, peer_stats[par][r].x);
+    if (healthy && !mbarrier_wait_bounded_cluster(&stats_barrier[par], uint32_t(it >> 1) & 1u)) healthy = false;
+    // the same fold over the slices of the row: lane r holds slice r (same tree on every CTA of the row)
+    const float2 theirs = lane < int(ranks) ? peer_stats[par][lane] : make_float2(-INFINITY, 0.0f);
+    const float row_m = warp_max(theirs.x);
     const float row_m2 = row_m * kLog2e;
-    float row_sum = 0.0f;                                      // rank order: the same sum on every CTA of the row
-    for (unsigned r = 0; r < ranks; ++r)
-      if (peer_stats[par][r].x != -INFINITY) row_sum += peer_stats[par][r].y * fast_exp2(fmaf(peer_stats[par][r].x, kLog2e, -row_m2));
+    const float row_sum = warp_sum(theirs.x == -INFINITY ? 0.0f : theirs.y * fast_exp2(fmaf(theirs.x, kLog2e, -row_m2)));
     // a row of nothing but -inf divides 0 by 0, as the reference does
     const float scale = warp_m == -INFINITY ? (row_m == -INFINITY ? __int_as_float(0x7fc00000) : 0.0f)
                                             : fast_exp2(fmaf(warp_m, kLog2e, -row_m2)) / row_sum;
@@ -600,9 +602,9 @@ softmax_cluster_stream_kernel(const T* x, T* out, int64_t rows, int64_t width, i
     }
   }
   if (!healthy) {
-    // never expected: a bounded wait ran out.  Flag it, give a copy that may still be in flight one more
-    // bounded chance to land (it must not outlive this CTA's shared memory), and meet the other CTAs below.
-    if (tid == 0 && status != nullptr) atomicOr(status, 1);
+    // Flag it, and give a copy that may still be in flight one more bounded chance to land: it must not
+    // outlive this CTA's shared memory.
+    if (status != nullptr) atomicOr(status, 1);
     if (bytes != 0u) { mbarrier_wait_bounded(&stage_barrier, 0u); mbarrier_wait_bounded(&stage_barrier, 1u); }
   }
   // nobody leaves while a neighbour may still store into its shared memory (only matters after a failure:
