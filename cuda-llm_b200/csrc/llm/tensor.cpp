@@ -58,6 +58,9 @@ using HostBuffer = std::vector<uint8_t>;
 }  // namespace
 
 // ---- codecs (reference src/tensor.cpp:11-13)
+// Host-side conversions only: the kernels use the hardware's round-to-nearest-even conversions.  The host F16
+// encoder TRUNCATES the mantissa of normal numbers (and rounds only subnormals), which is what the reference's
+// host code does; tests that need round-to-nearest-even bit patterns build them with the oracle's encoder.
 
 uint16_t encode_bf16(float value) { return uint16_t(float_bits(value) >> 16); }
 float decode_bf16(uint16_t bits) { return bits_float(uint32_t(bits) << 16); }
@@ -89,6 +92,9 @@ float decode_f16(uint16_t bits) {
 }
 
 // ---- construction (reference src/tensor.cpp:16-19)
+// CPU storage is a zero-filled byte vector owned through the shared_ptr's deleter; CUDA storage comes from the
+// counted allocator of tensor_cuda.cu and is NOT initialised.  The private constructor makes views: it checks
+// that the window [offset, offset + nbytes) lies inside the storage it is given.
 
 Tensor::Tensor(DType dtype, std::vector<int64_t> shape, DeviceType device)
     : dtype_(dtype), device_(device), shape_(std::move(shape)), strides_(row_major_strides(shape_)),
@@ -119,6 +125,8 @@ Tensor Tensor::from_f32(const std::vector<int64_t>& shape, const std::vector<flo
 }
 
 // ---- views (reference src/tensor.cpp:20-45)
+// All views need a contiguous source.  slice_first_dim moves the byte offset by whole rows of the first
+// dimension; the result is only element-aligned, which is why every kernel has a path for unaligned pointers.
 
 bool Tensor::is_contiguous() const { return strides_ == row_major_strides(shape_); }
 
@@ -156,6 +164,8 @@ Tensor Tensor::contiguous() const {
 }
 
 // ---- data access (reference src/tensor.cpp:46-51)
+// data() works for both devices (it is only an address); every typed or element accessor refuses CUDA storage
+// with std::runtime_error and checks the dtype it is asked for.
 
 void* Tensor::data() {
   if (!storage_) return nullptr;
