@@ -220,3 +220,56 @@ def test_device_order_restatement_is_consistent(port):
     want = ((res16.view(np.float16).astype(np.float32) * inv) * w16.astype(np.float32)).astype(np.float16)
     assert np.array_equal(nrm16, f16_bits(want))
     assert np.array_equal(port.dev_add(f16_bits(x16), f16_bits(y16)), f16_bits(exact.astype(np.float16)))
+
+
+# ---- the sampler restatement against the reference's own sampler test (tests/test_sampling_cuda.cpp:18-56)
+
+def test_sampler_restatement_on_the_reference_test_cases(port):
+    f = np.float32
+    two = np.array([2, 9, 1, 7, 3, 5], f)
+    assert port.sample_row(two, 1.0, 1, 1.0, 0, 0)[0] == 1                          # top_k = 1 is greedy
+    assert port.sample_row(two, 1.0, 3, 1.0, 42, 7)[0] == port.sample_row(two, 1.0, 3, 1.0, 42, 7)[0]
+    small = np.array([10, 9, 0, -1, -2, -3], f)
+    assert {port.sample_row(small, 1.0, 2, 1.0, 1, i)[0] for i in range(20)} <= {0, 1}      # top-k boundary
+    assert {port.sample_row(small, 1.0, 3, 0.5, 2, i)[0] for i in range(20)} <= {0, 1}      # top-k with top-p
+    crossing = np.array([np.log(f(0.505)), np.log(f(0.495)), -20, -20, -20, -20], f)
+    assert {port.sample_row(crossing, 1.0, 0, 0.51, 77, o)[0] for o in range(64)} == {0, 1}   # the crossing token is kept
+    ties = np.array([0, 0, 0, -10, -10, -10], f)
+    assert {port.sample_row(ties, 1.0, 0, 0.30, 88, o)[0] for o in range(64)} == {0}          # equal maxima: lowest id
+    # frequencies follow the retained, renormalised distribution
+    rng = np.random.default_rng(3)
+    row = (rng.standard_normal(500) * 2).astype(f)
+    top = np.argsort(-row, kind="stable")[:10]
+    draws = np.array([port.sample_row(row, 1.0, 10, 1.0, 5, o)[0] for o in range(3000)])
+    assert set(np.unique(draws)) <= set(top.tolist())
+    p = np.exp(row[top].astype(np.float64) - row[top[0]])
+    p /= p.sum()
+    assert np.abs(np.array([(draws == t).mean() for t in top]) - p).max() < 4 * np.sqrt(0.25 / 3000)
+
+
+def test_kv_move_restatements_against_plain_indexing(port):
+    """orc_paged_kv_write / orc_select_last_valid (the reference kernels' index arithmetic) against numpy indexing
+    of the pool layout [layers, total_blocks, 2, block_size, kv_heads, head_dim]."""
+    rng = np.random.default_rng(8)
+    layers, total_blocks, block_size, kv_heads, head_dim = 2, 12, 4, 2, 8
+    storage = rng.standard_normal((layers, total_blocks, 2, block_size, kv_heads, head_dim)).astype(np.float16)
+    key = rng.standard_normal((3, kv_heads, head_dim)).astype(np.float16)
+    value = rng.standard_normal((3, kv_heads, head_dim)).astype(np.float16)
+    tables = np.array([[0, 1, 2], [5, 4, 3], [9, 8, 7]], np.int32)
+    positions = np.array([0, 5, 11], np.int32)
+    got = storage.copy()
+    port.paged_kv_write(0, key, value, got, tables, positions, 1, total_blocks, block_size)
+    want = storage.copy()
+    for b in range(3):
+        blk, slot = tables[b, positions[b] // block_size], positions[b] % block_size
+        want[1, blk, 0, slot], want[1, blk, 1, slot] = key[b], value[b]
+    assert np.array_equal(got, want)
+    got = storage.copy()
+    port.paged_kv_write(1, key, value, got, tables[1], np.zeros(1, np.int32), 0, total_blocks, block_size)
+    want = storage.copy()
+    for t in range(3):
+        want[0, tables[1, t // block_size], 0, t % block_size] = key[t]
+        want[0, tables[1, t // block_size], 1, t % block_size] = value[t]
+    assert np.array_equal(got, want)
+    padded = rng.standard_normal((3, 5, 7)).astype(np.float32)
+    assert np.array_equal(port.select_last_valid(padded, [5, 1, 3]), padded[[0, 1, 2], [4, 0, 2]])
