@@ -315,6 +315,26 @@ int b2_paged_kv_prefill_copy(const void* key, const void* value, void* storage, 
                                kv_heads * head_dim * (dtype == B2_F32 ? 4 : 2), status, as_stream(stream));
 }
 
+int b2_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                          const int32_t* positions, void* q_out, void* storage, const int32_t* block_tables,
+                          const int32_t* slot_positions, int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                          float eps, float theta, int64_t tokens_per_table, int64_t max_blocks, int64_t layer, int64_t layers,
+                          int64_t total_blocks, int64_t block_size, int dtype, int32_t* status, b2_stream stream) {
+  const char* op = "b2_qk_norm_rope_paged";
+  const int rc = pool_checks(op, k, v, storage, block_tables, positions, tokens, max_blocks, layer, layers, total_blocks,
+                             block_size, kv_heads, head_dim, dtype);
+  if (rc != B2_OK) return rc;
+  B2_REQUIRE(q_heads > 0 && fits(tokens, (q_heads + kv_heads) * head_dim) && (q_heads + kv_heads) * head_dim < (1 << 30), op,
+             "q_heads must be > 0");
+  B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
+  B2_REQUIRE(eps > 0.0f && theta > 0.0f, op, "eps and theta must be positive");
+  B2_REQUIRE(tokens_per_table >= 1, op, "tokens_per_table must be >= 1");
+  B2_REQUIRE(tokens == 0 || (q && q_weight && k_weight && q_out), op, "null pointer");
+  return launch_qk_norm_rope_paged(q, k, v, q_weight, k_weight, positions, q_out, storage, block_tables, slot_positions, tokens,
+                                   q_heads, kv_heads, head_dim, eps, theta, tokens_per_table, max_blocks, layer, total_blocks,
+                                   block_size, dtype, status, as_stream(stream));
+}
+
 int b2_select_last_valid_rows(const void* padded, const int32_t* valid_lengths, void* out, int64_t batch, int64_t seq,
                               int64_t width, int dtype, int32_t* status, b2_stream stream) {
   const char* op = "b2_select_last_valid_rows";

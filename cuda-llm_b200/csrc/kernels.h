@@ -22,6 +22,12 @@ int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void
                         void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads,
                         int64_t head_dim, float eps, float theta, int dtype, cudaStream_t s);
 int rope_bulk_timeouts(unsigned int* out);   // blocking read of a device counter
+int launch_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* qw, const void* kw,
+                              const int32_t* positions, void* q_out, void* storage, const int32_t* block_tables,
+                              const int32_t* slot_positions, int64_t tokens, int64_t q_heads, int64_t k_heads,
+                              int64_t head_dim, float eps, float theta, int64_t tokens_per_table, int64_t max_blocks,
+                              int64_t layer, int64_t total_blocks, int64_t block_size, int dtype, int32_t* status,
+                              cudaStream_t s);
 // gather.cu
 int launch_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden,
                   int64_t vocab, int dtype, int32_t* status, cudaStream_t s);

@@ -250,20 +250,17 @@ __device__ __forceinline__ void rope_item_from_shared(const uint4* xs, uint4* ou
   }
 }
 
-// All heads of one tensor for one token, from the staged row.  kHv > 0 fixes hv (vectors per half head)
-// and kHeads > 0 the head count at compile time.  The 32 lanes cover 32/hv heads per step, i.e. always
-// 64 vectors: the lane's vector index simply advances by 64 per step, so full steps carry no index
-// arithmetic and no predicates, and with a fixed head count the steps are unrolled so that the loads,
-// shuffles and stores of different heads overlap.
-template <typename T, bool kNorm, int kHv, int kHeads>
-__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int heads_rt, int hv_rt,
+// All heads of one tensor for one token, from the staged row.  kHv > 0 fixes hv (vectors per half head) at
+// compile time.  The 32 lanes cover 32/hv heads per step, i.e. always 64 vectors: the lane's vector index simply
+// advances by 64 per step, so full steps carry no index arithmetic and no predicates.
+template <typename T, bool kNorm, int kHv>
+__device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const uint4* w, uint4* out, int heads, int hv_rt,
                                                        int hv_shift_rt, int lane,
                                                        const LaneAngles<Elem<T>::kPerVec / 2>& ang, float inv_dim,
                                                        float eps) {
   constexpr int P = Elem<T>::kPerVec / 2;
   const int hv = kHv > 0 ? kHv : hv_rt;
   const int shift = kHv > 0 ? (kHv == 1 ? 0 : kHv == 2 ? 1 : kHv == 4 ? 2 : kHv == 8 ? 3 : kHv == 16 ? 4 : 5) : hv_shift_rt;
-  const int heads = kHeads > 0 ? kHeads : heads_rt;
   const int v = lane & (hv - 1);
   float2 wl[P], wh[P];
   if (kNorm) {
@@ -273,15 +270,8 @@ __device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const ui
   const int items = heads << shift;
   int where = ((lane >> shift) << (shift + 1)) + v;
   const int full = items >> 5;
-  if (kHeads > 0 && kHv > 0) {
-#pragma unroll
-    for (int i = 0; i < full; ++i)
-      rope_item_from_shared<T, kNorm, P>(xs, out, where + i * 2 * kWarpSize, hv, true, wl, wh, ang, inv_dim, eps);
-    where += full * 2 * kWarpSize;
-  } else {
-    for (int i = 0; i < full; ++i, where += 2 * kWarpSize)
-      rope_item_from_shared<T, kNorm, P>(xs, out, where, hv, true, wl, wh, ang, inv_dim, eps);
-  }
+  for (int i = 0; i < full; ++i, where += 2 * kWarpSize)
+    rope_item_from_shared<T, kNorm, P>(xs, out, where, hv, true, wl, wh, ang, inv_dim, eps);
   if (items & 31) {
     // ragged last step: lanes past the end redo the last head (valid memory, converged shuffles) and store nothing
     const bool ok = (full << 5) + lane < items;
@@ -290,6 +280,18 @@ __device__ __forceinline__ void rope_heads_from_shared(const uint4* xs, const ui
   }
 }
 
+// Where the key and value rows of a token go when the kernel writes them straight into the paged KV cache
+// (storage [layers, total_blocks, 2, block_size, kv_heads, head_dim], plane 0 = keys, 1 = values): token t uses
+// row t / tokens_per_table of block_tables and cache position slot_positions[t] (or t % tokens_per_table).
+struct PagedTarget {
+  unsigned char* storage;
+  const int32_t* block_tables;
+  const int32_t* slot_positions;
+  const unsigned char* value;      // [tokens, kv_heads, head_dim], copied unchanged into plane 1
+  int64_t tokens_per_table, max_blocks, layer, total_blocks, block_size;
+  int32_t* status;                 // bit 0: a block id or position out of range (that token's K/V were not written)
+};
+
 // Shared memory per warp: two stages of (q row + k row), then two cos/sin tables (one per stage).
 // The table of the NEXT token is computed right after its rows have been requested and before the
 // warp waits for the current rows, so the fp64 angle arithmetic runs under the copy's latency.
@@ -297,16 +299,16 @@ constexpr int kBulkWarps = 4, kBulkCtasPerSm = 4;
 constexpr int kBulkFreqPerLane = kMaxTableHalf / kWarpSize;   // head_dim <= 256
 constexpr int kBulkMaxStages = 4;
 
-template <typename T, bool kNorm, int kHv, int kQHeads, int kKHeads>
+template <typename T, bool kNorm, int kHv, bool kPaged>
 __global__ void __launch_bounds__(kBulkWarps * kWarpSize, kBulkCtasPerSm)
 rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
                         int hv_shift, int64_t pos_period, float eps, float theta, int stages,
-                        const __grid_constant__ InvFreq freq) {
+                        const __grid_constant__ InvFreq freq, const __grid_constant__ PagedTarget paged) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int vecs_per_head = 2 * hv;
-  const int q_heads = kQHeads > 0 ? kQHeads : q.heads, k_heads = kQHeads > 0 ? kKHeads : k.heads;
+  const int q_heads = q.heads, k_heads = k.heads;
   const uint32_t q_bytes = uint32_t(q_heads) * vecs_per_head * 16u, k_bytes = uint32_t(k_heads) * vecs_per_head * 16u;
   const uint32_t stage_bytes = q_bytes + k_bytes, table_bytes = uint32_t(head_dim) * 4u;
   const uint32_t per_warp = uint32_t(stages) * stage_bytes + 2u * table_bytes;
@@ -401,11 +403,38 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
       break;
     }
     const uint4* xs = reinterpret_cast<const uint4*>(mine + uint32_t(stage) * stage_bytes);
-    rope_heads_from_shared<T, kNorm, kHv, kQHeads>(xs, q_w, q_out + size_t(t) * q_vecs, q_heads, hv, hv_shift, lane, ang,
-                                                   inv_dim, eps);
-    if (k_heads > 0)
-      rope_heads_from_shared<T, kNorm, kHv, kKHeads>(xs + q_vecs, k_w, k_out + size_t(t) * k_vecs, k_heads, hv, hv_shift,
-                                                     lane, ang, inv_dim, eps);
+    rope_heads_from_shared<T, kNorm, kHv>(xs, q_w, q_out + size_t(t) * q_vecs, q_heads, hv, hv_shift, lane, ang, inv_dim, eps);
+    if (kPaged) {
+      // the key row goes to its slot of the paged cache, and the value row is copied beside it
+      const int64_t table_row = t / paged.tokens_per_table;
+      const int64_t position = paged.slot_positions != nullptr ? int64_t(paged.slot_positions[t]) : t - table_row * paged.tokens_per_table;
+      bool ok = position >= 0 && position / paged.block_size < paged.max_blocks;
+      int64_t block = 0;
+      if (ok) {
+        block = paged.block_tables[table_row * paged.max_blocks + position / paged.block_size];
+        ok = block >= 0 && block < paged.total_blocks;
+      }
+      if (ok) {
+        const int64_t row_bytes = int64_t(k_vecs) * 16;
+        unsigned char* key_row = paged.storage +
+            ((((paged.layer * paged.total_blocks + block) * 2) * paged.block_size + position % paged.block_size) * row_bytes);
+        uint4* value_row = reinterpret_cast<uint4*>(key_row + paged.block_size * row_bytes);
+        const uint4* value_src = reinterpret_cast<const uint4*>(paged.value) + size_t(t) * k_vecs;
+        uint4 held[4];                       // the value row's loads fly under the key heads' arithmetic
+#pragma unroll
+        for (int i = 0; i < 4; ++i) if (lane + i * kWarpSize < k_vecs) held[i] = ld_stream(value_src + lane + i * kWarpSize);
+        rope_heads_from_shared<T, kNorm, kHv>(xs + q_vecs, k_w, reinterpret_cast<uint4*>(key_row), k_heads, hv, hv_shift, lane,
+                                              ang, inv_dim, eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) if (lane + i * kWarpSize < k_vecs) st_stream(value_row + lane + i * kWarpSize, held[i]);
+        for (int i = lane + 4 * kWarpSize; i < k_vecs; i += kWarpSize) st_stream(value_row + i, ld_stream(value_src + i));
+      } else if (lane == 0 && paged.status != nullptr) {
+        atomicOr(paged.status, 1);
+      }
+    } else if (k_heads > 0) {
+      rope_heads_from_shared<T, kNorm, kHv>(xs + q_vecs, k_w, k_out + size_t(t) * k_vecs, k_heads, hv, hv_shift, lane, ang,
+                                            inv_dim, eps);
+    }
     __syncwarp();   // stage and table are free again
     if (++stage == stages) { stage = 0; ++round; }
   }
@@ -484,7 +513,7 @@ template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
 
 template <typename T, bool kNorm>
 bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv, int hv_shift,
-                 int64_t pos_period, float eps, float theta, cudaStream_t s) {
+                 int64_t pos_period, float eps, float theta, cudaStream_t s, const PagedTarget* paged = nullptr) {
   static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
   if (!enabled) return false;
   constexpr int stages = 2, max_warps = kBulkWarps;   // deeper prefetch and other warp counts measured no faster
@@ -498,8 +527,11 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
   const size_t smem = size_t(warps) * (per_warp + bar_bytes);
   // the head size of the model family gets hv fixed at compile time (head_dim 128: 8 vectors of fp16, 16 of fp32
   // per half head); fixing the head counts as well measured no faster
-  auto kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8, 0, 0> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16, 0, 0>
-                                                                               : rope_tokens_bulk_kernel<T, kNorm, 0, 0, 0>;
+  auto kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8, false> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16, false>
+                                                                                 : rope_tokens_bulk_kernel<T, kNorm, 0, false>;
+  if (paged != nullptr)
+    kernel = hv == 8 ? rope_tokens_bulk_kernel<T, kNorm, 8, true> : hv == 16 ? rope_tokens_bulk_kernel<T, kNorm, 16, true>
+                                                                             : rope_tokens_bulk_kernel<T, kNorm, 0, true>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
     cudaGetLastError();
     return false;
@@ -507,7 +539,8 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
   const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * kBulkCtasPerSm;
   kernel<<<unsigned(ctas < cap ? ctas : cap), warps * kWarpSize, smem, s>>>(q, k, positions, tokens, int(head_dim), hv,
                                                                           hv_shift, pos_period, eps, theta, stages,
-                                                                          make_table(head_dim, theta));
+                                                                          make_table(head_dim, theta),
+                                                                          paged != nullptr ? *paged : PagedTarget{});
   return true;
 }
 
@@ -603,6 +636,38 @@ int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void
                                                   head_dim, eps, theta, s)
                          : launch_qk_typed<__half>(q, k, qw, kw, positions, q_out, k_out, tokens, q_heads, k_heads,
                                                    head_dim, eps, theta, s);
+}
+
+// Fused form that leaves the keys and values in the paged KV cache.  Only the vector (bulk-copy) kernel has it:
+// B2_ERR_UNSUPPORTED for shapes or alignments it cannot take, and the caller runs the separate operators instead.
+int launch_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* qw, const void* kw,
+                              const int32_t* positions, void* q_out, void* storage, const int32_t* block_tables,
+                              const int32_t* slot_positions, int64_t tokens, int64_t q_heads, int64_t k_heads,
+                              int64_t head_dim, float eps, float theta, int64_t tokens_per_table, int64_t max_blocks,
+                              int64_t layer, int64_t total_blocks, int64_t block_size, int dtype, int32_t* status,
+                              cudaStream_t s) {
+  if (tokens == 0) return B2_OK;
+  PagedTarget paged{static_cast<unsigned char*>(storage), block_tables, slot_positions, static_cast<const unsigned char*>(v),
+                    tokens_per_table, max_blocks, layer, total_blocks, block_size, status};
+  HeadSet qs{q, qw, q_out, int(q_heads)}, ks{k, kw, nullptr, int(k_heads)};
+  const bool aligned = aligned16(q) && aligned16(q_out) && aligned16(qw) && aligned16(k) && aligned16(kw) && aligned16(v) &&
+                       aligned16(storage);
+  int hv = 0, shift = 0;
+  bool launched = false;
+  if (dtype == B2_F32) {
+    if (aligned && vector_shape_ok<float>(head_dim, &hv)) {
+      while ((1 << shift) < hv) ++shift;
+      launched = launch_bulk<float, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, s, &paged);
+    }
+  } else if (aligned && vector_shape_ok<__half>(head_dim, &hv)) {
+    while ((1 << shift) < hv) ++shift;
+    launched = launch_bulk<__half, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, s, &paged);
+  }
+  if (!launched) {
+    set_error("b2_qk_norm_rope_paged: this shape or alignment has no fused kernel; use b2_qk_norm_rope and b2_paged_kv_write_*");
+    return B2_ERR_UNSUPPORTED;
+  }
+  return launch_status("qk_norm_rope_paged");
 }
 
 }  // namespace b2

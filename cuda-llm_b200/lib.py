@@ -79,6 +79,7 @@ _SIGNATURES = {
     "b2_paged_kv_write_decode_batch": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "b2_paged_kv_write_decode": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "b2_paged_kv_prefill_copy": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
+    "b2_qk_norm_rope_paged": (_i, [_p] * 10 + [_i64, _i64, _i64, _i64, _f, _f, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "b2_select_last_valid_rows": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p, _p]),
     "b2_sampler_workspace_bytes": (_sz, [_i64, _i64]),
     "b2_sample_rows": (_i, [_p, _i64, _i64, _i64, _i, _f, C.c_int32, _f, C.c_uint64, _p, _p, _p, _p]),

@@ -147,7 +147,30 @@ def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
         ms = timed(calls, nreps(100))
         record("paged_kv_write_decode_batch", f"B={B}, {kv_heads} heads x {head_dim} f16", 4 * B * row_bytes + 20 * B, ms, B,
                note="latency-bound: 2 MB moved")
-        del storage, sets
+        # the attention prologue in one launch: QK-norm + RoPE with K and V landing in the paged cache
+        Tq = 16384
+        q, kk, vv = randn(Tq, 16, head_dim), randn(Tq, kv_heads, head_dim), randn(Tq, kv_heads, head_dim)
+        qo, ko = torch.empty_like(q), torch.empty_like(kk)
+        g = (torch.rand(head_dim, device=dev) + 0.5).half()
+        rpos = torch.randint(0, 512, (Tq,), device=dev, dtype=torch.int32)
+        fused = [lambda: lib.check(L.b2_qk_norm_rope_paged(q.data_ptr(), kk.data_ptr(), vv.data_ptr(), g.data_ptr(), g.data_ptr(),
+                                                           rpos.data_ptr(), qo.data_ptr(), storage.data_ptr(), table.data_ptr(),
+                                                           None, Tq, 16, kv_heads, head_dim, 1e-6, 1e6, Tq, table.numel(), 1,
+                                                           layers, total_blocks, block_size, F16, None, s))]
+        ms = timed(fused, nreps(40))
+        fused_bytes = 2 * Tq * 16 * head_dim * 2 + 4 * Tq * row_bytes + 8 * Tq      # q in/out, k in, v in, K and V rows out
+        record("qk_norm_rope_paged (QK-norm + RoPE + K/V into the paged cache, one launch)", f"T={Tq}, 16+8 heads x {head_dim} f16",
+               fused_bytes, ms, Tq)
+
+        def separate():
+            lib.check(L.b2_qk_norm_rope(q.data_ptr(), kk.data_ptr(), g.data_ptr(), g.data_ptr(), rpos.data_ptr(), qo.data_ptr(),
+                                        ko.data_ptr(), Tq, 16, kv_heads, head_dim, 1e-6, 1e6, F16, s))
+            lib.check(L.b2_paged_kv_prefill_copy(ko.data_ptr(), vv.data_ptr(), storage.data_ptr(), table.data_ptr(), Tq,
+                                                 table.numel(), 1, layers, total_blocks, block_size, kv_heads, head_dim, F16, None, s))
+        ms = timed([separate], nreps(40))
+        record("qk_norm_rope + paged_kv_prefill_copy (two launches)", f"T={Tq}, 16+8 heads x {head_dim} f16",
+               fused_bytes + 2 * Tq * row_bytes, ms, Tq, note="moves the keys twice more; bytes counted per launch sequence")
+        del storage, sets, q, kk, vv, qo, ko
         Bp, S = 64, 16
         padded = [randn(Bp, S, VOCAB, dtype=torch.float32) for _ in range(2)]
         lengths = torch.randint(1, S + 1, (Bp,), device=dev, dtype=torch.int32)

@@ -592,3 +592,33 @@ def select_last_valid_logits(padded_logits, valid_lengths: Sequence[int]):
     _lib.check(_lib.load().b2_select_last_valid_rows(_ptr(padded_logits), _ptr(lengths), _ptr(out), batch, seq, vocab,
                                                      _code(padded_logits), None, _stream()))
     return out
+
+
+def qk_norm_rope_paged_out(q, k, v, q_weight, k_weight, positions_device, eps: float, theta: float, q_out, storage, layer: int,
+                           block_tables, slot_positions=None, tokens_per_table: int = 1, status=None) -> None:
+    """b2_qk_norm_rope_paged: per-head RMSNorm + RoPE of q and k in one launch, the rotated keys and the values
+    written straight into the paged KV pool.  Decode batch: block_tables [B, max_blocks], slot_positions =
+    positions_device, tokens_per_table = 1.  One packed sequence: block_tables [max_blocks], slot_positions None,
+    tokens_per_table = tokens.  Raises lib.B2Error (status -3) for shapes only the scalar kernels take."""
+    op = "qk_norm_rope_paged"
+    layers, total_blocks, _, block_size, kv_heads, head_dim = _pool_args(storage, k, v, op)
+    _req(q, op)
+    _same_dtype(op, q, k, q_weight, k_weight)
+    if q.dim() != 3 or q.shape[0] != k.shape[0] or q.shape[2] != head_dim:
+        raise ValueError(f"{op}: q must be [tokens, q_heads, head_dim] with the pool's head_dim")
+    if tuple(q_weight.shape) != (head_dim,) or tuple(k_weight.shape) != (head_dim,) or not (eps > 0) or not (theta > 0):
+        raise ValueError(f"{op}: incompatible shape/epsilon/theta")
+    _output_req(q_out, q.shape, q.dtype, op)
+    tokens = q.shape[0]
+    _positions_device(positions_device, tokens, op, exact=True)
+    _i32_device(block_tables, None, op, "block tables")
+    if slot_positions is not None:
+        _i32_device(slot_positions, (tokens,), op, "slot positions")
+    max_blocks = block_tables.shape[-1]
+    rows_needed = -(-tokens // tokens_per_table)
+    if block_tables.numel() < rows_needed * max_blocks or not 0 <= layer < layers or tokens_per_table < 1:
+        raise ValueError(f"{op}: invalid block tables or layer")
+    _lib.check(_lib.load().b2_qk_norm_rope_paged(_ptr(q), _ptr(k), _ptr(v), _ptr(q_weight), _ptr(k_weight), _ptr(positions_device),
+                                                 _ptr(q_out), _ptr(storage), _ptr(block_tables), _ptr(slot_positions), tokens,
+                                                 q.shape[1], kv_heads, head_dim, eps, theta, tokens_per_table, max_blocks, layer,
+                                                 layers, total_blocks, block_size, _code(q), _ptr(status), _stream()))

@@ -248,6 +248,27 @@ B2_API int b2_paged_kv_prefill_copy(const void* key, const void* value, void* st
                                     int64_t total_blocks, int64_t block_size, int64_t kv_heads, int64_t head_dim,
                                     int dtype, int32_t* status, b2_stream stream);
 
+/* The attention prologue of a layer in ONE launch: per-head RMSNorm + RoPE of q and k as b2_qk_norm_rope,
+ * with the rotated keys written straight into their slots of the paged KV pool and the value rows copied
+ * beside them (plane 1) -- instead of cuda_rms_norm x2, cuda_rope_* x2 and cuda_paged_kv_write_decode_batch
+ * (src/qwen3_layer_cuda.cu:390-403) or cuda_paged_kv_prefill_copy_packed (:860-880).  The keys never make
+ * the round trip through a [tokens, kv_heads, head_dim] buffer.
+ *   q [tokens, q_heads, head_dim], k and v [tokens, kv_heads, head_dim], positions int32[tokens] (rotary);
+ *   token t uses row t / tokens_per_table of block_tables [.., max_blocks] and cache position
+ *   slot_positions[t], or t % tokens_per_table when slot_positions is NULL
+ *   (decode batch: tokens_per_table = 1, slot_positions = positions; one packed sequence: tokens_per_table =
+ *   tokens, slot_positions = NULL).
+ * Results are bit-identical to b2_qk_norm_rope followed by b2_paged_kv_write_*.  Bad block ids or positions:
+ * that token's K/V are skipped and bit 0 of *status is raised.  Returns B2_ERR_UNSUPPORTED for head sizes or
+ * alignments that only the scalar kernels take (use the separate calls then).  Fast mode only. */
+B2_API int b2_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* q_weight,
+                                 const void* k_weight, const int32_t* positions, void* q_out, void* storage,
+                                 const int32_t* block_tables, const int32_t* slot_positions, int64_t tokens,
+                                 int64_t q_heads, int64_t kv_heads, int64_t head_dim, float eps, float theta,
+                                 int64_t tokens_per_table, int64_t max_blocks, int64_t layer, int64_t layers,
+                                 int64_t total_blocks, int64_t block_size, int dtype, int32_t* status,
+                                 b2_stream stream);
+
 /* out[b, :] = padded[b, valid_lengths[b] - 1, :] for padded [batch, seq, width]: the logits of each
  * prompt's last real token, gathered in one launch.  valid_lengths: device int32[batch]; a length outside
  * [1, seq] zero-fills that row and raises bit 0 of *status (device int32, may be NULL).

@@ -67,3 +67,49 @@ def test_layer_operator_sequence_replays_from_a_cuda_graph(b2, batch):
     for name in again:
         assert torch.equal(again[name], captured[name]), name
     assert captured["ids"].tolist() == [5] * batch
+
+
+def test_sampling_and_the_paged_attention_prologue_replay_from_a_cuda_graph(b2):
+    """b2_sample_rows (a memset and kernels only) and b2_qk_norm_rope_paged are capturable like the rest: the graph
+    replays the draw and the cache writes on whatever the input tensors hold at replay time."""
+    from cuda_llm_b200.ops import SamplingConfig
+    rng = np.random.default_rng(11)
+    batch, heads, kv_heads, dim, block_size = 4, 16, 8, 128, 16
+    h = lambda *s: torch.from_numpy(wl.normal(rng, s, dtype=np.float16)).to(DEV)
+    logits = torch.from_numpy(wl.normal(rng, (batch, wl.VOCAB), 4.0)).to(DEV)
+    offsets = torch.arange(batch, dtype=torch.int64, device=DEV)
+    cfg = SamplingConfig(temperature=0.8, top_k=50, top_p=0.95, seed=3)
+    q, k, v = h(batch, heads, dim), h(batch, kv_heads, dim), h(batch, kv_heads, dim)
+    gq, gk = torch.from_numpy(wl.gamma(rng, dim, dtype=np.float16)).to(DEV), torch.from_numpy(wl.gamma(rng, dim, dtype=np.float16)).to(DEV)
+    pos = torch.tensor([5, 17, 0, 31], dtype=torch.int32, device=DEV)
+    tables = torch.arange(batch * 2, dtype=torch.int32, device=DEV).reshape(batch, 2).contiguous()
+
+    def run(ids, q_out, storage):
+        ops.sample_rows_out(logits, cfg, offsets, ids)
+        ops.qk_norm_rope_paged_out(q, k, v, gq, gk, pos, wl.EPS, wl.THETA, q_out, storage, 0, tables, pos, 1)
+
+    def fresh():
+        return (torch.zeros(batch, dtype=torch.int32, device=DEV), torch.zeros_like(q),
+                torch.zeros(1, batch * 2, 2, block_size, kv_heads, dim, dtype=torch.float16, device=DEV))
+
+    eager = fresh()
+    run(*eager)                      # also sizes the cached sampler workspace before capture
+    torch.cuda.synchronize()
+    captured = fresh()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            run(*captured)
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(eager, captured):
+        assert torch.equal(a, b)
+    logits[:, 77] = 1e4              # new inputs, same graph
+    k.copy_(h(batch, kv_heads, dim))
+    graph.replay()
+    again = fresh()
+    run(*again)
+    torch.cuda.synchronize()
+    for a, b in zip(again, captured):
+        assert torch.equal(a, b)
+    assert captured[0].tolist() == [77] * batch

@@ -95,3 +95,67 @@ def test_select_last_valid_logits(b2, port, dtype, batch, seq, width):
         ops.select_last_valid_logits(dev(padded), [seq + 1] * batch)
     with pytest.raises(ValueError):
         ops.select_last_valid_logits(dev(padded)[0], [1])
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("tokens,mode", [(1, "decode"), (7, "decode"), (256, "decode"), (100, "prefill"), (1000, "prefill")])
+def test_qk_norm_rope_straight_into_the_paged_cache(b2, port, dtype, tokens, mode):
+    """b2_qk_norm_rope_paged = b2_qk_norm_rope + the paged K/V write, bit for bit, and within the parity bound of
+    the CPU oracle's rms_norm -> rope for the keys that land in the cache."""
+    from cuda_llm_b200 import workloads as wl
+    rng = np.random.default_rng(tokens)
+    q_heads, kv_heads, head_dim, block_size, layers = 16, 8, 128, 16, 2
+    q = wl.normal(rng, (tokens, q_heads, head_dim)).astype(dtype)
+    k = wl.normal(rng, (tokens, kv_heads, head_dim)).astype(dtype)
+    v = wl.normal(rng, (tokens, kv_heads, head_dim)).astype(dtype)
+    gq, gk = wl.gamma(rng, head_dim).astype(dtype), wl.gamma(rng, head_dim).astype(dtype)
+    if mode == "decode":
+        max_blocks = 4
+        total_blocks = tokens * max_blocks + 3
+        tables = rng.permutation(total_blocks)[: tokens * max_blocks].reshape(tokens, max_blocks).astype(np.int32)
+        positions = rng.integers(0, max_blocks * block_size, tokens).astype(np.int32)
+        slots, per_table = positions, 1
+    else:
+        max_blocks = -(-tokens // block_size)
+        total_blocks = max_blocks + 5
+        tables = rng.permutation(total_blocks)[:max_blocks].astype(np.int32)
+        positions = np.arange(tokens, dtype=np.int32) + 3          # rotary positions need not equal the cache slots
+        slots, per_table = None, tokens
+    storage = rng.standard_normal((layers, total_blocks, 2, block_size, kv_heads, head_dim)).astype(dtype)
+
+    # the separate operators
+    want_q, k_rot = torch.empty_like(dev(q)), torch.empty_like(dev(k))
+    ops.qk_norm_rope_out(dev(q), dev(k), dev(gq), dev(gk), dev(positions), wl.EPS, wl.THETA, want_q, k_rot)
+    want_storage = dev(storage)
+    if mode == "decode":
+        ops.paged_kv_write_decode_batch(k_rot, dev(v), want_storage, 1, dev(tables), dev(positions))
+    else:
+        ops.paged_kv_prefill_copy_packed(k_rot, dev(v), want_storage, dev(tables), 1)
+    # one launch
+    got_q, got_storage = torch.empty_like(want_q), dev(storage)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.qk_norm_rope_paged_out(dev(q), dev(k), dev(v), dev(gq), dev(gk), dev(positions), wl.EPS, wl.THETA, got_q, got_storage, 1,
+                               dev(tables), None if slots is None else dev(slots), per_table, status)
+    assert torch.equal(got_q.view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(got_storage.view(torch.uint8), want_storage.view(torch.uint8))
+    assert int(status.item()) == 0
+    # the keys in the cache against the CPU oracle
+    # (1 fp16 ulp / 1e-5 of the output, or of the larger input of the rotated pair where the output cancelled:
+    # the rule of the RoPE parity tests)
+    from test_gpu_rope import pair_scale
+    from util import ulp16
+    kf = k.astype(np.float32)
+    normed = port.rms_norm(kf.reshape(-1, head_dim), gk.astype(np.float32), wl.EPS).reshape(kf.shape)
+    ref_k = port.rope(normed, positions, wl.THETA)
+    scale = np.maximum(np.abs(ref_k), pair_scale(normed))
+    got = host(got_storage)
+    for t in (0, tokens // 2, tokens - 1):
+        pos = int(positions[t]) if mode == "decode" else t
+        blk = tables[t, pos // block_size] if mode == "decode" else tables[pos // block_size]
+        row = got[1, blk, 0, pos % block_size].astype(np.float64)
+        err = np.abs(row - ref_k[t])
+        if dtype == np.float16:
+            assert float((err / ulp16(scale[t])).max()) <= 1.0, f"cached key of token {t}"
+        else:
+            assert float((err / scale[t]).max()) <= 1e-5, f"cached key of token {t}"
+        assert np.array_equal(got[1, blk, 1, pos % block_size], v[t])
