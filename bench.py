@@ -151,6 +151,71 @@ def cpu_baseline(target_seconds: float, steps: int = 1, warmup: int = 0):
                                      f"CPU operators take; GB/s counts the fp16 workload's algorithmic bytes per row"}
 
 
+def cpu_operator_table():
+    """The reference's unmodified CPU operators (oracle/_ref; the C port where the reference has no CPU form) on
+    bounded samples of the configurations' shapes: single thread as the reference runs them, and rows split over all
+    host threads.  A reported baseline: rows/s and the GB/s those rows are worth in the fp16/fp32 GPU workload."""
+    import concurrent.futures as cf
+    import numpy as np
+    import oracle
+    ref, port = oracle.ref(), oracle.port()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/liboracle_ref.so was not built (reference tree absent at build time)"}
+    threads = max(1, ref.hardware_threads())
+    rng = np.random.default_rng(7)
+    f = np.float32
+    table = []
+
+    def timed(fn):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        return time.perf_counter() - t0
+
+    def entry(op, shape, rows, gpu_bytes_per_row, single, chunked, kind="reference"):
+        t1 = timed(single)
+        tn = timed(chunked) if chunked is not None else None
+        e = {"op": op, "sample": shape, "kind": kind, "single_thread_rows_per_s": round(rows / t1, 1),
+             "single_thread_gbs_equivalent": round(rows * gpu_bytes_per_row / t1 / 1e9, 4)}
+        if tn is not None:
+            e.update({"threads": threads, "all_threads_rows_per_s": round(rows / tn, 1),
+                      "all_threads_gbs_equivalent": round(rows * gpu_bytes_per_row / tn / 1e9, 4)})
+        table.append(e)
+
+    def split(fn, *arrays):
+        """fn over disjoint row slices of the arrays, one slice per host thread (ctypes releases the GIL)."""
+        n = arrays[0].shape[0]
+        bounds = [(n * i // threads, n * (i + 1) // threads) for i in range(threads)]
+
+        def run():
+            with cf.ThreadPoolExecutor(threads) as pool:
+                list(pool.map(lambda b: fn(*[a[b[0]:b[1]] for a in arrays]) if b[1] > b[0] else None, bounds))
+        return run
+
+    w4096 = (rng.random(4096, dtype=f) + f(0.5))
+    x = rng.standard_normal((2048, 4096), dtype=f)
+    entry("rms_norm", "2048 x 4096 f32", 2048, 2 * 4096 * 2, lambda: ref.rms_norm(x, w4096, 1e-6),
+          split(lambda a: ref.rms_norm(a, w4096, 1e-6), x))
+    g, u = rng.standard_normal((1024, 3072), dtype=f) * 2, rng.standard_normal((1024, 3072), dtype=f) * 2
+    entry("swiglu", "1024 x 3072 f32", 1024, 3 * 3072 * 2, lambda: ref.swiglu(g, u), split(lambda a, b: ref.swiglu(a, b), g, u))
+    q = rng.standard_normal((1024, 24, 128), dtype=f)
+    pos = rng.integers(0, 512, 1024).astype(np.int32)
+    w128 = (rng.random(128, dtype=f) + f(0.5))
+    qk = lambda a, p: ref.rope(ref.rms_norm(a.reshape(-1, 128), w128, 1e-6).reshape(a.shape), p, 1e6)
+    entry("qk rms_norm + rope", "1024 tokens x 24 heads x 128 f32", 1024, 2 * 24 * 128 * 2 + 4, lambda: qk(q, pos), split(qk, q, pos))
+    emb = rng.standard_normal((8192, 4096), dtype=f) * f(0.02)
+    ids = rng.integers(0, 8192, 4096).astype(np.int32)
+    entry("embedding_lookup", "4096 ids, table 8192 x 4096 f32", 4096, 2 * 4096 * 2 + 4, lambda: ref.embedding_lookup(emb, ids),
+          split(lambda i: ref.embedding_lookup(emb, i), ids))
+    logits = rng.standard_normal((16, 151936), dtype=f) * 4
+    entry("softmax_last_dim", "16 x 151936 f32", 16, 2 * 151936 * 4, lambda: ref.softmax(logits), split(lambda a: ref.softmax(a), logits))
+    entry("argmax (C restatement of the device rule: the reference has no CPU argmax)", "16 x 151936 f32", 16, 151936 * 4,
+          lambda: port.argmax_rows(logits), None, kind="port")
+    entry("sample top_k=50 top_p=0.95 (C restatement of the device rule)", "4 x 151936 f32", 4, 151936 * 4,
+          lambda: [port.sample_row(logits[r], 0.8, 50, 0.95, 7, r) for r in range(4)], None, kind="port")
+    return {"threads_available": threads, "entries": table}
+
+
 def reference_gpu_kernels(L, lib, dev, stream):
     """The reference's own CUDA operators (src/ops_cuda.cu recompiled for sm_100a, oracle/_ref/libref_cuda.so)
     timed on this GPU beside ours, same shapes, device-resident tensors, CUDA events.  A reported baseline."""
@@ -405,6 +470,11 @@ def main():
             _, _, line["cpu_baseline"] = cpu_baseline(10.0)
         except Exception as exc:  # the baseline is reported, never required for the GPU number
             line["cpu_baseline"] = {"error": str(exc)}
+    if world == 1 and not args.no_cpu and not args.no_ops:
+        try:
+            line["cpu_ops"] = cpu_operator_table()
+        except Exception as exc:
+            line["cpu_ops"] = {"error": str(exc)}
     if op_table is not None:
         line["ops"] = op_table
     if ref_gpu is not None:

@@ -101,6 +101,19 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
         _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, nreps)
     if want("argmax") or want("softmax"):
         _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table)
+    if world == 1 and want("copy"):
+        # a yardstick measured in the same run with the same harness: plain device-to-device copies (torch's kernel, not
+        # ours) of 1 GiB and of the byte counts of the two small configurations
+        for label, nbytes in (("1 GiB each way", 1 << 30), ("100.7 MB each way (configuration 3's bytes)", 100_663_296),
+                              ("155.6 MB each way (configuration 5's softmax bytes)", 155_582_464)):
+            n = max(2, min(4, -(-512 * 1024 * 1024 // nbytes)))
+            bufs = [(torch.empty(nbytes, dtype=torch.uint8, device=dev), torch.empty(nbytes, dtype=torch.uint8, device=dev))
+                    for _ in range(n)]
+            for a, _ in bufs:
+                a.fill_(1)
+            ms = timed([(lambda b=b: b[1].copy_(b[0])) for b in bufs], nreps(20))
+            record("device copy (library kernel, yardstick only)", label, 2 * nbytes, ms)
+            del bufs
     if world == 1 and (want("sampler") or want("kvmove")):
         _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
     return table
