@@ -101,6 +101,132 @@ bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t
   }
 }
 
+// ---- the same network for full 4096-key tiles, with the keys in registers.  The shared-memory kernel above
+// moves every key through shared memory at every step (its bandwidth is what that kernel is bound by); here a
+// thread keeps 16 keys in registers and a step costs shared memory only when the partner is in another warp:
+//   layout B  thread t holds elements 16t .. 16t+15   steps j = 1..8 in registers, j = 16..256 by warp shuffles
+//   layout S  thread t holds elements t, t+256, ...   steps j = 512..2048 in registers
+// and two transposes through (swizzled) shared memory per phase that has steps of both kinds.
+constexpr int kRegKeys = 16, kRegThreads = kTile / kRegKeys;   // 256 threads per 4096-key tile
+
+__device__ __forceinline__ int swizzled(int e) { return e ^ ((e >> 4) & 15); }   // 64-bit accesses of either layout hit 16 banks pairs
+
+__device__ __forceinline__ void steps_in_registers_b(unsigned long long (&key)[kRegKeys], int64_t first_global, int64_t k,
+                                                     int j_from) {
+#pragma unroll
+  for (int j = 8; j >= 1; j >>= 1) {
+    if (j > j_from) continue;
+#pragma unroll
+    for (int r = 0; r < kRegKeys; ++r)
+      if ((r & j) == 0) compare_exchange(key[r], key[r | j], ((first_global + r) & k) == 0);
+  }
+}
+
+__device__ __forceinline__ void steps_by_shuffle_b(unsigned long long (&key)[kRegKeys], int64_t first_global, int64_t k,
+                                                   int j_from, int lane) {
+  for (int j = j_from; j >= 16; j >>= 1) {
+    const int m = j >> 4;
+    const bool lower = (lane & m) == 0;
+#pragma unroll
+    for (int r = 0; r < kRegKeys; ++r) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, key[r], m);
+      const bool descending = ((first_global + r) & k) == 0;
+      const bool keep_larger = lower == descending;
+      key[r] = (key[r] < other) == keep_larger ? other : key[r];
+    }
+  }
+}
+
+// layout S: element of register r is r * 256 + t; steps j = 2048, 1024, 512 (those <= j_from)
+__device__ __forceinline__ void steps_in_registers_s(unsigned long long (&key)[kRegKeys], int64_t tile_global, int t, int64_t k,
+                                                     int j_from) {
+#pragma unroll
+  for (int m = 8; m >= 2; m >>= 1) {
+    if (m * kRegThreads > j_from) continue;
+#pragma unroll
+    for (int r = 0; r < kRegKeys; ++r)
+      if ((r & m) == 0) compare_exchange(key[r], key[r | m], ((tile_global + r * kRegThreads + t) & k) == 0);
+  }
+}
+
+__device__ __forceinline__ void layout_b_to_s(unsigned long long (&key)[kRegKeys], unsigned long long* tile, int t) {
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) tile[swizzled(t * kRegKeys + r)] = key[r];
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) key[r] = tile[swizzled(r * kRegThreads + t)];
+  __syncthreads();
+}
+__device__ __forceinline__ void layout_s_to_b(unsigned long long (&key)[kRegKeys], unsigned long long* tile, int t) {
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) tile[swizzled(r * kRegThreads + t)] = key[r];
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) key[r] = tile[swizzled(t * kRegKeys + r)];
+  __syncthreads();
+}
+
+// k_first == 2: sorts every 4096-key tile from scratch (phases 2 .. 4096).  k_first == k_last > 4096: the steps
+// j = 2048 .. 1 that finish a merge whose wide steps ran in global memory.
+__global__ void __launch_bounds__(kRegThreads)
+bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last) {
+  __shared__ unsigned long long tile[kTile];
+  const int64_t row = blockIdx.y, tile_global = int64_t(blockIdx.x) * kTile;
+  unsigned long long* base = keys + row * padded + tile_global;
+  const int t = threadIdx.x, lane = t & 31;
+  const int64_t first_global = tile_global + int64_t(t) * kRegKeys;   // layout B: global index of register 0
+  unsigned long long key[kRegKeys];
+  if (k_first > kTile) {
+    // a merge: coalesced loads give layout S directly
+#pragma unroll
+    for (int r = 0; r < kRegKeys; ++r) key[r] = base[r * kRegThreads + t];
+    steps_in_registers_s(key, tile_global, t, k_first, kTile / 2);
+    layout_s_to_b(key, tile, t);
+    steps_by_shuffle_b(key, first_global, k_first, 256, lane);
+    steps_in_registers_b(key, first_global, k_first, 8);
+  } else {
+    const uint4* in = reinterpret_cast<const uint4*>(base + t * kRegKeys);
+#pragma unroll
+    for (int r = 0; r < kRegKeys; r += 2) {
+      const uint4 v = in[r >> 1];
+      key[r] = (static_cast<unsigned long long>(v.y) << 32) | v.x;
+      key[r + 1] = (static_cast<unsigned long long>(v.w) << 32) | v.z;
+    }
+    for (int64_t k = k_first; k <= k_last; k <<= 1) {
+      const int top = int(k >> 1);
+      if (top >= 512) {
+        layout_b_to_s(key, tile, t);
+        steps_in_registers_s(key, tile_global, t, k, top);
+        layout_s_to_b(key, tile, t);
+      }
+      if (top >= 16) steps_by_shuffle_b(key, first_global, k, top < 256 ? top : 256, lane);
+      steps_in_registers_b(key, first_global, k, top < 8 ? top : 8);
+    }
+  }
+  uint4* out = reinterpret_cast<uint4*>(base + t * kRegKeys);
+#pragma unroll
+  for (int r = 0; r < kRegKeys; r += 2)
+    out[r >> 1] = make_uint4(uint32_t(key[r]), uint32_t(key[r] >> 32), uint32_t(key[r + 1]), uint32_t(key[r + 1] >> 32));
+}
+
+// Two wide steps (j and j/2, both >= the tile) in one pass over global memory: the four elements that the two
+// steps connect are loaded once.
+__global__ void __launch_bounds__(256)
+bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j) {
+  const int64_t row = blockIdx.y, h = j >> 1;
+  unsigned long long* base = keys + row * padded;
+  for (int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < padded / 4; q += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t i = ((q & ~(h - 1)) << 2) | (q & (h - 1));   // bits j and j/2 clear
+    unsigned long long a0 = base[i], a1 = base[i + h], a2 = base[i + j], a3 = base[i + j + h];
+    const bool descending = (i & k) == 0;
+    compare_exchange(a0, a2, descending);
+    compare_exchange(a1, a3, descending);
+    compare_exchange(a0, a1, descending);
+    compare_exchange(a2, a3, descending);
+    base[i] = a0; base[i + h] = a1; base[i + j] = a2; base[i + j + h] = a3;
+  }
+}
+
 // ---- small top_k: radix select of the k-th largest key over all 64 bits (six digits of 11, 11, 11, 11,
 // 11 and 9 bits, most significant first).  Keys are unique (they carry the token index), so "every key
 // >= the k-th largest" is exactly k keys and the tie rule needs no special case.
@@ -210,13 +336,14 @@ select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const 
 }
 
 // ---- small top_k, the usual case: two passes over the LOGITS and no key array at all.
-//   pass 1  histogram of the top 11 bits of every token's order-preserving score bits
-//   cut     the highest bin b with (tokens in bins >= b) >= top_k
-//   pass 2  the keys of all tokens in bins >= b are gathered (a few hundred for a vocabulary of 150k)
+//   pass 1  histogram of the top 11 bits of every token's order-preserving LOGIT bits (no division)
+//   cut     one bin below the highest bin b with (tokens in bins >= b) >= top_k
+//   pass 2  the keys (exact scores) of all tokens in bins >= the cut are gathered: some hundreds of 150k
 //   finish  one thread block sorts the candidates and keeps the top_k largest
-// Exact whenever the candidates fit kCandidates; a row whose cut bin is too crowded (long runs of equal or
-// nearly equal scores) raises a flag, and the radix select over all 64 key bits above then redoes the
-// call (every stage of it is launched in any case and returns at once when the flag is down).
+// Exact whenever the candidates fit kCandidates and the division can neither overflow nor underflow near the
+// cut; otherwise (long runs of equal or nearly equal logits, an extreme temperature) a flag is raised and the
+// radix select over all 64 key bits above redoes the call (every stage of it is launched in any case and
+// returns at once when the flag is down).
 constexpr int kCandidates = 4096;
 
 struct CutState {            // per row
@@ -224,35 +351,66 @@ struct CutState {            // per row
   unsigned int taken;        // compaction cursor
 };
 
-__device__ __forceinline__ unsigned int score_bin(float score) {
-  const uint32_t b = __float_as_uint(score);
+// The bin of a LOGIT (top 11 bits of its order-preserving bit pattern: sign, exponent, two mantissa bits).
+// Scores are logits / temperature with temperature > 0, a monotonic map, so the k largest scores belong to
+// tokens whose logits lie at or just below the k largest logits; binning the logits spares a division per token.
+__device__ __forceinline__ unsigned int logit_bin(float x) {
+  const uint32_t b = __float_as_uint(x);
   return ((b & 0x80000000u) ? ~b : (b | 0x80000000u)) >> 21;
+}
+// exponent field of the values of a bin
+__device__ __forceinline__ unsigned int bin_exponent(unsigned int bin) {
+  return (bin & 0x400u) ? ((bin >> 2) & 0xffu) : (~(bin >> 2) & 0xffu);
+}
+
+// f(value, index) for every element of a row, 16-byte loads when the row allows, blocks of the grid's x dimension
+// striding over the row
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& f) {
+  constexpr int N = Elem<T>::kPerVec;
+  const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x, stride = int64_t(gridDim.x) * blockDim.x;
+  if (aligned16(src)) {
+    const int64_t nvec = width / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    for (int64_t v = first; v < nvec; v += stride) {
+      float e[N];
+      Elem<T>::unpack(ld_stream(vp + v), e);
+#pragma unroll
+      for (int q = 0; q < N; ++q) f(e[q], v * N + q);
+    }
+    for (int64_t i = nvec * N + first; i < width; i += stride) f(Elem<T>::load(src + i), i);
+  } else {
+    for (int64_t i = first; i < width; i += stride) f(Elem<T>::load(src + i), i);
+  }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-topk_histogram_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, unsigned int* histograms) {
+topk_histogram_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int* histograms) {
   __shared__ unsigned int local[kSelectBins];
   const int64_t row = blockIdx.y;
   for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x) local[b] = 0u;
   __syncthreads();
-  const T* src = logits + row * row_stride;
   const int lane = threadIdx.x & 31;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
-    const unsigned int bin = score_bin(__fdiv_rn(Elem<T>::load(src + i), temperature));
-    // scores crowd into a few dozen bins: lanes with the same bin add once, through their lowest lane
+  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t) {
+    const unsigned int bin = logit_bin(x);
+    // logits crowd into a few dozen bins: lanes with the same bin add once, through their lowest lane
     const unsigned int same = __match_any_sync(__activemask(), bin);
     if (lane == __ffs(int(same)) - 1) atomicAdd(&local[bin], unsigned(__popc(same)));
-  }
+  });
   __syncthreads();
   unsigned int* out = histograms + row * kSelectBins;
   for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x)
     if (local[b] != 0u) atomicAdd(&out[b], local[b]);
 }
 
-// one thread block per row: suffix counts from the top bin down, 8 bins per thread
+// One thread block per row: suffix counts from the top bin down, 8 bins per thread.  The cut is the bin that
+// holds the k-th largest logit MINUS ONE: a token whose score equals the k-th largest score has a logit within a
+// rounding error of the k-th largest logit, which one whole bin (a quarter of the magnitude) more than covers --
+// as long as logits / temperature neither overflows nor underflows near the cut, which `safe` (set by the host
+// from the temperature) and the cut bin's exponent guarantee; otherwise the exact fallback is asked for.
 __global__ void __launch_bounds__(256)
-topk_cut_kernel(unsigned int top_k, CutState* cut, unsigned int* histograms) {
+topk_cut_kernel(unsigned int top_k, int safe, CutState* cut, unsigned int* histograms, int* overflow) {
   __shared__ unsigned int counts[kSelectBins];
   __shared__ unsigned int group_sum[256], above_group[256];
   const int64_t row = blockIdx.x;
@@ -283,7 +441,12 @@ topk_cut_kernel(unsigned int top_k, CutState* cut, unsigned int* histograms) {
   if (above < top_k && above + group_sum[t] >= top_k) {
     for (int b = 7; b >= 0; --b) {
       above += counts[t * 8 + b];
-      if (above >= top_k) { cut[row].cut_bin = unsigned(t * 8 + b); break; }
+      if (above >= top_k) {
+        const unsigned int bin = unsigned(t * 8 + b), exponent = bin_exponent(bin);
+        cut[row].cut_bin = bin > 0u ? bin - 1u : 0u;
+        if (!safe || exponent < 28u || exponent > 226u) atomicExch(overflow, 1);
+        break;
+      }
     }
   }
   if (t == 0) cut[row].taken = 0u;
@@ -294,16 +457,14 @@ __global__ void __launch_bounds__(256)
 topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, CutState* cut,
                    unsigned long long* candidates) {
   const int64_t row = blockIdx.y;
-  const T* src = logits + row * row_stride;
   const unsigned int cut_bin = cut[row].cut_bin;
   unsigned long long* out = candidates + row * int64_t(kCandidates);
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
-    const float score = __fdiv_rn(Elem<T>::load(src + i), temperature);
-    if (score_bin(score) >= cut_bin) {
+  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t i) {
+    if (logit_bin(x) >= cut_bin) {
       const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
-      if (slot < unsigned(kCandidates)) out[slot] = sample_key(score, uint32_t(i));
+      if (slot < unsigned(kCandidates)) out[slot] = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
     }
-  }
+  });
 }
 
 // Sorts one row's candidates in shared memory, descending, and leaves the top_k largest at the front of the
@@ -357,16 +518,27 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
   const float maximum = key_score(sorted[0]);
   const int tid = threadIdx.x;
 
-  // running sums cum[i] = e_0 + ... + e_i, added in order by one thread
-  if (tid == 0) carry = 0.0f;
+  // running sums cum[i] = e_0 + ... + e_i, added in order by one thread.  The terms come in descending order, so
+  // once adding the smallest term seen so far no longer changes the fp32 sum, no later term can (rounding is
+  // monotonic): from there on every running sum equals the current one, exactly as the serial walk would find,
+  // and the rest of the row is filled in parallel.
+  __shared__ int frozen;
+  if (tid == 0) { carry = 0.0f; frozen = 0; }
+  __syncthreads();
   for (int64_t base = 0; base < limit; base += kChunk) {
     const int n = int(limit - base < kChunk ? limit - base : kChunk);
+    if (frozen) {
+      const float settled = carry;
+      for (int j = tid; j < n; j += kSelectThreads) cum[base + j] = settled;
+      continue;                                   // `frozen` and `carry` no longer change: no barrier needed
+    }
     for (int j = tid; j < n; j += kSelectThreads) stage[j] = expf(key_score(sorted[base + j]) - maximum);
     __syncthreads();
     if (tid == 0) {
-      float sum = carry;
-      for (int j = 0; j < n; ++j) { sum += stage[j]; stage[j] = sum; }
+      float sum = carry, term = 0.0f;
+      for (int j = 0; j < n; ++j) { term = stage[j]; sum += term; stage[j] = sum; }
       carry = sum;
+      if (sum + term == sum) frozen = 1;
     }
     __syncthreads();
     for (int j = tid; j < n; j += kSelectThreads) cum[base + j] = stage[j];
@@ -375,10 +547,12 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
   const float total = carry;
   __syncthreads();   // everyone has read the total before thread 0 reuses `carry`
 
-  // top-p: the shortest prefix whose normalised mass, added term by term, reaches top_p
+  // top-p: the shortest prefix whose normalised mass, added term by term, reaches top_p.  The same argument ends
+  // the walk early: once the smallest quotient seen so far no longer moves the running mass, it stays below top_p
+  // for good and the prefix is everything, as the serial walk would conclude after visiting every token.
   int64_t prefix = limit;
   if (top_p < 1.0f) {
-    if (tid == 0) { carry = 0.0f; found = -1; }
+    if (tid == 0) { carry = 0.0f; found = -1; frozen = 0; }
     __syncthreads();
     for (int64_t base = 0; base < limit; base += kChunk) {
       const int n = int(limit - base < kChunk ? limit - base : kChunk);
@@ -386,15 +560,18 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
         stage[j] = __fdiv_rn(expf(key_score(sorted[base + j]) - maximum), total);
       __syncthreads();
       if (tid == 0) {
-        float cumulative = carry;
+        float cumulative = carry, term = 0.0f;
         for (int j = 0; j < n; ++j) {
-          cumulative += stage[j];
+          term = stage[j];
+          cumulative += term;
           if (cumulative >= top_p) { found = j; break; }
         }
         carry = cumulative;
+        if (found < 0 && cumulative + term == cumulative) frozen = 1;
       }
       __syncthreads();
       if (found >= 0) { prefix = base + found + 1; break; }
+      if (frozen) break;
     }
   }
   __syncthreads();
@@ -470,15 +647,18 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     // only the k largest keys matter.  Two passes over the logits find them ...
     if (cudaMemsetAsync(histograms, 0, size_t(rows) * (size_t(kSelectBins) * 4 + sizeof(CutState)) + 16, s) != cudaSuccess)
       return launch_status("sample_rows");
+    // logits / temperature stays a normal number near the cut only for a moderate temperature (and a moderate
+    // logit at the cut, which the cut kernel checks)
+    const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
-      topk_histogram_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, histograms);
-      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), cut, histograms);
+      topk_histogram_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, histograms);
+      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), safe, cut, histograms, overflow);
       topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
     } else {
       const __half* x = static_cast<const __half*>(logits);
-      topk_histogram_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, histograms);
-      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), cut, histograms);
+      topk_histogram_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, histograms);
+      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), safe, cut, histograms, overflow);
       topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
     }
     topk_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, cut, candidates, overflow);
@@ -499,11 +679,16 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     make_keys(nullptr);
     const int tile = int(padded < kTile ? padded : kTile);
     const dim3 tile_grid(unsigned(padded / tile), unsigned(rows));
-    const size_t smem = size_t(tile) * 8;
-    bitonic_tile_kernel<<<tile_grid, kSortThreads, smem, s>>>(keys, padded, tile, 2, tile);
-    for (int64_t k = int64_t(tile) * 2; k <= padded; k <<= 1) {
-      for (int64_t j = k >> 1; j >= tile; j >>= 1) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);
-      bitonic_tile_kernel<<<tile_grid, kSortThreads, smem, s>>>(keys, padded, tile, k, k);
+    if (tile < kTile) {
+      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile);   // the whole row is one small tile
+    } else {
+      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile);
+      for (int64_t k = int64_t(kTile) * 2; k <= padded; k <<= 1) {
+        int64_t j = k >> 1;
+        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);   // steps j and j/2
+        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);                         // one step left over
+        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k);
+      }
     }
   }
   sampler_pick_kernel<<<unsigned(rows), kSelectThreads, 0, s>>>(keys, width, padded, top_k, top_p, seed, draw_offsets, running,

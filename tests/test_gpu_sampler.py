@@ -114,6 +114,27 @@ def test_every_row_equals_the_references_own_sampler_and_the_restatement(b2, por
     assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize("temperature", [1e-7, 3e7])
+def test_extreme_temperatures_take_the_exact_path(b2, port, temperature):
+    """logits / temperature overflows (tiny temperature) or flushes towards zero (huge): scores of different logits
+    collapse and the index order decides, which only the exact select over the true scores gets right."""
+    refcu = oracle.ref_cuda()
+    rows, width = 4, 151936
+    x = rows_for(width, rows, 99, np.float32, "plain")
+    x[0, :20000] *= 1e32                         # overflows to +-inf at the small temperature
+    x[1] *= 1e-33                                # denormal scores at the large temperature
+    t = dev(x)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    offsets = np.arange(rows, dtype=np.int64) + 3
+    for cfg in (SamplingConfig(temperature, 50, 1.0, 5), SamplingConfig(temperature, 7, 0.9, 6)):
+        ops.sample_rows_out(t, cfg, dev(offsets), out)
+        got = host(out)
+        for r in range(rows):
+            if refcu is not None:
+                want = refcu.sample_row(t, rows, width, 0, r, cfg.temperature, cfg.top_k, cfg.top_p, cfg.seed, int(offsets[r]))
+                assert int(got[r]) == want, f"row {r} {cfg}: {int(got[r])} vs the reference's {want}"
+
+
 def test_draws_follow_the_retained_distribution(b2, port):
     """Frequencies over many draw offsets match the truncated, renormalised softmax (a property the
     reference's tests do not check, independent of any oracle)."""
