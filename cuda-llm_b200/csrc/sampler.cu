@@ -9,11 +9,11 @@
 // What changes is how the order and the sums are produced:
 //   keys     one 64-bit key per token, (order-preserving bits of the score) << 32 | ~index, so one
 //            unsigned sort gives the reference's order including its tie rule
-//   sort     when 0 < top_k <= 2048 only the k largest keys matter: one pass over the logits histograms
-//            the top bits of the scores, a second pass gathers the few hundred tokens at or above the bin
-//            that holds the k-th largest, and one thread block sorts those in shared memory (rows with too
-//            many near-equal scores fall back to a radix select over all 64 key bits); otherwise a bitonic
-//            network sorts the whole row (4096-key tiles in shared memory, wider steps in global memory)
+//   sort     when 0 < top_k <= 2048 only the k largest keys matter: a threshold taken from a sorted sample of
+//            the row, ONE pass over the logits that gathers the few hundred tokens above it, and a one-block
+//            sort of those (checked; a call whose sample misled it is redone by a radix select over all 64
+//            key bits); otherwise a bitonic network sorts the whole row (keys in registers, 4096-key tiles,
+//            wider steps in global memory)
 //   select   one thread block per row: the exponentials of a 2048-token chunk are computed in
 //            parallel, one thread adds them in order (the only serial part left) and records the
 //            running sums; the top-p cut walks the same way and stops at the crossing; the final pick
@@ -335,32 +335,34 @@ select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const 
   for (int i = threadIdx.x; i < top_k; i += kSortThreads) dst[i] = buf[i];
 }
 
-// ---- small top_k, the usual case: two passes over the LOGITS and no key array at all.
-//   pass 1  histogram of the top 11 bits of every token's order-preserving LOGIT bits (no division)
-//   cut     one bin below the highest bin b with (tokens in bins >= b) >= top_k
-//   pass 2  the keys (exact scores) of all tokens in bins >= the cut are gathered: some hundreds of 150k
-//   finish  one thread block sorts the candidates and keeps the top_k largest
-// Exact whenever the candidates fit kCandidates and the division can neither overflow nor underflow near the
-// cut; otherwise (long runs of equal or nearly equal logits, an extreme temperature) a flag is raised and the
-// radix select over all 64 key bits above redoes the call (every stage of it is launched in any case and
-// returns at once when the flag is down).
-constexpr int kCandidates = 4096;
+// ---- small top_k, the usual case: ONE pass over the logits and no key array.
+//   splitter  a thread block per row sorts 2048 evenly spaced logits of the row and takes, as threshold, the
+//             sample whose rank makes "about 6 x top_k, and with near certainty at least top_k" tokens of the
+//             whole row lie above it, lowered by 2^-12 of its magnitude
+//   gather    the one pass: every token whose logit is at or above the threshold has its exact score computed and
+//             its key appended to the row's candidate list (a few hundred of 150k tokens)
+//   finish    one thread block checks the count, sorts the candidates and keeps the top_k largest
+// The result is exact or the call is redone: when a row ends with fewer than top_k or more than kCandidates
+// candidates (unlucky sample, long runs of equal logits), or when logits / temperature could overflow or lose
+// precision near the threshold (then equal scores may hide behind different logits), a flag is raised and the
+// radix select over all 64 key bits above redoes every row; its stages are launched in any case and return at
+// once when the flag is down.  The margin covers the tokens whose score can equal the top_k-th score although
+// their logit is smaller: scores are logits / temperature, a monotonic map with a relative rounding error of
+// 2^-24.  A NaN logit also sends the call to the exact select (whose key order ranks NaNs as the reference's sort does).
+constexpr int kCandidates = 8192;
+constexpr int kSplitSamples = 2048;
 
 struct CutState {            // per row
-  unsigned int cut_bin;      // candidates are the tokens whose bin is >= this
+  float threshold;           // candidates are the tokens whose logit is >= this
   unsigned int taken;        // compaction cursor
 };
 
-// The bin of a LOGIT (top 11 bits of its order-preserving bit pattern: sign, exponent, two mantissa bits).
-// Scores are logits / temperature with temperature > 0, a monotonic map, so the k largest scores belong to
-// tokens whose logits lie at or just below the k largest logits; binning the logits spares a division per token.
-__device__ __forceinline__ unsigned int logit_bin(float x) {
+__device__ __forceinline__ uint32_t ordered_bits(float x) {
   const uint32_t b = __float_as_uint(x);
-  return ((b & 0x80000000u) ? ~b : (b | 0x80000000u)) >> 21;
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-// exponent field of the values of a bin
-__device__ __forceinline__ unsigned int bin_exponent(unsigned int bin) {
-  return (bin & 0x400u) ? ((bin >> 2) & 0xffu) : (~(bin >> 2) & 0xffu);
+__device__ __forceinline__ float from_ordered_bits(uint32_t o) {
+  return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
 }
 
 // f(value, index) for every element of a row, 16-byte loads when the row allows, blocks of the grid's x dimension
@@ -386,96 +388,72 @@ __device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& 
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-topk_histogram_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int* histograms) {
-  __shared__ unsigned int local[kSelectBins];
-  const int64_t row = blockIdx.y;
-  for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x) local[b] = 0u;
-  __syncthreads();
-  const int lane = threadIdx.x & 31;
-  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t) {
-    const unsigned int bin = logit_bin(x);
-    // logits crowd into a few dozen bins: lanes with the same bin add once, through their lowest lane
-    const unsigned int same = __match_any_sync(__activemask(), bin);
-    if (lane == __ffs(int(same)) - 1) atomicAdd(&local[bin], unsigned(__popc(same)));
-  });
-  __syncthreads();
-  unsigned int* out = histograms + row * kSelectBins;
-  for (int b = threadIdx.x; b < kSelectBins; b += blockDim.x)
-    if (local[b] != 0u) atomicAdd(&out[b], local[b]);
-}
-
-// One thread block per row: suffix counts from the top bin down, 8 bins per thread.  The cut is the bin that
-// holds the k-th largest logit MINUS ONE: a token whose score equals the k-th largest score has a logit within a
-// rounding error of the k-th largest logit, which one whole bin (a quarter of the magnitude) more than covers --
-// as long as logits / temperature neither overflows nor underflows near the cut, which `safe` (set by the host
-// from the temperature) and the cut bin's exponent guarantee; otherwise the exact fallback is asked for.
-__global__ void __launch_bounds__(256)
-topk_cut_kernel(unsigned int top_k, int safe, CutState* cut, unsigned int* histograms, int* overflow) {
-  __shared__ unsigned int counts[kSelectBins];
-  __shared__ unsigned int group_sum[256], above_group[256];
+topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int top_k, int safe, CutState* cut,
+                     int* overflow) {
+  __shared__ uint32_t sample[kSplitSamples];
   const int64_t row = blockIdx.x;
-  unsigned int* hist = histograms + row * kSelectBins;
-  const int t = threadIdx.x;
-  for (int b = t; b < kSelectBins; b += 256) { counts[b] = hist[b]; hist[b] = 0u; }   // left cleared for the next user
-  __syncthreads();
-  unsigned int sum = 0;
-  for (int b = 0; b < 8; ++b) sum += counts[t * 8 + b];
-  group_sum[t] = sum;
-  // above_group[t] = tokens in the groups above t: suffix sums inside each warp by shuffles, then the warps above
-  unsigned int suffix = sum;                       // inclusive, over lanes >= this one
-  const int lane = t & 31, warp = t >> 5;
-#pragma unroll
-  for (int offset = 1; offset < 32; offset <<= 1) {
-    const unsigned int other = __shfl_down_sync(0xffffffffu, suffix, offset);
-    if (lane + offset < 32) suffix += other;
+  const T* src = logits + row * row_stride;
+  for (int s = threadIdx.x; s < kSplitSamples; s += 256) {
+    const float x = Elem<T>::load(src + (int64_t(s) * width) / kSplitSamples);   // width > kSplitSamples: distinct tokens
+    sample[s] = x == x ? ordered_bits(x) : 0u;                                     // a NaN never ranks
   }
-  __shared__ unsigned int warp_total[8];
-  if (lane == 0) warp_total[warp] = suffix;
   __syncthreads();
-  unsigned int higher = 0;
-  for (int w = warp + 1; w < 8; ++w) higher += warp_total[w];
-  above_group[t] = higher + suffix - sum;
-  __syncthreads();
-  // exactly one thread owns the bin where the count from the top first reaches top_k
-  unsigned int above = above_group[t];
-  if (above < top_k && above + group_sum[t] >= top_k) {
-    for (int b = 7; b >= 0; --b) {
-      above += counts[t * 8 + b];
-      if (above >= top_k) {
-        const unsigned int bin = unsigned(t * 8 + b), exponent = bin_exponent(bin);
-        cut[row].cut_bin = bin > 0u ? bin - 1u : 0u;
-        if (!safe || exponent < 28u || exponent > 226u) atomicExch(overflow, 1);
-        break;
+  for (int k = 2; k <= kSplitSamples; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int p = threadIdx.x; p < kSplitSamples / 2; p += 256) {
+        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+        const uint32_t a = sample[i], b = sample[i | j];
+        if ((a < b) == ((i & k) == 0)) { sample[i] = b; sample[i | j] = a; }
       }
+      __syncthreads();
     }
   }
-  if (t == 0) cut[row].taken = 0u;
+  if (threadIdx.x != 0) return;
+  // expected rank of the top_k-th token among the samples, plus three standard deviations and two
+  const float expected = float(top_k) * float(kSplitSamples) / float(width);
+  int rank = int(ceilf(expected + 3.0f * sqrtf(expected))) + 2;
+  bool ok = safe != 0 && rank < kSplitSamples;
+  float threshold = -INFINITY;
+  if (ok) {
+    const float at_rank = from_ordered_bits(sample[rank]);
+    const unsigned int exponent = (__float_as_uint(at_rank) >> 23) & 0xffu;
+    ok = exponent >= 28u && exponent <= 226u;            // 2^-99 .. 2^99: the division stays exact to rounding
+    threshold = at_rank - 0.000244140625f * fabsf(at_rank);   // 2^-12 of the magnitude: 4096 rounding errors of the division
+  }
+  if (!ok) atomicExch(overflow, 1);
+  cut[row].threshold = threshold;
+  cut[row].taken = 0u;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, CutState* cut,
-                   unsigned long long* candidates) {
+                   unsigned long long* candidates, const int* overflow) {
+  if (*overflow != 0) return;                      // the call is being redone by the exact select anyway
   const int64_t row = blockIdx.y;
-  const unsigned int cut_bin = cut[row].cut_bin;
+  const float threshold = cut[row].threshold;
   unsigned long long* out = candidates + row * int64_t(kCandidates);
+  bool strange = false;
   for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t i) {
-    if (logit_bin(x) >= cut_bin) {
+    if (x >= threshold) {
       const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
       if (slot < unsigned(kCandidates)) out[slot] = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
     }
+    strange |= x != x;
   });
+  if (strange) atomicExch(const_cast<int*>(overflow), 1);
 }
 
 // Sorts one row's candidates in shared memory, descending, and leaves the top_k largest at the front of the
-// row's key area; more candidates than fit raise *overflow (the exact fallback then overwrites every row).
+// row's key area; too few or too many candidates raise *overflow (the exact fallback then overwrites every row).
 __global__ void __launch_bounds__(kSortThreads)
 topk_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const CutState* cut,
                    const unsigned long long* candidates, int* overflow) {
-  __shared__ unsigned long long buf[kCandidates];
+  extern __shared__ unsigned long long buf[];
   const int64_t row = blockIdx.x;
   const unsigned int count = cut[row].taken;
-  if (count > unsigned(kCandidates)) {
+  if (*overflow != 0) return;
+  if (count < unsigned(top_k) || count > unsigned(kCandidates)) {
     if (threadIdx.x == 0) atomicExch(overflow, 1);
     return;
   }
@@ -644,25 +622,27 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
   };
 
   if (top_k > 0 && top_k <= kMaxSelectK && width > kTile) {
-    // only the k largest keys matter.  Two passes over the logits find them ...
+    // only the k largest keys matter: a sampled threshold, one pass over the logits, a small sort ...
     if (cudaMemsetAsync(histograms, 0, size_t(rows) * (size_t(kSelectBins) * 4 + sizeof(CutState)) + 16, s) != cudaSuccess)
       return launch_status("sample_rows");
-    // logits / temperature stays a normal number near the cut only for a moderate temperature (and a moderate
-    // logit at the cut, which the cut kernel checks)
+    // logits / temperature stays a normal number near the threshold only for a moderate temperature (and a
+    // moderate logit there, which the splitter kernel checks)
     const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
+    static const bool finish_ready = [] {
+      return cudaFuncSetAttribute(topk_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) == cudaSuccess;
+    }();
+    if (!finish_ready) { cudaGetLastError(); set_error("sample_rows: cannot reserve shared memory"); return B2_ERR_CUDA; }
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
-      topk_histogram_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, histograms);
-      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), safe, cut, histograms, overflow);
-      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
+      topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow);
+      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow);
     } else {
       const __half* x = static_cast<const __half*>(logits);
-      topk_histogram_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, histograms);
-      topk_cut_kernel<<<unsigned(rows), 256, 0, s>>>(unsigned(top_k), safe, cut, histograms, overflow);
-      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates);
+      topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow);
+      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow);
     }
-    topk_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, cut, candidates, overflow);
-    // ... unless a row's cut bin was too crowded: then (and only then) the radix select over all 64 key bits runs
+    topk_finish_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, top_k, cut, candidates, overflow);
+    // ... unless that could not be trusted: then (and only then) the radix select over all 64 key bits runs
     make_keys(overflow);
     select_init_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(state, rows, unsigned(top_k), overflow);
     const int shifts[kSelectRounds] = {53, 42, 31, 20, 9, 0}, widths[kSelectRounds] = {11, 11, 11, 11, 11, 9};

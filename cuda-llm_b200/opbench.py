@@ -128,13 +128,13 @@ def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
         ids = torch.empty(R, dtype=torch.int32, device=dev)
         offs = torch.arange(R, dtype=torch.int64, device=dev)
         ws = torch.empty(L.b2_sampler_workspace_bytes(R, VOCAB), dtype=torch.uint8, device=dev)
-        for label, temp, top_k, top_p in (("top_k=50 top_p=0.95 (radix select)", 0.8, 50, 0.95),
+        for label, temp, top_k, top_p in (("top_k=50 top_p=0.95 (sampled threshold, one pass)", 0.8, 50, 0.95),
                                           ("top_k=0 top_p=0.9 (whole-vocabulary sort)", 1.0, 0, 0.9)):
             calls = [(lambda x=x: lib.check(L.b2_sample_rows(x.data_ptr(), R, VOCAB, VOCAB, F32, temp, top_k, top_p, 7,
                                                              offs.data_ptr(), ids.data_ptr(), ws.data_ptr(), s))) for x in logits]
             ms = timed(calls, nreps(6), warm=2)
             record(f"sample_rows {label}", f"{R}x{VOCAB} f32", R * VOCAB * 4 + 12 * R, ms, R,
-                   note="bytes = the logits read once; the ordered fp32 sums (one thread per row) set the time, not HBM")
+                   note="bytes = the logits read once; launches and the ordered fp32 sums set the time, not HBM")
         del logits, ws
     if want("kvmove"):
         half = torch.float16

@@ -62,9 +62,12 @@ def test_reference_sampler_test_cases(b2):
         sampler.sample_last_row(xf, SamplingConfig(temperature=1, top_k=1, top_p=0), 0)
 
 
+# top_k values on both sides of every path boundary: 1, small (sampled threshold), 2048 (largest for that path),
+# 3000 (whole-row sort), 0 (everything)
 CONFIGS = [SamplingConfig(1.0, 0, 1.0, 11), SamplingConfig(0.7, 50, 1.0, 12), SamplingConfig(1.3, 0, 0.9, 13),
            SamplingConfig(0.8, 40, 0.95, 14), SamplingConfig(1.0, 2048, 0.5, 15), SamplingConfig(2.0, 3000, 0.999, 16),
-           SamplingConfig(1.0, 1, 1.0, 17), SamplingConfig(0.5, 0, 0.3, 18)]
+           SamplingConfig(1.0, 1, 1.0, 17), SamplingConfig(0.5, 0, 0.3, 18), SamplingConfig(1.1, 700, 0.98, 19),
+           SamplingConfig(0.9, 2048, 1.0, 20), SamplingConfig(1.0, 5, 0.7, 21)]
 
 
 def rows_for(width, rows, seed, dtype, kind="ties"):
