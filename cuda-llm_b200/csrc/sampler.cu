@@ -176,22 +176,16 @@ bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t 
   const int t = threadIdx.x, lane = t & 31;
   const int64_t first_global = tile_global + int64_t(t) * kRegKeys;   // layout B: global index of register 0
   unsigned long long key[kRegKeys];
-  if (k_first > kTile) {
-    // a merge: coalesced loads give layout S directly
+  // global memory is always read and written in layout S: a warp's 32 lanes touch 256 consecutive bytes
 #pragma unroll
-    for (int r = 0; r < kRegKeys; ++r) key[r] = base[r * kRegThreads + t];
+  for (int r = 0; r < kRegKeys; ++r) key[r] = base[r * kRegThreads + t];
+  if (k_first > kTile) {
     steps_in_registers_s(key, tile_global, t, k_first, kTile / 2);
     layout_s_to_b(key, tile, t);
     steps_by_shuffle_b(key, first_global, k_first, 256, lane);
     steps_in_registers_b(key, first_global, k_first, 8);
   } else {
-    const uint4* in = reinterpret_cast<const uint4*>(base + t * kRegKeys);
-#pragma unroll
-    for (int r = 0; r < kRegKeys; r += 2) {
-      const uint4 v = in[r >> 1];
-      key[r] = (static_cast<unsigned long long>(v.y) << 32) | v.x;
-      key[r + 1] = (static_cast<unsigned long long>(v.w) << 32) | v.z;
-    }
+    layout_s_to_b(key, tile, t);
     for (int64_t k = k_first; k <= k_last; k <<= 1) {
       const int top = int(k >> 1);
       if (top >= 512) {
@@ -203,10 +197,9 @@ bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t 
       steps_in_registers_b(key, first_global, k, top < 8 ? top : 8);
     }
   }
-  uint4* out = reinterpret_cast<uint4*>(base + t * kRegKeys);
+  layout_b_to_s(key, tile, t);
 #pragma unroll
-  for (int r = 0; r < kRegKeys; r += 2)
-    out[r >> 1] = make_uint4(uint32_t(key[r]), uint32_t(key[r] >> 32), uint32_t(key[r + 1]), uint32_t(key[r + 1] >> 32));
+  for (int r = 0; r < kRegKeys; ++r) base[r * kRegThreads + t] = key[r];
 }
 
 // Two wide steps (j and j/2, both >= the tile) in one pass over global memory: the four elements that the two
