@@ -106,8 +106,9 @@ select_last_valid_kernel(const unsigned char* padded, const int32_t* valid_lengt
   }
 }
 
+// one warp per row (or row part) and as many blocks as that takes: blocks dispatched in order walk memory in order
 unsigned grid_for(int64_t warps_wanted) {
-  const int64_t ctas = (warps_wanted + kWarps - 1) / kWarps, cap = int64_t(sm_count()) * 8;
+  const int64_t ctas = (warps_wanted + kWarps - 1) / kWarps, cap = 0x7fffffffll;
   return unsigned(ctas < 1 ? 1 : (ctas < cap ? ctas : cap));
 }
 
