@@ -29,8 +29,15 @@ void to_device(const Tensor& t, void* p) {
   CUDA_CHECK(cudaMemcpy(p, t.data(), t.nbytes(), cudaMemcpyDeviceToDevice));
   CUDA_CHECK(cudaDeviceSynchronize());
 }
+// Every door first waits for the device: the reference runs on the per-thread default stream, which does not
+// order itself after a caller's non-blocking stream, and its kernels trust what they read (the embedding kernel
+// dereferences any id), so inputs still being written by the caller must have landed before they are copied.
 template <class F> int guarded(F&& f) {
-  try { f(); return 0; } catch (const std::invalid_argument&) { return -1; } catch (const std::exception&) { return -2; }
+  try {
+    CUDA_CHECK(cudaDeviceSynchronize());
+    f();
+    return 0;
+  } catch (const std::invalid_argument&) { return -1; } catch (const std::exception&) { return -2; }
 }
 // milliseconds per call of `f`, CUDA events on the per-thread default stream (where the reference launches)
 template <class F> float timed(F&& f, int reps) {
@@ -211,6 +218,7 @@ REFCU_API int refcu_sample_row(const void* logits, int64_t rows, int64_t vocab, 
 REFCU_API float refcu_time_sample_row(const void* logits, int64_t rows, int64_t vocab, int dtype, float temperature, int32_t top_k,
                                       float top_p, int reps) {
   try {
+    CUDA_CHECK(cudaDeviceSynchronize());
     llm::CudaSampler sampler{static_cast<size_t>(vocab)};
     llm::SamplingConfig config;
     config.temperature = temperature;
