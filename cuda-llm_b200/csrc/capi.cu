@@ -232,6 +232,25 @@ int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out_ids, b
   return launch_argmax_decode(keys, rows, out_ids, as_stream(stream));
 }
 
+int b2_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab, int dtype,
+                      int mode, int64_t index_base, void* logits_out, int64_t logits_stride, int32_t* out_ids,
+                      int64_t* out_keys, void* workspace, b2_stream stream) {
+  const char* op = "b2_lm_head_argmax";
+  B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
+  B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
+  B2_REQUIRE(rows >= 0 && rows < (1 << 24), op, "rows must be >= 0");
+  B2_REQUIRE(hidden_size > 0 && vocab > 0 && vocab <= 0x7fffffffll && fits(vocab, hidden_size), op,
+             "hidden_size and vocab must be > 0 and vocab must fit int32");
+  B2_REQUIRE(hidden_size <= 8192, op, "hidden_size must be <= 8192");
+  B2_REQUIRE(index_base >= 0 && index_base + vocab <= 0xffffffffll, op, "global indices must fit 32 bits");
+  B2_REQUIRE(logits_out == nullptr || (logits_stride >= vocab && fits(rows > 0 ? rows : 1, logits_stride)), op,
+             "logits_stride must be >= vocab");
+  B2_REQUIRE(logits_out || out_ids || out_keys, op, "no output given");
+  B2_REQUIRE(rows == 0 || (hidden && table && workspace), op, "null pointer");
+  return launch_lm_head_argmax(hidden, table, rows, hidden_size, vocab, dtype, mode, index_base, logits_out, logits_stride,
+                               out_ids, out_keys, workspace, as_stream(stream));
+}
+
 size_t b2_softmax_workspace_bytes(int64_t rows) { return rows > 0 ? softmax_workspace_bytes(rows) : 0; }
 
 int b2_softmax_rows(const void* x, void* out, int64_t rows, int64_t width, int dtype, int mode, void* workspace,

@@ -46,6 +46,11 @@ int launch_softmax_rebase(const float* row_max, const float* global_max, float* 
 int launch_softmax_apply(const void* x, void* out, int64_t rows, int64_t width, int dtype, const float* row_max,
                          const float* row_sum, cudaStream_t s);
 
+// lmhead.cu: logits = hidden x table^T for a few rows, fused with the row arg-max (one pass over the table)
+int launch_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab,
+                          int dtype, int mode, int64_t index_base, void* logits_out, int64_t logits_stride,
+                          int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s);
+
 // kvmove.cu: mode 0 = decode batch (one block table and one position per token), 1 = packed prefill (token t at
 // slot t of one block table), 2 = single decode (*positions is the cache length after the append)
 int launch_paged_kv_write(int mode, const void* key, const void* value, void* storage, const int32_t* block_tables,

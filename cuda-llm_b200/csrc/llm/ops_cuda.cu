@@ -356,6 +356,29 @@ void cuda_argmax_rows_out(const Tensor& logits, Tensor& ids, cudaStream_t stream
   check(b2_argmax_rows(logits.data(), rows, width, width, dtype_code(logits), static_cast<int32_t*>(ids.data()), ws, stream));
 }
 
+// Argument rules of the reference's cuda_lm_head (src/ops_cuda.cu:885), then one fused launch.
+void cuda_lm_head_argmax_out(const Tensor& hidden, const Tensor& embedding, Tensor& ids, Tensor* logits, cudaStream_t stream) {
+  const char* op = "cuda_lm_head";
+  if (hidden.device() != DeviceType::CUDA || embedding.device() != DeviceType::CUDA)
+    reject(op, "hidden and tied embedding must be CUDA");
+  if (hidden.shape().size() != 2 || embedding.shape().size() != 2) reject(op, "hidden and embedding must be rank-2");
+  if (hidden.shape().back() != embedding.shape()[1]) reject(op, "hidden_size mismatch");
+  if (hidden.dtype() != embedding.dtype()) reject(op, "all input dtypes must match");
+  if (hidden.dtype() != DType::F32 && hidden.dtype() != DType::F16) reject(op, "supports only F32/F16");
+  if (!hidden.is_contiguous() || !embedding.is_contiguous()) reject(op, "requires contiguous CUDA tensor");
+  const int64_t rows = hidden.shape()[0], hsz = hidden.shape()[1], vocab = embedding.shape()[0];
+  if (rows <= 0 || hsz <= 0 || vocab <= 0) reject(op, "shape dimensions must be > 0");
+  if (ids.device() != DeviceType::CUDA || ids.dtype() != DType::I32 || !ids.is_contiguous() ||
+      ids.shape() != std::vector<int64_t>{rows})
+    reject(op, "ids must be CUDA/I32 [rows]");
+  if (logits != nullptr && (logits->device() != DeviceType::CUDA || logits->dtype() != hidden.dtype() || !logits->is_contiguous() ||
+                            logits->shape() != std::vector<int64_t>{rows, vocab}))
+    reject(op, "logits must be CUDA [rows, vocab] of the inputs' dtype");
+  void* ws = scratch("argmax_rows").get(b2_argmax_workspace_bytes(rows), true);
+  check(b2_lm_head_argmax(hidden.data(), embedding.data(), rows, hsz, vocab, dtype_code(hidden), mode_code(), 0,
+                          logits ? logits->data() : nullptr, vocab, static_cast<int32_t*>(ids.data()), nullptr, ws, stream));
+}
+
 // ---------------------------------------------------------------- sampler
 
 // reference src/ops_cuda.cu:886-890.  The workspace (keys, running sums, one result slot, one draw offset)

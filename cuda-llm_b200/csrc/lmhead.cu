@@ -1,0 +1,371 @@
+// Decode-size LM head fused with the greedy pick: logits = hidden x table^T for a handful of
+// rows, and each row's arg-max, in ONE pass over the tied embedding table.
+//
+// Replaces, for decode batches, the reference's pair "cuda_lm_head / cuda_linear_out into a
+// [rows, vocab] logits tensor, then cuda_argmax_last_row" (reference include/llm/ops_cuda.h:154,157;
+// src/ops_cuda.cu:885; src/qwen3_cuda_model.cpp:1070-1071,1339).  With one to four rows the product
+// is bound by reading the table once (151936 x 1024 fp16 = 311 MB), not by arithmetic, so this is
+// streaming work for the CUDA cores like the rest of this library: no tensor cores, no library GEMM.
+// Writing the logits is optional; the pick never reads them back.
+//
+// Arithmetic.  fp32 accumulation of fp16 or fp32 storage; the logit is rounded to the storage type
+// before it is compared (the reference picks from the stored logits).  The pick follows the
+// reference's rule (src/ops_cuda.cu:562-563): largest value, ties to the lowest index, NaN never wins,
+// nothing comparable -> 0.  B2_DETERMINISTIC adds the products one by one in ascending k with a
+// separately rounded multiply, the order of the reference's CPU `linear` (src/ops_cpu.cpp:9) and,
+// for fp16 storage (where the product of two halves is exact in fp32), also of its
+// `linear_f16_reference` kernel (src/ops_cuda.cu:101-111).  B2_FAST splits k over the lanes of a
+// warp in a fixed order (run-to-run bit-identical).
+#include <cfloat>
+#include <climits>
+
+#include "b2ops.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b2 {
+namespace {
+
+constexpr int kLmThreads = 256;
+constexpr int kLmWarps = kLmThreads / kWarpSize;
+constexpr int kLmNone = INT_MAX;
+constexpr unsigned long long kLmSignBit = 0x8000000000000000ull;
+
+__device__ __forceinline__ bool lm_beats(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+// the packed key of b2_argmax_keys: unsigned order == (value ascending, index descending); 0 = nothing seen
+__device__ __forceinline__ unsigned long long lm_pack_key(float v, uint32_t global_index) {
+  const uint32_t b = __float_as_uint(v);
+  const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return (static_cast<unsigned long long>(ordered) << 32) | (0xffffffffu - global_index);
+}
+
+template <typename T> __device__ __forceinline__ float round_to_storage(float v);
+template <> __device__ __forceinline__ float round_to_storage<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_to_storage<__half>(float v) { return __half2float(__float2half(v)); }
+
+// Sums M values held by every lane over the 32 lanes with M-1 + log2(32/M) shuffles instead of 5*M:
+// at each of the first log2(M) steps a lane hands half of its values to its partner and keeps the
+// other half.  Afterwards v[0] of lane l is the total of value number l >> (5 - log2 M).
+template <int M>
+__device__ __forceinline__ void reduce_transpose(float (&v)[M], int lane) {
+  int offset = 16;
+#pragma unroll
+  for (int m = M; m > 1; m >>= 1) {
+    const int half = m >> 1;
+    const bool upper = (lane & offset) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, offset);
+    }
+    offset >>= 1;
+  }
+#pragma unroll
+  for (; offset > 0; offset >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], offset);
+}
+
+template <int M> struct Log2;
+template <> struct Log2<1> { static constexpr int value = 0; };
+template <> struct Log2<2> { static constexpr int value = 1; };
+template <> struct Log2<4> { static constexpr int value = 2; };
+template <> struct Log2<8> { static constexpr int value = 3; };
+
+// Folds the thread block's candidates (slots[warp][slot], `slots_per_row` slots for each of R rows,
+// slot = jj * R + r) into the call-wide keys, and lets the last block to arrive publish the result
+// and leave the scratch zeroed for the next call.
+template <int R>
+__device__ __forceinline__ void lm_publish(const float (*slot_v)[8], const int (*slot_i)[8], int warps, int slots_per_row,
+                                           int64_t index_base, int32_t* out_ids, int64_t* out_keys,
+                                           unsigned long long* keys, unsigned int* ticket) {
+  __shared__ int last_block;
+  if (threadIdx.x < R) {
+    const int r = threadIdx.x;
+    float bv = -FLT_MAX;
+    int bi = kLmNone;
+    for (int w = 0; w < warps; ++w)
+      for (int jj = 0; jj < slots_per_row; ++jj) {
+        const float v = slot_v[w][jj * R + r];
+        const int i = slot_i[w][jj * R + r];
+        if (lm_beats(v, i, bv, bi)) { bv = v; bi = i; }
+      }
+    if (bi != kLmNone) atomicMax(keys + r, lm_pack_key(bv, uint32_t(index_base + bi)));
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) last_block = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!last_block || threadIdx.x >= R) return;
+  __threadfence();
+  const int r = threadIdx.x;
+  const unsigned long long key = atomicExch(keys + r, 0ull);
+  if (out_keys != nullptr) out_keys[r] = static_cast<int64_t>(key ^ kLmSignBit);
+  if (out_ids != nullptr) out_ids[r] = key == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(key & 0xffffffffull));
+  if (r == 0) *ticket = 0u;
+}
+
+// ---------------------------------------------------------------------------
+// Fast kernel.  Persistent grid; a warp takes J table rows at a time (warp g of W takes rows
+// (g + i*W)*J .. +J-1, so at any moment the whole GPU reads one contiguous stretch of the table).
+// Lane l owns the 16-byte vectors l, l+32, ... of a table row; the matching elements of the R hidden
+// rows sit in its registers as fp32 for the whole kernel, so the only traffic in the loop is the
+// table itself: KV 16-byte streaming loads per lane per table row, J*KV of them in flight.
+// H = KV * 32 * (elements per vector) exactly.
+// ---------------------------------------------------------------------------
+template <typename T, int KV, int R, int J, bool kAhead>
+__global__ void __launch_bounds__(kLmThreads, 1)
+lm_head_argmax_kernel(const T* __restrict__ hidden, const T* __restrict__ table, int64_t vocab, int64_t index_base,
+                      T* __restrict__ logits_out, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
+                      unsigned long long* keys, unsigned int* ticket) {
+  constexpr int N = Elem<T>::kPerVec;
+  constexpr int H = KV * kWarpSize * N;
+  constexpr int M = J * R;                       // sums a warp produces per step
+  constexpr int kGroup = kWarpSize >> Log2<M>::value;  // lanes that end up holding the same sum
+  __shared__ float slot_v[kLmWarps][8];
+  __shared__ int slot_i[kLmWarps][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  float h[R][KV * N];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      Elem<T>::unpack(ld_reuse(hidden + int64_t(r) * H + (k * kWarpSize + lane) * N), &h[r][k * N]);
+
+  const int my = lane >> (5 - Log2<M>::value);   // which of the M sums this lane holds after the reduction
+  const int my_jj = my / R, my_r = my - my_jj * R;
+  float bv = -FLT_MAX;
+  int bi = kLmNone;
+
+  const int64_t total_warps = int64_t(gridDim.x) * kLmWarps;
+  auto load_rows = [&](int64_t p, uint4 (&dst)[J][KV]) {
+#pragma unroll
+    for (int jj = 0; jj < J; ++jj) {
+      int64_t j = p * J + jj;
+      if (j >= vocab) j = vocab - 1;             // a ragged last step re-reads a row; its sum is dropped below
+      const T* row = table + j * H;
+#pragma unroll
+      for (int k = 0; k < KV; ++k) dst[jj][k] = ld_stream(row + (k * kWarpSize + lane) * N);
+    }
+  };
+  int64_t p = int64_t(blockIdx.x) * kLmWarps + warp;
+  uint4 w[J][KV];
+  if (p * J < vocab) load_rows(p, w);
+  for (; p * J < vocab; p += total_warps) {
+    // the next step's rows are requested before this step's arithmetic (where the registers allow it)
+    const int64_t pn = p + total_warps;
+    uint4 nx[J][KV];
+    if constexpr (kAhead) { if (pn * J < vocab) load_rows(pn, nx); }
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        float f[N];
+        Elem<T>::unpack(w[jj][k], f);
+#pragma unroll
+        for (int q = 0; q < N; ++q)
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[jj * R + r] = fmaf(f[q], h[r][k * N + q], acc[jj * R + r]);
+      }
+    reduce_transpose<M>(acc, lane);
+    const int64_t j = p * J + my_jj;
+    if (j < vocab) {
+      const float v = round_to_storage<T>(acc[0]);
+      if (logits_out != nullptr && (lane & (kGroup - 1)) == 0) Elem<T>::store(logits_out + my_r * logits_stride + j, v);
+      if (v > bv) { bv = v; bi = int(j); }       // a lane's rows ascend: strictly-greater keeps the lowest index
+    }
+    if constexpr (kAhead) {
+#pragma unroll
+      for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+        for (int k = 0; k < KV; ++k) w[jj][k] = nx[jj][k];
+    } else {
+      if (pn * J < vocab) load_rows(pn, w);
+    }
+  }
+  if ((lane & (kGroup - 1)) == 0) { slot_v[warp][my] = bv; slot_i[warp][my] = bi; }
+  __syncthreads();
+  lm_publish<R>(slot_v, slot_i, kLmWarps, J, index_base, out_ids, out_keys, keys, ticket);
+}
+
+// ---------------------------------------------------------------------------
+// Ordered kernel (B2_DETERMINISTIC, and every shape the fast kernel is not built for): one thread
+// per table row walks k upwards, `acc = rn(acc + rn(x * w))`; the hidden rows sit in shared memory
+// as fp32 (every lane reads the same word: a broadcast).  Each thread reads its own row in 16-byte
+// pieces; the 128-byte lines it touches stay in L1 until it has walked through them.
+// ---------------------------------------------------------------------------
+constexpr int kOrdLmThreads = 128;
+
+template <typename T, int R, bool kVec>
+__global__ void __launch_bounds__(kOrdLmThreads)
+lm_head_ordered_kernel(const T* __restrict__ hidden, const T* __restrict__ table, int64_t vocab, int H, int64_t index_base,
+                       T* __restrict__ logits_out, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
+                       unsigned long long* keys, unsigned int* ticket) {
+  constexpr int N = Elem<T>::kPerVec;
+  extern __shared__ float hs[];                  // [R][H]
+  __shared__ float slot_v[kOrdLmThreads / kWarpSize][8];
+  __shared__ int slot_i[kOrdLmThreads / kWarpSize][8];
+  for (int i = threadIdx.x; i < R * H; i += kOrdLmThreads) hs[i] = Elem<T>::load(hidden + i);
+  __syncthreads();
+
+  const int64_t j = int64_t(blockIdx.x) * kOrdLmThreads + threadIdx.x;
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+  if (j < vocab) {
+    const T* row = table + j * H;
+    if (kVec) {
+      for (int k = 0; k < H; k += N) {
+        float f[N];
+        Elem<T>::unpack(__ldg(reinterpret_cast<const uint4*>(row + k)), f);
+#pragma unroll
+        for (int q = 0; q < N; ++q)
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[r] = __fadd_rn(acc[r], __fmul_rn(hs[r * H + k + q], f[q]));
+      }
+    } else {
+      for (int k = 0; k < H; ++k) {
+        const float f = Elem<T>::load(row + k);
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = __fadd_rn(acc[r], __fmul_rn(hs[r * H + k], f));
+      }
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float bv = -FLT_MAX;
+    int bi = kLmNone;
+    if (j < vocab) {
+      const float v = round_to_storage<T>(acc[r]);
+      if (logits_out != nullptr) Elem<T>::store(logits_out + r * logits_stride + j, v);
+      if (v > bv) { bv = v; bi = int(j); }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_down_sync(0xffffffffu, bv, offset);
+      const int oi = __shfl_down_sync(0xffffffffu, bi, offset);
+      if (lm_beats(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { slot_v[warp][r] = bv; slot_i[warp][r] = bi; }
+  }
+  __syncthreads();
+  lm_publish<R>(slot_v, slot_i, kOrdLmThreads / kWarpSize, 1, index_base, out_ids, out_keys, keys, ticket);
+}
+
+// ---------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------
+
+template <typename T, int KV, int R, int J, bool kAhead>
+int launch_fast(const T* hidden, const T* table, int64_t vocab, int64_t index_base, T* logits_out, int64_t logits_stride,
+                int32_t* out_ids, int64_t* out_keys, unsigned long long* keys, unsigned int* ticket, cudaStream_t s) {
+  auto kernel = lm_head_argmax_kernel<T, KV, R, J, kAhead>;
+  static int per_sm = 0;                         // resident thread blocks per SM (same on every B200)
+  if (per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kLmThreads, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm = n > 4 ? 4 : n;
+  }
+  int64_t blocks = int64_t(sm_count()) * per_sm;
+  const int64_t needed = (vocab + int64_t(J) * kLmWarps - 1) / (int64_t(J) * kLmWarps);
+  if (blocks > needed) blocks = needed;
+  kernel<<<unsigned(blocks), kLmThreads, 0, s>>>(hidden, table, vocab, index_base, logits_out, logits_stride, out_ids,
+                                                 out_keys, keys, ticket);
+  return launch_status("lm_head_argmax");
+}
+
+template <typename T, int R>
+int launch_ordered(const T* hidden, const T* table, int64_t vocab, int64_t H, int64_t index_base, T* logits_out,
+                   int64_t logits_stride, int32_t* out_ids, int64_t* out_keys, unsigned long long* keys,
+                   unsigned int* ticket, cudaStream_t s) {
+  const size_t smem = size_t(R) * size_t(H) * sizeof(float);
+  const unsigned blocks = unsigned((vocab + kOrdLmThreads - 1) / kOrdLmThreads);
+  const bool vec = aligned16(table) && H % Elem<T>::kPerVec == 0;
+  if (vec)
+    lm_head_ordered_kernel<T, R, true><<<blocks, kOrdLmThreads, smem, s>>>(hidden, table, vocab, int(H), index_base, logits_out,
+                                                                          logits_stride, out_ids, out_keys, keys, ticket);
+  else
+    lm_head_ordered_kernel<T, R, false><<<blocks, kOrdLmThreads, smem, s>>>(hidden, table, vocab, int(H), index_base,
+                                                                           logits_out, logits_stride, out_ids, out_keys, keys,
+                                                                           ticket);
+  return launch_status("lm_head_argmax (ordered)");
+}
+
+// hidden rows the register-resident kernel takes in one pass over the table, 0 = shape not built
+template <typename T> int fast_rows_per_pass(int64_t H) {
+  // a lane keeps H / 32 fp32 registers per hidden row and one table row's worth of 16-byte vectors
+  if (H == 1024) return 4;
+  if (H == 2048) return 2;
+  if (H == 4096) return Elem<T>::kPerVec == 8 ? 1 : 0;   // fp32 rows of 4096 do not fit the register file
+  return 0;
+}
+
+template <typename T>
+int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t H, int64_t vocab, int mode,
+                 int64_t index_base, void* logits_, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
+                 void* workspace, cudaStream_t s) {
+  constexpr int N = Elem<T>::kPerVec;
+  const T* hidden = static_cast<const T*>(hidden_);
+  const T* table = static_cast<const T*>(table_);
+  T* logits = static_cast<T*>(logits_);
+  auto* keys = static_cast<unsigned long long*>(workspace);
+  auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
+  const bool fast_ok = mode == B2_FAST && aligned16(hidden) && aligned16(table) && fast_rows_per_pass<T>(H) > 0;
+  const int cap = fast_ok ? fast_rows_per_pass<T>(H) : (H <= 2048 ? 4 : H <= 4096 ? 2 : 1)   /* ordered kernel: R * H floats of shared memory, <= 32 KB */;
+  for (int64_t r0 = 0; r0 < rows;) {
+    int R = rows - r0 >= 4 ? 4 : rows - r0 >= 2 ? 2 : 1;
+    if (R > cap) R = cap;
+    const T* hp = hidden + r0 * H;
+    T* lp = logits ? logits + r0 * logits_stride : nullptr;
+    int32_t* ip = out_ids ? out_ids + r0 : nullptr;
+    int64_t* kp = out_keys ? out_keys + r0 : nullptr;
+    int rc;
+#define B2_LM_FAST(KV, RR, JJ, AH) \
+  rc = launch_fast<T, KV, RR, JJ, AH>(hp, table, vocab, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
+#define B2_LM_ORD(RR) \
+  rc = launch_ordered<T, RR>(hp, table, vocab, H, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
+    if (fast_ok) {
+      constexpr int KV1 = 1024 / (kWarpSize * N), KV2 = 2 * KV1;
+      [[maybe_unused]] constexpr int KV4 = 4 * KV1;
+      if (H == 1024) {
+        if (R == 4) B2_LM_FAST(KV1, 4, (N == 8 ? 2 : 1), false);
+        else if (R == 2) B2_LM_FAST(KV1, 2, (N == 8 ? 2 : 1), true);
+        else B2_LM_FAST(KV1, 1, (N == 8 ? 2 : 1), true);
+      } else if (H == 2048) {
+        if (R == 2) B2_LM_FAST(KV2, 2, 1, false);
+        else B2_LM_FAST(KV2, 1, 1, true);
+      } else {
+        if constexpr (N == 8) B2_LM_FAST(KV4, 1, 1, false);
+        else rc = B2_ERR_UNSUPPORTED;
+      }
+    } else {
+      if (R == 4) B2_LM_ORD(4);
+      else if (R == 2) B2_LM_ORD(2);
+      else B2_LM_ORD(1);
+    }
+#undef B2_LM_FAST
+#undef B2_LM_ORD
+    if (rc != B2_OK) return rc;
+    r0 += R;
+  }
+  return B2_OK;
+}
+
+}  // namespace
+
+int launch_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab,
+                          int dtype, int mode, int64_t index_base, void* logits_out, int64_t logits_stride,
+                          int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  return dtype == B2_F32 ? launch_typed<float>(hidden, table, rows, hidden_size, vocab, mode, index_base, logits_out,
+                                               logits_stride, out_ids, out_keys, workspace, s)
+                         : launch_typed<__half>(hidden, table, rows, hidden_size, vocab, mode, index_base, logits_out,
+                                                logits_stride, out_ids, out_keys, workspace, s);
+}
+
+}  // namespace b2

@@ -31,7 +31,7 @@ def _peak():
 
 def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, only=None, reps_scale=1.0):
     """only: substring selecting one group of entries ("add_rms_norm", "headline_shape", "qk_norm_rope",
-    "swiglu", "gather", "argmax", "softmax"); reps_scale shortens the runs for profiler captures."""
+    "swiglu", "gather", "argmax", "softmax", "sampler", "kvmove", "lm_head"); reps_scale shortens the runs for profiler captures."""
     from . import sharded
 
     def want(group):
@@ -116,7 +116,44 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
             del bufs
     if world == 1 and (want("sampler") or want("kvmove")):
         _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
+    if world == 1 and want("lm_head"):
+        _lm_head(L, lib, dev, s, timed, record, randn, nreps)
     return table
+
+
+def _lm_head(L, lib, dev, s, timed, record, randn, nreps):
+    """Decode-size LM head fused with the greedy pick, Qwen3-0.6B's shape (151936 x 1024): bytes = the table read once
+    (+ hidden rows and ids; + the logits when they are written).  Two tables alternate (622 MB > L2).  Beside it the
+    two-step form it replaces, with a library GEMM standing in for the reference's cuBLAS call: matmul into a logits
+    tensor, then this library's argmax over it."""
+    F16, F32, FAST, DET = lib.F16, lib.F32, lib.FAST, lib.DETERMINISTIC
+    H = 1024
+    ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    for dtype, code, e in ((torch.float16, F16, 2), (torch.float32, F32, 4)):
+        tables = [randn(VOCAB, H, sigma=0.02, dtype=dtype) for _ in range(2)]
+        for R in (1, 4):
+            hidden = randn(R, H, dtype=dtype)
+            ids = torch.empty(R, dtype=torch.int32, device=dev)
+            logits = torch.empty(R, VOCAB, dtype=dtype, device=dev)
+            name = "f16" if e == 2 else "f32"
+            for label, lp, mode in (("ids only", 0, FAST), ("ids + logits written", logits.data_ptr(), FAST),
+                                    ("ids only, deterministic (k-ordered sums)", 0, DET)):
+                if mode == DET and (R != 1 or e != 2):
+                    continue
+                calls = [(lambda t=t: lib.check(L.b2_lm_head_argmax(hidden.data_ptr(), t.data_ptr(), R, H, VOCAB, code, mode, 0,
+                                                                    lp, VOCAB, ids.data_ptr(), None, ws.data_ptr(), s)))
+                         for t in tables]
+                ms = timed(calls, nreps(20))
+                record(f"lm_head_argmax ({label})", f"{R} x {H} by {VOCAB} x {H} {name}",
+                       VOCAB * H * e + R * H * e + 4 * R + (R * VOCAB * e if lp else 0), ms, R)
+
+            def two_step(t):
+                torch.matmul(hidden, t.t(), out=logits)
+                lib.check(L.b2_argmax_rows(logits.data_ptr(), R, VOCAB, VOCAB, code, ids.data_ptr(), ws.data_ptr(), s))
+            ms = timed([(lambda t=t: two_step(t)) for t in tables], nreps(20))
+            record("library GEMM into logits + argmax_rows (two launches, yardstick)", f"{R} x {H} by {VOCAB} x {H} {name}",
+                   VOCAB * H * e + R * H * e + 4 * R + 2 * R * VOCAB * e, ms, R)
+        del tables
 
 
 def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):

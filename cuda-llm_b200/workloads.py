@@ -105,6 +105,13 @@ def config5(rows=256, vocab=VOCAB, seed=5001):
     return {"logits": logits, "planted": planted}
 
 
+def lm_head_case(rows=4, hidden=1024, vocab=VOCAB, seed=6001, dtype=np.float16):
+    """Decode-size LM head: final-norm outputs ~N(0,1) against a tied embedding table ~N(0,0.02)
+    (the table of configurations 1 and 4), Qwen3-0.6B shape by default."""
+    rng = np.random.default_rng(seed)
+    return {"hidden": normal(rng, (rows, hidden), 1.0, dtype), "table": normal(rng, (vocab, hidden), 0.02, dtype)}
+
+
 def shard_range(total, world, rank):
     """Contiguous [lo, hi) slice of `total` units owned by `rank` of `world`."""
     return total * rank // world, total * (rank + 1) // world

@@ -191,6 +191,32 @@ B2_API int b2_argmax_keys(const void* logits, int64_t rows, int64_t width, int64
                           int64_t index_base, int64_t* keys, void* workspace, b2_stream stream);
 B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out_ids, b2_stream stream);
 
+/* Decode-size LM head fused with the greedy pick: logits[r, j] = sum_k hidden[r, k] * table[j, k]
+ * and, per row, the arg-max over j, in one pass over the table; the pick never reads the logits
+ * back from memory.  Meant for decode batches (1-4 rows, any count accepted): there the product is
+ * bound by reading the table once, not by arithmetic, so it runs on the CUDA cores like the other
+ * streaming operators (every 4 rows, 2 at hidden 2048, 1 at 4096, cost one more pass over the
+ * table; prefill-sized row counts belong to a GEMM).
+ * hidden: rows x hidden_size; table: vocab x hidden_size (the tied embedding); same dtype.
+ * logits_out: NULL, or rows x vocab of that dtype, consecutive rows `logits_stride` elements apart.
+ * out_ids: NULL or int32[rows]; out_keys: NULL or int64[rows] packed as by b2_argmax_keys with
+ * index_base added to every index (a vocabulary-sharded table: reduce the keys with a signed MAX,
+ * then b2_argmax_decode_keys).  At least one of the three outputs must be given.
+ * The logit is rounded to the storage type before it is compared, and the pick follows
+ * b2_argmax_rows' rule.  B2_DETERMINISTIC adds the products in ascending k with separately
+ * rounded multiplies (the reference's CPU `linear`, and for fp16 its linear_f16_reference kernel);
+ * B2_FAST splits k over a warp in a fixed order.  Hidden sizes 1024 and 2048 (fp16 also 4096) with
+ * 16-byte aligned pointers take the register-resident kernel in B2_FAST; other shapes (hidden_size
+ * up to 8192) take the ordered kernel in both modes.
+ * workspace: as for b2_argmax_rows (b2_argmax_workspace_bytes(rows), zero-filled once).
+ * Replaces, for decode, cuda_lm_head / cuda_linear_out followed by cuda_argmax_last_row
+ * (include/llm/ops_cuda.h:154,157; src/ops_cuda.cu:885,101-111; src/qwen3_cuda_model.cpp:1070-1071,
+ * 1339); CPU twin lm_head = linear (include/llm/ops.h:12; src/ops_cpu.cpp:9,17). */
+B2_API int b2_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size,
+                             int64_t vocab, int dtype, int mode, int64_t index_base, void* logits_out,
+                             int64_t logits_stride, int32_t* out_ids, int64_t* out_keys, void* workspace,
+                             b2_stream stream);
+
 /* Row softmax over the last dimension: out = exp(x - max) / sum.
  * B2_FAST keeps each row on chip (a thread-block cluster holds it in distributed
  * shared memory) when it fits, otherwise makes two passes; B2_DETERMINISTIC adds the

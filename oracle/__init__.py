@@ -99,6 +99,14 @@ class Port:
                                       C.c_int64(h), _ptr(res), _ptr(nrm))
         return res, nrm
 
+    def linear(self, x, w):
+        """reference src/ops_cpu.cpp:9 / :17 (lm_head): [rows, in] x [out, in]^T in fp32, k ascending."""
+        x, w = _f32(x), _f32(w)
+        out = np.empty((x.shape[0], w.shape[0]), np.float32)
+        self.lib.orc_cpu_linear(_ptr(x), _ptr(w), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]), C.c_int64(w.shape[0]),
+                                _ptr(out))
+        return out
+
     def swiglu(self, gate, up):
         gate, up = _f32(gate), _f32(up)
         out = np.empty_like(gate)
@@ -271,6 +279,13 @@ class Ref:
 
     def hardware_threads(self) -> int:
         return int(self.lib.ref_hardware_threads())
+
+    def lm_head(self, hidden, table):
+        hidden, table = _f32(hidden), _f32(table)
+        out = np.empty((hidden.shape[0], table.shape[0]), np.float32)
+        self._ok(self.lib.ref_lm_head(_ptr(hidden), _ptr(table), C.c_int64(hidden.shape[0]), C.c_int64(hidden.shape[1]),
+                                      C.c_int64(table.shape[0]), _ptr(out)), "lm_head")
+        return out
 
     def swiglu(self, gate, up):
         gate, up = _f32(gate), _f32(up)

@@ -109,6 +109,19 @@ ORC_API int orc_cpu_embedding_lookup(const float* table, int64_t vocab, int64_t 
   return 0;
 }
 
+/* reference src/ops_cpu.cpp:9 (linear) and :17 (lm_head = linear): out[i, j] = sum_k x[i, k] * w[j, k],
+ * one fp32 accumulator per output, k ascending, product rounded before it is added (the reference
+ * builds for baseline x86-64: no fused multiply-add). */
+ORC_API void orc_cpu_linear(const float* x, const float* w, int64_t rows, int64_t in, int64_t out_features,
+                            float* out) {
+  for (int64_t i = 0; i < rows; ++i)
+    for (int64_t j = 0; j < out_features; ++j) {
+      float z = 0.0f;
+      for (int64_t k = 0; k < in; ++k) z += x[i * in + k] * w[j * in + k];  /* built with -ffp-contract=off */
+      out[i * out_features + j] = z;
+    }
+}
+
 /* reference src/ops_cpu.cpp:10 (rms_norm): fp32 running sum of squares in index
  * order, r = 1/sqrt(sum/H + eps) in fp32, out = (x*r)*w. */
 ORC_API void orc_cpu_rms_norm(const float* x, const float* w, float eps,

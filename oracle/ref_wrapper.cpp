@@ -51,6 +51,9 @@ REF_API int ref_embedding_lookup(const float* table, int64_t vocab, int64_t hidd
     unwrap(llm::embedding_lookup(wrap(table, {vocab, hidden}), v), out);
   });
 }
+REF_API int ref_lm_head(const float* hidden, const float* table, int64_t rows, int64_t in, int64_t vocab, float* out) {
+  return guarded([&] { unwrap(llm::lm_head(wrap(hidden, {rows, in}), wrap(table, {vocab, in})), out); });
+}
 REF_API float ref_decode_f16(uint16_t h) { return llm::decode_f16(h); }
 REF_API uint16_t ref_encode_f16(float x) { return llm::encode_f16(x); }
 

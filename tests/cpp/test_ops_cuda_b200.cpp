@@ -24,6 +24,7 @@ void orc_cpu_swiglu(const float*, const float*, int64_t, float*);
 int orc_cpu_rope(const float*, const int32_t*, float, int64_t, int64_t, int64_t, float*);
 void orc_cpu_softmax(const float*, int64_t, int64_t, float*);
 int orc_cpu_embedding_lookup(const float*, int64_t, int64_t, const int32_t*, int64_t, float*);
+void orc_cpu_linear(const float*, const float*, int64_t, int64_t, int64_t, float*);
 int32_t orc_argmax_row_f32(const float*, int64_t);
 uint16_t orc_f32_to_f16_rn(float);
 void orc_dev_add_rms_norm(const void*, const void*, const void*, float, int64_t, int64_t, void*, void*, int);
@@ -215,6 +216,47 @@ static void argmax_cases() {
   expect_throw("argmax empty shape", [&] { cuda_argmax_last_row(Tensor(DType::F32, {}, DeviceType::CUDA)); });
 }
 
+// Decode-size LM head + greedy pick against the CPU operator lm_head = linear (reference src/ops_cpu.cpp:9,17;
+// known answer of reference tests/test_ops_cpu.cpp:14) followed by the arg-max rule.
+static void lm_head_argmax_cases() {
+  Tensor w = Tensor::from_f32({3, 2}, {1, 2, 3, 4, 5, 6}), x = Tensor::from_f32({1, 2}, {2, 3});
+  Tensor ids(DType::I32, {1}, DeviceType::CUDA), logits(DType::F32, {1, 3}, DeviceType::CUDA);
+  cuda_lm_head_argmax_out(cuda(x), cuda(w), ids, &logits);
+  metric("cuda_lm_head_argmax logits [1,2]x[3,2]", logits, {8, 18, 28}, 0);
+  if (ids.to(DeviceType::CPU).data_i32()[0] != 2) fail("cuda_lm_head_argmax known answer");
+  const int rows = 3, hidden = 1024, vocab = 777;
+  std::vector<float> h(size_t(rows) * hidden), t(size_t(vocab) * hidden), want(size_t(rows) * vocab);
+  uint32_t state = 12345u;
+  auto next = [&] { state = state * 1664525u + 1013904223u; return float(int32_t(state >> 8) % 2001 - 1000) / 1000.0f; };
+  for (auto& v : h) v = next();
+  for (auto& v : t) v = 0.02f * next();
+  for (const bool f16 : {false, true}) {
+    Tensor ht = Tensor::from_f32({rows, hidden}, h), tt = Tensor::from_f32({vocab, hidden}, t);
+    if (f16) { ht = half_of(ht); tt = half_of(tt); }
+    const Tensor hw = f16 ? widen(ht) : ht, tw = f16 ? widen(tt) : tt;
+    orc_cpu_linear(hw.data_f32(), tw.data_f32(), rows, hidden, vocab, want.data());
+    Tensor out_ids(DType::I32, {rows}, DeviceType::CUDA), out_logits(ht.dtype(), {rows, vocab}, DeviceType::CUDA);
+    {
+      CudaReductionModeGuard ordered(CudaReductionMode::kDeterministic);
+      cuda_lm_head_argmax_out(cuda(ht), cuda(tt), out_ids, &out_logits);
+    }
+    metric(std::string("cuda_lm_head_argmax deterministic ") + (f16 ? "f16" : "f32"), out_logits, want, f16 ? 2e-3f : 0.0f);
+    Tensor got = out_ids.to(DeviceType::CPU);
+    Tensor stored = f16 ? widen(out_logits.to(DeviceType::CPU)) : out_logits.to(DeviceType::CPU);
+    for (int r = 0; r < rows; ++r)
+      if (got.data_i32()[r] != orc_argmax_row_f32(stored.data_f32() + size_t(r) * vocab, vocab)) fail("cuda_lm_head_argmax ids");
+    Tensor fast_ids(DType::I32, {rows}, DeviceType::CUDA);
+    cuda_lm_head_argmax_out(cuda(ht), cuda(tt), fast_ids, &out_logits);
+    metric(std::string("cuda_lm_head_argmax fast ") + (f16 ? "f16" : "f32"), out_logits, want, f16 ? 2e-3f : 1e-5f);
+  }
+  expect_throw("lm_head CPU input", [&] { cuda_lm_head_argmax_out(x, cuda(w), ids); });
+  expect_throw("lm_head hidden_size mismatch", [&] { cuda_lm_head_argmax_out(cuda(Tensor::from_f32({1, 3}, {1, 2, 3})), cuda(w), ids); });
+  expect_throw("lm_head dtype mismatch", [&] { cuda_lm_head_argmax_out(cuda(half_of(x)), cuda(w), ids); });
+  expect_throw("lm_head rank", [&] { cuda_lm_head_argmax_out(cuda(Tensor::from_f32({2}, {2, 3})), cuda(w), ids); });
+  Tensor two(DType::I32, {2}, DeviceType::CUDA);
+  expect_throw("lm_head ids shape", [&] { cuda_lm_head_argmax_out(cuda(x), cuda(w), two); });
+}
+
 static void embedding_cases() {
   const int vocab = 7, hidden = 4;
   Tensor ew = Tensor::from_f32({vocab, hidden}, {.01f, .02f, .03f, .04f, .10f, .20f, .30f, .40f, -.10f, -.20f, -.30f, -.40f, .50f, .60f,
@@ -280,6 +322,7 @@ int main() {
     std::cout << "CUDA device=" << prop.name << " compute_capability=" << prop.major << "." << prop.minor << "\n";
     operators_against_oracle();
     argmax_cases();
+    lm_head_argmax_cases();
     embedding_cases();
     tensor_and_allocation_cases();
     CUDA_CHECK(cudaDeviceSynchronize());

@@ -13,8 +13,8 @@ Writes
                         (artifacts/phase25/qwen3_full_prefill/case_seq{4,8})
   c1_reference.npz      outputs of the reference's own compiled CPU operators (oracle/_ref) on
                         the seeded configuration-1 inputs (cuda_llm_b200.workloads.config1)
-  small_reference.npz   the same for small fp16 cases of configurations 2, 3 and 5
-                        (inputs regenerated from their seeds by the tests)
+  small_reference.npz   the same for small fp16 cases of configurations 2, 3 and 5 and of the
+                        decode-size LM head (inputs regenerated from their seeds by the tests)
 """
 import os
 import sys
@@ -85,6 +85,9 @@ def reference_outputs():
     small["c3_k"] = ref.rope(ref.rms_norm(k.reshape(-1, 128), gk, wl.EPS).reshape(k.shape), c3["positions"], wl.THETA)
     c5 = wl.config5(rows=4, vocab=8192, seed=5002)
     small["c5_softmax"] = ref.softmax(c5["logits"])
+    lm = wl.lm_head_case(rows=4, hidden=1024, vocab=640, seed=6002, dtype=np.float16)
+    small["lm_head_logits"] = ref.lm_head(port.decode_f16(lm["hidden"].view(np.uint16)),
+                                          port.decode_f16(lm["table"].view(np.uint16)))
     np.savez_compressed(os.path.join(HERE, "small_reference.npz"), **small)
 
 

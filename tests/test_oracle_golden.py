@@ -200,6 +200,27 @@ def test_port_reproduces_committed_reference_outputs(port, golden):
     assert same(res, s["c2_residual"]) and same(nrm, s["c2_normalized"])
 
 
+# ---- linear / lm_head (reference src/ops_cpu.cpp:9,17) ---------------------------------------
+
+def test_linear_known_answer_and_reference_bits(port, ref, golden):
+    """reference tests/test_ops_cpu.cpp:14,19: [2,3] x [[1,2],[3,4],[5,6]]^T = [8,18,28], lm_head == linear;
+    then bit equality with the reference's compiled lm_head and with its committed outputs."""
+    x = np.array([[2, 3]], np.float32)
+    w = np.array([[1, 2], [3, 4], [5, 6]], np.float32)
+    assert port.linear(x, w).tolist() == [[8.0, 18.0, 28.0]]
+    bits = lambda a: np.ascontiguousarray(a).view(np.uint32)
+    lm = wl.lm_head_case(rows=4, hidden=1024, vocab=640, seed=6002, dtype=np.float16)
+    got = port.linear(port.decode_f16(f16_bits(lm["hidden"])).reshape(4, 1024),
+                      port.decode_f16(f16_bits(lm["table"])).reshape(640, 1024))
+    assert np.array_equal(bits(got), bits(golden("small_reference")["lm_head_logits"]))
+    if ref is None:
+        return
+    assert ref.lm_head(x, w).tolist() == [[8.0, 18.0, 28.0]]
+    rng = np.random.default_rng(77)
+    h, t = wl.normal(rng, (3, 333)), wl.normal(rng, (211, 333), 0.02)
+    assert np.array_equal(bits(port.linear(h, t)), bits(ref.lm_head(h, t)))
+
+
 # ---- the device-order restatement (deterministic mode's target) ------------------------------
 
 def test_device_order_restatement_is_consistent(port):
