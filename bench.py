@@ -292,6 +292,19 @@ def reference_gpu_kernels(L, lib, dev, stream):
     sws, sout = ops.softmax_workspace(dev, R), torch.empty_like(logits)
     row(f"softmax {R}x{vocab} f32", ref.time_softmax(logits, R, vocab, 0, 1),
         ours(lambda: lib.check(L.b2_softmax_rows(logits.data_ptr(), sout.data_ptr(), R, vocab, lib.F32, lib.FAST, sws.data_ptr(), s))))
+    # decode tail: the reference's cuda_lm_head (library GEMM into a fresh logits tensor) + cuda_argmax_last_row
+    for R in (1, 4):
+        hid = torch.randn(R, 1024, device=dev).to(half)
+        emb = (torch.randn(vocab, 1024, device=dev) * 0.02).to(half)
+        lm_ids = torch.empty(R, dtype=torch.int32, device=dev)
+        ref_ms = ref.time_lm_head_argmax(hid, emb, R, 1024, vocab, 1, 5)
+        if ref_ms > 0:
+            row(f"lm_head + argmax, {R} x 1024 by {vocab} x 1024 f16", ref_ms,
+                ours(lambda: lib.check(L.b2_lm_head_argmax(hid.data_ptr(), emb.data_ptr(), R, 1024, vocab, lib.F16, lib.FAST, 0,
+                                                           None, vocab, lm_ids.data_ptr(), None, ws.data_ptr(), s))),
+                note="reference: cuda_lm_head (cuBLASLt GEMM, allocates the logits) + cuda_argmax_last_row (last row only, "
+                     "blocking, 2 cudaMalloc + 2 cudaFree); ours: one launch, every row, ids stay on the device")
+        del hid, emb
     # sampling: the reference draws one token per blocking call; ours draws all rows in one call
     sampler_ws = torch.empty(L.b2_sampler_workspace_bytes(R, vocab), dtype=torch.uint8, device=dev)
     offs = torch.arange(R, dtype=torch.int64, device=dev)

@@ -71,16 +71,17 @@ template <> struct Log2<1> { static constexpr int value = 0; };
 template <> struct Log2<2> { static constexpr int value = 1; };
 template <> struct Log2<4> { static constexpr int value = 2; };
 template <> struct Log2<8> { static constexpr int value = 3; };
+template <> struct Log2<16> { static constexpr int value = 4; };
 
 // Folds the thread block's candidates (slots[warp][slot], `slots_per_row` slots for each of R rows,
 // slot = jj * R + r) into the call-wide keys, and lets the last block to arrive publish the result
-// and leave the scratch zeroed for the next call.
+// and leave the scratch zeroed for the next call.  Only the first `valid` of the R rows exist.
 template <int R>
-__device__ __forceinline__ void lm_publish(const float (*slot_v)[8], const int (*slot_i)[8], int warps, int slots_per_row,
+__device__ __forceinline__ void lm_publish(const float (*slot_v)[16], const int (*slot_i)[16], int warps, int slots_per_row,
                                            int64_t index_base, int32_t* out_ids, int64_t* out_keys,
-                                           unsigned long long* keys, unsigned int* ticket) {
+                                           unsigned long long* keys, unsigned int* ticket, int valid = R) {
   __shared__ int last_block;
-  if (threadIdx.x < R) {
+  if (threadIdx.x < valid) {
     const int r = threadIdx.x;
     float bv = -FLT_MAX;
     int bi = kLmNone;
@@ -96,7 +97,7 @@ __device__ __forceinline__ void lm_publish(const float (*slot_v)[8], const int (
   __syncthreads();
   if (threadIdx.x == 0) last_block = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1 : 0;
   __syncthreads();
-  if (!last_block || threadIdx.x >= R) return;
+  if (!last_block || threadIdx.x >= valid) return;
   __threadfence();
   const int r = threadIdx.x;
   const unsigned long long key = atomicExch(keys + r, 0ull);
@@ -122,8 +123,8 @@ lm_head_argmax_kernel(const T* __restrict__ hidden, const T* __restrict__ table,
   constexpr int H = KV * kWarpSize * N;
   constexpr int M = J * R;                       // sums a warp produces per step
   constexpr int kGroup = kWarpSize >> Log2<M>::value;  // lanes that end up holding the same sum
-  __shared__ float slot_v[kLmWarps][8];
-  __shared__ int slot_i[kLmWarps][8];
+  __shared__ float slot_v[kLmWarps][16];
+  __shared__ int slot_i[kLmWarps][16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   float h[R][KV * N];
@@ -193,6 +194,110 @@ lm_head_argmax_kernel(const T* __restrict__ hidden, const T* __restrict__ table,
 }
 
 // ---------------------------------------------------------------------------
+// Fast kernel for two to four hidden rows (and for hidden sizes the register-resident kernel is not
+// built for).  With more than one hidden row the registers that held them are needed for table
+// data in flight, so the hidden rows move to shared memory as fp32 and a warp takes J = 4 table rows
+// per step: every 32 bytes a lane reads from shared memory (8 hidden values of one row) meet 4 table
+// vectors, which keeps shared-memory traffic at R/2 times the table's (2x for four rows).  K is walked
+// in chunks of 32 lanes x 4 vectors; the J x 4 streaming loads of a chunk are all issued before its
+// arithmetic, and three thread blocks of four warps per SM keep ~100 KB of the table in flight per SM.
+// H is a multiple of the chunk (1024 fp16 / 512 fp32 elements).
+// ---------------------------------------------------------------------------
+constexpr int kLmSmemThreads = 128;
+constexpr int kLmSmemWarps = kLmSmemThreads / kWarpSize;
+constexpr int kLmChunkVecs = 4;
+
+template <typename T, int R, int J>
+__global__ void __launch_bounds__(kLmSmemThreads, 3)
+lm_head_argmax_smem_kernel(const T* __restrict__ hidden, const T* __restrict__ table, int64_t vocab, int H, int64_t index_base,
+                           T* __restrict__ logits_out, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
+                           unsigned long long* keys, unsigned int* ticket, int valid) {
+  constexpr int N = Elem<T>::kPerVec;
+  constexpr int KC = kLmChunkVecs;
+  constexpr int kChunk = kWarpSize * KC * N;
+  constexpr int M = J * R;
+  constexpr int kGroup = kWarpSize >> Log2<M>::value;
+  extern __shared__ __align__(16) float hs[];    // [R][H]
+  __shared__ float slot_v[kLmSmemWarps][16];
+  __shared__ int slot_i[kLmSmemWarps][16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (int i = threadIdx.x; i < R * H / N; i += kLmSmemThreads) {
+    float f[N];
+    if (i * N < valid * H) {                     // three rows ride in the four-row kernel: the fourth is zeros
+      Elem<T>::unpack(ld_reuse(hidden + int64_t(i) * N), f);
+    } else {
+#pragma unroll
+      for (int q = 0; q < N; ++q) f[q] = 0.0f;
+    }
+#pragma unroll
+    for (int q = 0; q < N; q += 4) *reinterpret_cast<float4*>(hs + i * N + q) = make_float4(f[q], f[q + 1], f[q + 2], f[q + 3]);
+  }
+  __syncthreads();
+
+  const int my = lane >> (5 - Log2<M>::value);
+  const int my_jj = my / R, my_r = my - my_jj * R;
+  float bv = -FLT_MAX;
+  int bi = kLmNone;
+  const int chunks = H / kChunk;
+  const int64_t total_warps = int64_t(gridDim.x) * kLmSmemWarps;
+  for (int64_t p = int64_t(blockIdx.x) * kLmSmemWarps + warp; p * J < vocab; p += total_warps) {
+    const T* rows[J];
+#pragma unroll
+    for (int jj = 0; jj < J; ++jj) {
+      int64_t j = p * J + jj;
+      if (j >= vocab) j = vocab - 1;             // a ragged last step re-reads a row; its sums are dropped below
+      rows[jj] = table + j * H + lane * N;
+    }
+    // packed fp32x2 arithmetic (one instruction per two multiply-adds): even and odd k accumulate apart
+    float2 acc2[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc2[m] = make_float2(0.0f, 0.0f);
+    for (int c = 0; c < chunks; ++c) {
+      uint4 w[J][KC];
+#pragma unroll
+      for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+        for (int k = 0; k < KC; ++k) w[jj][k] = ld_stream(rows[jj] + c * kChunk + k * kWarpSize * N);
+#pragma unroll
+      for (int k = 0; k < KC; ++k) {
+        float2 f[J][N / 2];
+#pragma unroll
+        for (int jj = 0; jj < J; ++jj) Elem<T>::unpack2(w[jj][k], f[jj]);
+        const float* hk = hs + c * kChunk + (k * kWarpSize + lane) * N;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float2 hr[N / 2];
+#pragma unroll
+          for (int q = 0; q < N / 4; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(hk + r * H + 4 * q);
+            hr[2 * q] = make_float2(t.x, t.y);
+            hr[2 * q + 1] = make_float2(t.z, t.w);
+          }
+#pragma unroll
+          for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+            for (int q = 0; q < N / 2; ++q) acc2[jj * R + r] = __ffma2_rn(f[jj][q], hr[q], acc2[jj * R + r]);
+        }
+      }
+    }
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = acc2[m].x + acc2[m].y;
+    reduce_transpose<M>(acc, lane);
+    const int64_t j = p * J + my_jj;
+    if (j < vocab && my_r < valid) {
+      const float v = round_to_storage<T>(acc[0]);
+      if (logits_out != nullptr && (lane & (kGroup - 1)) == 0) Elem<T>::store(logits_out + my_r * logits_stride + j, v);
+      if (v > bv) { bv = v; bi = int(j); }
+    }
+  }
+  if ((lane & (kGroup - 1)) == 0) { slot_v[warp][my] = bv; slot_i[warp][my] = bi; }
+  __syncthreads();
+  lm_publish<R>(slot_v, slot_i, kLmSmemWarps, J, index_base, out_ids, out_keys, keys, ticket, valid);
+}
+
+// ---------------------------------------------------------------------------
 // Ordered kernel (B2_DETERMINISTIC, and every shape the fast kernel is not built for): one thread
 // per table row walks k upwards, `acc = rn(acc + rn(x * w))`; the hidden rows sit in shared memory
 // as fp32 (every lane reads the same word: a broadcast).  Each thread reads its own row in 16-byte
@@ -207,8 +312,8 @@ lm_head_ordered_kernel(const T* __restrict__ hidden, const T* __restrict__ table
                        unsigned long long* keys, unsigned int* ticket) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ float hs[];                  // [R][H]
-  __shared__ float slot_v[kOrdLmThreads / kWarpSize][8];
-  __shared__ int slot_i[kOrdLmThreads / kWarpSize][8];
+  __shared__ float slot_v[kOrdLmThreads / kWarpSize][16];
+  __shared__ int slot_i[kOrdLmThreads / kWarpSize][16];
   for (int i = threadIdx.x; i < R * H; i += kOrdLmThreads) hs[i] = Elem<T>::load(hidden + i);
   __syncthreads();
 
@@ -280,6 +385,32 @@ int launch_fast(const T* hidden, const T* table, int64_t vocab, int64_t index_ba
 }
 
 template <typename T, int R>
+int launch_smem(const T* hidden, const T* table, int64_t vocab, int64_t H, int64_t index_base, T* logits_out,
+                int64_t logits_stride, int32_t* out_ids, int64_t* out_keys, unsigned long long* keys, unsigned int* ticket,
+                int valid, cudaStream_t s) {
+  constexpr int J = 4;
+  auto kernel = lm_head_argmax_smem_kernel<T, R, J>;
+  const size_t smem = size_t(R) * size_t(H) * sizeof(float);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    return launch_status("lm_head_argmax (shared-memory attribute)");
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kLmSmemThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+  int64_t blocks = int64_t(sm_count()) * per_sm;
+  const int64_t needed = (vocab + int64_t(J) * kLmSmemWarps - 1) / (int64_t(J) * kLmSmemWarps);
+  if (blocks > needed) blocks = needed;
+  kernel<<<unsigned(blocks), kLmSmemThreads, smem, s>>>(hidden, table, vocab, int(H), index_base, logits_out, logits_stride,
+                                                       out_ids, out_keys, keys, ticket, valid);
+  return launch_status("lm_head_argmax");
+}
+
+// hidden rows the shared-memory kernel takes in one pass (R * H fp32 values within 64 KB), 0 = shape not built
+template <typename T> int smem_rows_per_pass(int64_t H) {
+  if (H % (kWarpSize * kLmChunkVecs * Elem<T>::kPerVec) != 0) return 0;
+  return H <= 4096 ? 4 : H <= 8192 ? 2 : 1;
+}
+
+template <typename T, int R>
 int launch_ordered(const T* hidden, const T* table, int64_t vocab, int64_t H, int64_t index_base, T* logits_out,
                    int64_t logits_stride, int32_t* out_ids, int64_t* out_keys, unsigned long long* keys,
                    unsigned int* ticket, cudaStream_t s) {
@@ -296,11 +427,10 @@ int launch_ordered(const T* hidden, const T* table, int64_t vocab, int64_t H, in
   return launch_status("lm_head_argmax (ordered)");
 }
 
-// hidden rows the register-resident kernel takes in one pass over the table, 0 = shape not built
+// 1 where the register-resident kernel is built for this hidden size (it then serves single rows), else 0
 template <typename T> int fast_rows_per_pass(int64_t H) {
-  // a lane keeps H / 32 fp32 registers per hidden row and one table row's worth of 16-byte vectors
-  if (H == 1024) return 4;
-  if (H == 2048) return 2;
+  // a lane keeps H / 32 fp32 registers of the hidden row and one table row's worth of 16-byte vectors
+  if (H == 1024 || H == 2048) return 1;
   if (H == 4096) return Elem<T>::kPerVec == 8 ? 1 : 0;   // fp32 rows of 4096 do not fit the register file
   return 0;
 }
@@ -315,10 +445,17 @@ int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t 
   T* logits = static_cast<T*>(logits_);
   auto* keys = static_cast<unsigned long long*>(workspace);
   auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
-  const bool fast_ok = mode == B2_FAST && aligned16(hidden) && aligned16(table) && fast_rows_per_pass<T>(H) > 0;
-  const int cap = fast_ok ? fast_rows_per_pass<T>(H) : (H <= 2048 ? 4 : H <= 4096 ? 2 : 1)   /* ordered kernel: R * H floats of shared memory, <= 32 KB */;
+  const bool aligned = aligned16(hidden) && aligned16(table);
+  const int reg_cap = mode == B2_FAST && aligned ? fast_rows_per_pass<T>(H) : 0;    // register-resident kernel: one row
+  const int smem_cap = mode == B2_FAST && aligned ? smem_rows_per_pass<T>(H) : 0;
+  const int ord_cap = H <= 2048 ? 4 : H <= 4096 ? 2 : 1;   // ordered kernel: R * H floats of shared memory, <= 32 KB
   for (int64_t r0 = 0; r0 < rows;) {
-    int R = rows - r0 >= 4 ? 4 : rows - r0 >= 2 ? 2 : 1;
+    const int64_t left = rows - r0;
+    const bool use_reg = reg_cap > 0 && (left == 1 || smem_cap == 0);
+    const bool use_smem = !use_reg && smem_cap > 0;
+    const int cap = use_reg ? 1 : use_smem ? smem_cap : ord_cap;
+    int R = left >= 4 ? 4 : left >= 2 ? 2 : 1;   // rows this pass takes
+    if (use_smem && left == 3 && cap >= 4) R = 3;  // three rows ride in the four-row kernel
     if (R > cap) R = cap;
     const T* hp = hidden + r0 * H;
     T* lp = logits ? logits + r0 * logits_stride : nullptr;
@@ -327,28 +464,32 @@ int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t 
     int rc;
 #define B2_LM_FAST(KV, RR, JJ, AH) \
   rc = launch_fast<T, KV, RR, JJ, AH>(hp, table, vocab, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
+#define B2_LM_SMEM(RR) \
+  rc = launch_smem<T, RR>(hp, table, vocab, H, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, R, s)
 #define B2_LM_ORD(RR) \
   rc = launch_ordered<T, RR>(hp, table, vocab, H, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
-    if (fast_ok) {
+    if (use_reg) {
       constexpr int KV1 = 1024 / (kWarpSize * N), KV2 = 2 * KV1;
       [[maybe_unused]] constexpr int KV4 = 4 * KV1;
       if (H == 1024) {
-        if (R == 4) B2_LM_FAST(KV1, 4, (N == 8 ? 2 : 1), false);
-        else if (R == 2) B2_LM_FAST(KV1, 2, (N == 8 ? 2 : 1), true);
-        else B2_LM_FAST(KV1, 1, (N == 8 ? 2 : 1), true);
+        B2_LM_FAST(KV1, 1, (N == 8 ? 2 : 1), true);
       } else if (H == 2048) {
-        if (R == 2) B2_LM_FAST(KV2, 2, 1, false);
-        else B2_LM_FAST(KV2, 1, 1, true);
+        B2_LM_FAST(KV2, 1, 1, true);
       } else {
         if constexpr (N == 8) B2_LM_FAST(KV4, 1, 1, false);
         else rc = B2_ERR_UNSUPPORTED;
       }
+    } else if (use_smem) {
+      if (R >= 3) B2_LM_SMEM(4);
+      else if (R == 2) B2_LM_SMEM(2);
+      else B2_LM_SMEM(1);
     } else {
       if (R == 4) B2_LM_ORD(4);
       else if (R == 2) B2_LM_ORD(2);
       else B2_LM_ORD(1);
     }
 #undef B2_LM_FAST
+#undef B2_LM_SMEM
 #undef B2_LM_ORD
     if (rc != B2_OK) return rc;
     r0 += R;

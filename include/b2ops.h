@@ -195,8 +195,8 @@ B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out
  * and, per row, the arg-max over j, in one pass over the table; the pick never reads the logits
  * back from memory.  Meant for decode batches (1-4 rows, any count accepted): there the product is
  * bound by reading the table once, not by arithmetic, so it runs on the CUDA cores like the other
- * streaming operators (every 4 rows, 2 at hidden 2048, 1 at 4096, cost one more pass over the
- * table; prefill-sized row counts belong to a GEMM).
+ * streaming operators (every 4 rows, 2 above hidden size 4096, cost one more pass over the table;
+ * prefill-sized row counts belong to a GEMM).
  * hidden: rows x hidden_size; table: vocab x hidden_size (the tied embedding); same dtype.
  * logits_out: NULL, or rows x vocab of that dtype, consecutive rows `logits_stride` elements apart.
  * out_ids: NULL or int32[rows]; out_keys: NULL or int64[rows] packed as by b2_argmax_keys with
@@ -205,8 +205,8 @@ B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out
  * The logit is rounded to the storage type before it is compared, and the pick follows
  * b2_argmax_rows' rule.  B2_DETERMINISTIC adds the products in ascending k with separately
  * rounded multiplies (the reference's CPU `linear`, and for fp16 its linear_f16_reference kernel);
- * B2_FAST splits k over a warp in a fixed order.  Hidden sizes 1024 and 2048 (fp16 also 4096) with
- * 16-byte aligned pointers take the register-resident kernel in B2_FAST; other shapes (hidden_size
+ * B2_FAST splits k over a warp in a fixed order.  B2_FAST needs 16-byte aligned pointers and a
+ * hidden size that is a multiple of 1024 (fp16) or 512 (fp32) elements; other shapes (hidden_size
  * up to 8192) take the ordered kernel in both modes.
  * workspace: as for b2_argmax_rows (b2_argmax_workspace_bytes(rows), zero-filled once).
  * Replaces, for decode, cuda_lm_head / cuda_linear_out followed by cuda_argmax_last_row

@@ -398,6 +398,15 @@ class RefCuda:
                  "argmax_last_row")
         return int(r.value)
 
+    def lm_head_argmax(self, hidden, table, rows, hidden_size, vocab, dtype, logits_out=None) -> int:
+        """cuda_lm_head followed by cuda_argmax_last_row, as the reference's decode tail runs them."""
+        r = C.c_int32(-1)
+        self._ok(self.lib.refcu_lm_head_argmax(self._p(hidden), self._p(table), C.c_int64(rows), C.c_int64(hidden_size),
+                                               C.c_int64(vocab), C.c_int(dtype),
+                                               self._p(logits_out) if logits_out is not None else None, C.byref(r)),
+                 "lm_head_argmax")
+        return int(r.value)
+
     def sample_row(self, logits, rows, vocab, dtype, row, temperature, top_k, top_p, seed, draw_offset) -> int:
         """CudaSampler::sample_row of the reference: one token, one blocking call."""
         r = C.c_int32(-1)
@@ -437,6 +446,12 @@ class RefCuda:
     def time_argmax_last_row(self, logits, rows, width, dtype, reps):
         return float(self.lib.refcu_time_argmax_last_row(self._p(logits), C.c_int64(rows), C.c_int64(width), C.c_int(dtype),
                                                          C.c_int(reps)))
+
+
+    def time_lm_head_argmax(self, hidden, table, rows, hidden_size, vocab, dtype, reps):
+        self.lib.refcu_time_lm_head_argmax.restype = C.c_float
+        return float(self.lib.refcu_time_lm_head_argmax(self._p(hidden), self._p(table), C.c_int64(rows), C.c_int64(hidden_size),
+                                                        C.c_int64(vocab), C.c_int(dtype), C.c_int(reps)))
 
 
 _ref_cuda = False

@@ -123,6 +123,18 @@ REFCU_API int refcu_argmax_last_row(const void* logits, int64_t rows, int64_t wi
   return guarded([&] { *result_host = llm::cuda_argmax_last_row(from_device(logits, dtype_of(dtype), {rows, width})); });
 }
 
+// The decode tail of the reference: cuda_lm_head (a library GEMM into a fresh logits tensor) followed by
+// cuda_argmax_last_row (reference src/ops_cuda.cu:885,871; src/qwen3_cuda_model.cpp:1070-1071,1339).
+REFCU_API int refcu_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab,
+                                   int dtype, void* logits_out, int32_t* last_row_id_host) {
+  return guarded([&] {
+    const DType d = dtype_of(dtype);
+    Tensor logits = llm::cuda_lm_head(from_device(hidden, d, {rows, hidden_size}), from_device(table, d, {vocab, hidden_size}));
+    if (logits_out != nullptr) to_device(logits, logits_out);
+    *last_row_id_host = llm::cuda_argmax_last_row(logits);
+  });
+}
+
 // ---- timings of the reference kernels on tensors already on the device (copies excluded); ms per call, < 0 on error
 REFCU_API float refcu_time_add_rms_norm(const void* lhs, const void* rhs, const void* w, int64_t rows, int64_t hidden, float eps,
                                         int dtype, int reps) {
@@ -190,6 +202,17 @@ REFCU_API float refcu_time_argmax_last_row(const void* logits, int64_t rows, int
   guarded([&] {
     Tensor a = from_device(logits, dtype_of(dtype), {rows, width});
     ms = timed([&] { (void)llm::cuda_argmax_last_row(a); }, reps);
+  });
+  return ms;
+}
+
+REFCU_API float refcu_time_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab,
+                                          int dtype, int reps) {
+  float ms = -1;
+  guarded([&] {
+    const DType d = dtype_of(dtype);
+    Tensor h = from_device(hidden, d, {rows, hidden_size}), t = from_device(table, d, {vocab, hidden_size});
+    ms = timed([&] { (void)llm::cuda_argmax_last_row(llm::cuda_lm_head(h, t)); }, reps);
   });
   return ms;
 }

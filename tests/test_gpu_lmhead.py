@@ -52,7 +52,8 @@ def _run(hidden, table, mode, with_logits=True):
 
 SHAPES = [(1, 1024, 640), (2, 1024, 641), (3, 1024, 5003), (4, 1024, 2049), (5, 1024, 700), (7, 1024, 333),
           (1, 2048, 515), (2, 2048, 1030), (3, 2048, 77), (1, 4096, 300), (2, 4096, 129),
-          (2, 384, 1000), (1, 8, 5), (4, 100, 257), (1, 8192, 40)]
+          (2, 384, 1000), (1, 8, 5), (4, 100, 257), (1, 8192, 40), (4, 4096, 300), (2, 8192, 40), (3, 3072, 200),
+          (1, 1536, 100), (6, 1024, 500), (4, 2048, 9)]
 
 
 @pytest.mark.parametrize("rows,hidden,vocab", SHAPES)

@@ -111,3 +111,26 @@ def test_deterministic_swiglu_rope_softmax_track_reference_kernels(refcu, dtype)
     got = ops.cuda_softmax_last_dim(lg, "deterministic")
     peak = want.float().max(dim=1, keepdim=True).values
     assert float(((got.float() - want.float()).abs() / torch.maximum(want.float(), peak)).max()) <= (2e-6 if dtype == np.float32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows", [1, 4])
+def test_lm_head_argmax_against_the_reference_decode_tail(refcu, rows, dtype):
+    """The reference's decode tail on the same GPU: cuda_lm_head (its library GEMM) into a logits tensor, then
+    cuda_argmax_last_row.  Its summation order is the GEMM library's, so logits are compared at the reference's own
+    GPU-test tolerances (1e-4 / 5e-3), the index of the last row exactly (a planted winner decides it)."""
+    c = wl.lm_head_case(rows, 1024, wl.VOCAB, seed=6700 + rows, dtype=dtype)
+    planted = 1000 + 37 * rows
+    c["table"][planted] = (c["hidden"][rows - 1].astype(np.float32) * np.float32(0.02)).astype(dtype)
+    h, t = dev(c["hidden"]), dev(c["table"])
+    want_logits = torch.empty(rows, wl.VOCAB, dtype=h.dtype, device=DEV)
+    want_id = refcu.lm_head_argmax(h, t, rows, 1024, wl.VOCAB, code(h), want_logits)
+    assert want_id == planted
+    tol = 1e-4 if dtype == np.float32 else 5e-3
+    for mode in ("fast", "deterministic"):
+        got_logits = torch.empty_like(want_logits)
+        ids = ops.lm_head_argmax(h, t, logits_out=got_logits, mode=mode)
+        assert int(ids[rows - 1]) == want_id
+        scale = max(1.0, float(want_logits.float().abs().max()))
+        assert float((got_logits.float() - want_logits.float()).abs().max()) <= tol * scale
+
