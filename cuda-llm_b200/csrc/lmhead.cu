@@ -199,16 +199,22 @@ lm_head_argmax_kernel(const T* __restrict__ hidden, const T* __restrict__ table,
 // data in flight, so the hidden rows move to shared memory as fp32 and a warp takes J = 4 table rows
 // per step: every 32 bytes a lane reads from shared memory (8 hidden values of one row) meet 4 table
 // vectors, which keeps shared-memory traffic at R/2 times the table's (2x for four rows).  K is walked
-// in chunks of 32 lanes x 4 vectors; the J x 4 streaming loads of a chunk are all issued before its
-// arithmetic, and three thread blocks of four warps per SM keep ~100 KB of the table in flight per SM.
+// in chunks of 32 lanes x 4 vectors; the J x 4 streaming loads of a chunk are issued back to back: for fp32
+// right before the chunk's arithmetic (three thread blocks of four warps per SM, ~100 KB of the table in
+// flight per SM), for fp16, which carries twice the arithmetic per byte, one chunk ahead (two blocks per
+// SM).  Packed fp32x2 multiply-adds; hidden rows laid out in two planes so shared-memory reads are free
+// of bank conflicts.  Measured and dropped: staging the table through shared memory with bulk copies
+// (cp.async.bulk + mbarrier rings, 16 KB in flight per warp at no register cost) was slower (62.8 us
+// against 58.4 for four fp16 rows): the kernel is bound by its own instruction stream there (2 FMAs per
+// byte), not by copy latency, and the extra shared-memory reads cost more than the registers they freed.
 // H is a multiple of the chunk (1024 fp16 / 512 fp32 elements).
 // ---------------------------------------------------------------------------
 constexpr int kLmSmemThreads = 128;
 constexpr int kLmSmemWarps = kLmSmemThreads / kWarpSize;
 constexpr int kLmChunkVecs = 4;
 
-template <typename T, int R, int J>
-__global__ void __launch_bounds__(kLmSmemThreads, 3)
+template <typename T, int R, int J, bool kAhead>
+__global__ void __launch_bounds__(kLmSmemThreads, kAhead ? 2 : 3)
 lm_head_argmax_smem_kernel(const T* __restrict__ hidden, const T* __restrict__ table, int64_t vocab, int H, int64_t index_base,
                            T* __restrict__ logits_out, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
                            unsigned long long* keys, unsigned int* ticket, int valid) {
@@ -222,16 +228,24 @@ lm_head_argmax_smem_kernel(const T* __restrict__ hidden, const T* __restrict__ t
   __shared__ int slot_i[kLmSmemWarps][16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-  for (int i = threadIdx.x; i < R * H / N; i += kLmSmemThreads) {
+  // Layout of a hidden row in shared memory: the first four floats of every 16-byte table vector in one plane,
+  // the next four (fp16 vectors hold eight) in a second plane H/2 floats further on, so that the lanes of a warp
+  // read consecutive 16-byte pieces of a plane: no bank conflicts (eight floats per lane side by side would put
+  // lanes i and i+4 on the same banks).
+  constexpr int P = N / 4;
+  const int plane = H / P, vecs_per_row = H / N;
+  for (int i = threadIdx.x; i < R * vecs_per_row; i += kLmSmemThreads) {
+    const int r = i / vecs_per_row, v = i - r * vecs_per_row;
     float f[N];
-    if (i * N < valid * H) {                     // three rows ride in the four-row kernel: the fourth is zeros
+    if (r < valid) {                             // three rows ride in the four-row kernel: the fourth is zeros
       Elem<T>::unpack(ld_reuse(hidden + int64_t(i) * N), f);
     } else {
 #pragma unroll
       for (int q = 0; q < N; ++q) f[q] = 0.0f;
     }
 #pragma unroll
-    for (int q = 0; q < N; q += 4) *reinterpret_cast<float4*>(hs + i * N + q) = make_float4(f[q], f[q + 1], f[q + 2], f[q + 3]);
+    for (int q = 0; q < P; ++q)
+      *reinterpret_cast<float4*>(hs + r * H + q * plane + v * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
   }
   __syncthreads();
 
@@ -241,44 +255,64 @@ lm_head_argmax_smem_kernel(const T* __restrict__ hidden, const T* __restrict__ t
   int bi = kLmNone;
   const int chunks = H / kChunk;
   const int64_t total_warps = int64_t(gridDim.x) * kLmSmemWarps;
-  for (int64_t p = int64_t(blockIdx.x) * kLmSmemWarps + warp; p * J < vocab; p += total_warps) {
-    const T* rows[J];
+  // one chunk of J table rows: J x KC streaming loads, all issued back to back
+  auto load_chunk = [&](int64_t p, int c, uint4 (&dst)[J][KC]) {
 #pragma unroll
     for (int jj = 0; jj < J; ++jj) {
       int64_t j = p * J + jj;
       if (j >= vocab) j = vocab - 1;             // a ragged last step re-reads a row; its sums are dropped below
-      rows[jj] = table + j * H + lane * N;
+      const T* row = table + j * H + c * kChunk + lane * N;
+#pragma unroll
+      for (int k = 0; k < KC; ++k) dst[jj][k] = ld_stream(row + k * kWarpSize * N);
     }
+  };
+  int64_t p = int64_t(blockIdx.x) * kLmSmemWarps + warp;
+  uint4 w[J][KC];
+  if constexpr (kAhead) { if (p * J < vocab) load_chunk(p, 0, w); }
+  for (; p * J < vocab; p += total_warps) {
     // packed fp32x2 arithmetic (one instruction per two multiply-adds): even and odd k accumulate apart
     float2 acc2[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc2[m] = make_float2(0.0f, 0.0f);
     for (int c = 0; c < chunks; ++c) {
-      uint4 w[J][KC];
-#pragma unroll
-      for (int jj = 0; jj < J; ++jj)
-#pragma unroll
-        for (int k = 0; k < KC; ++k) w[jj][k] = ld_stream(rows[jj] + c * kChunk + k * kWarpSize * N);
+      // kAhead: the chunk after this one (of these rows, or the first of the next rows) is requested before this
+      // chunk's arithmetic, so the copy latency and the arithmetic overlap inside one warp
+      uint4 nx[J][KC];
+      if constexpr (kAhead) {
+        const bool last = c + 1 == chunks;
+        const int64_t pn = last ? p + total_warps : p;
+        if (pn * J < vocab) load_chunk(pn, last ? 0 : c + 1, nx);
+      } else {
+        load_chunk(p, c, w);
+      }
 #pragma unroll
       for (int k = 0; k < KC; ++k) {
         float2 f[J][N / 2];
 #pragma unroll
         for (int jj = 0; jj < J; ++jj) Elem<T>::unpack2(w[jj][k], f[jj]);
-        const float* hk = hs + c * kChunk + (k * kWarpSize + lane) * N;
+        const float* hk = hs + ((c * KC + k) * kWarpSize + lane) * 4;
+        float2 hr[R][N / 2];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          float2 hr[N / 2];
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-          for (int q = 0; q < N / 4; ++q) {
-            const float4 t = *reinterpret_cast<const float4*>(hk + r * H + 4 * q);
-            hr[2 * q] = make_float2(t.x, t.y);
-            hr[2 * q + 1] = make_float2(t.z, t.w);
+          for (int q = 0; q < P; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(hk + r * H + q * plane);
+            hr[r][2 * q] = make_float2(t.x, t.y);
+            hr[r][2 * q + 1] = make_float2(t.z, t.w);
           }
+        // q outermost: consecutive multiply-adds go to J * R different accumulators, none waits for the one before
+#pragma unroll
+        for (int q = 0; q < N / 2; ++q)
 #pragma unroll
           for (int jj = 0; jj < J; ++jj)
 #pragma unroll
-            for (int q = 0; q < N / 2; ++q) acc2[jj * R + r] = __ffma2_rn(f[jj][q], hr[q], acc2[jj * R + r]);
-        }
+            for (int r = 0; r < R; ++r) acc2[jj * R + r] = __ffma2_rn(f[jj][q], hr[r][q], acc2[jj * R + r]);
+      }
+      if constexpr (kAhead) {
+#pragma unroll
+        for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+          for (int k = 0; k < KC; ++k) w[jj][k] = nx[jj][k];
       }
     }
     float acc[M];
@@ -389,7 +423,10 @@ int launch_smem(const T* hidden, const T* table, int64_t vocab, int64_t H, int64
                 int64_t logits_stride, int32_t* out_ids, int64_t* out_keys, unsigned long long* keys, unsigned int* ticket,
                 int valid, cudaStream_t s) {
   constexpr int J = 4;
-  auto kernel = lm_head_argmax_smem_kernel<T, R, J>;
+  // fp16 rows carry twice the arithmetic per byte: there the next chunk is requested ahead of the arithmetic
+  // fp16 rows carry twice the arithmetic per byte: there the next chunk is requested ahead of the arithmetic
+  // (measured on 4 x 1024 by 151936 x 1024: 58.4 us against 60.2; fp32 is at the copy rate either way)
+  auto kernel = lm_head_argmax_smem_kernel<T, R, J, (Elem<T>::kPerVec == 8 && R >= 2)>;
   const size_t smem = size_t(R) * size_t(H) * sizeof(float);
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
