@@ -104,6 +104,23 @@ def sharded_argmax(logits_shard: torch.Tensor, index_base: int, group=None, keys
     return out
 
 
+def sharded_lm_head_argmax(hidden: torch.Tensor, table_shard: torch.Tensor, index_base: int, group=None,
+                           keys: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy pick over a tied embedding whose rows [index_base, index_base + shard rows) live on this rank
+    (a vocabulary-parallel LM head): every rank reads only its slice of the table once
+    (b2_lm_head_argmax, keys form), then one all-reduce(MAX) of `rows` packed keys and the decode, exactly
+    the exchange of sharded_argmax; no logits tensor exists anywhere."""
+    rows = hidden.shape[0]
+    if keys is None:
+        keys = torch.empty(rows, dtype=torch.int64, device=hidden.device)
+    _ops.lm_head_argmax(hidden, table_shard, want_ids=False, keys_out=keys, index_base=index_base)
+    keys = allreduce_argmax_keys(keys, group)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=keys.device)
+    _lib.check(_lib.load().b2_argmax_decode_keys(keys.data_ptr(), rows, out.data_ptr(), _ops._stream()))
+    return out
+
+
 def _rebase_kernel(row_max: torch.Tensor, global_max: torch.Tensor, row_sum: torch.Tensor) -> None:
     _lib.check(_lib.load().b2_softmax_rebase(row_max.data_ptr(), global_max.data_ptr(), row_sum.data_ptr(),
                                              row_sum.shape[0], _ops._stream()))

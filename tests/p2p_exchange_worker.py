@@ -41,6 +41,17 @@ def main():
             nccl = sharded.sharded_softmax(shard).cpu().numpy().astype(np.float64)
             assert float((np.abs(got - nccl) / np.maximum(exact, floor)).max()) <= 1e-5
         assert not ex.timed_out()
+        # vocabulary-parallel LM head: every rank reads its rows of the tied embedding once; planted winners
+        lm = wl.lm_head_case(4, 1024, wl.VOCAB, seed=6800, dtype=np.float16)
+        planted = np.array([11, wl.VOCAB // 2 - 1, wl.VOCAB // 2, wl.VOCAB - 1], np.int32)
+        for r in range(4):
+            lm["table"][planted[r]] = (lm["hidden"][r].astype(np.float32) * np.float32(0.02)).astype(np.float16)
+        tlo, thi = wl.shard_range(wl.VOCAB, world, rank)
+        hidden = torch.from_numpy(lm["hidden"]).to(device)
+        table_shard = torch.from_numpy(np.ascontiguousarray(lm["table"][tlo:thi])).to(device)
+        for call in range(3):
+            ids = sharded.sharded_lm_head_argmax(hidden, table_shard, tlo)
+            assert np.array_equal(ids.cpu().numpy(), planted), f"rank {rank} call {call}: sharded LM head"
     finally:
         ex.close()
     dist.barrier()

@@ -62,7 +62,15 @@ def _worker(rank, world, tcp_port, rows, width, seed, result_dir):
         local_sum.mul_(torch.exp(local_max - global_max))
     gmax, gsum = sharded.allreduce_softmax_stats(torch.from_numpy(m.copy()), torch.from_numpy(s.copy()), rebase)
     probs = np.exp(mine.astype(np.float64) - gmax.numpy()[:, None]) / gsum.numpy()[:, None].astype(np.float64)
-    np.savez(os.path.join(result_dir, f"rank{rank}.npz"), ids=ids, probs=probs, lo=lo, hi=hi)
+    # vocabulary-parallel LM head: the table's rows split over the ranks, local logits -> keys -> the same exchange
+    lm = wl.lm_head_case(3, 64, 500, seed=seed + 1, dtype=np.float32)
+    tlo, thi = wl.shard_range(500, world, rank)
+    part = port.linear(lm["hidden"], lm["table"][tlo:thi])
+    best = port.argmax_rows(part)
+    lm_keys = torch.tensor([port.argmax_key(float(part[r, best[r]]), tlo + int(best[r])) for r in range(3)], dtype=torch.int64)
+    sharded.allreduce_argmax_keys(lm_keys)
+    lm_ids = np.array([sharded.decode_key(int(k)) for k in lm_keys], np.int32)
+    np.savez(os.path.join(result_dir, f"rank{rank}.npz"), ids=ids, probs=probs, lo=lo, hi=hi, lm_ids=lm_ids)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -76,7 +84,10 @@ def test_vocab_sharded_protocols_over_gloo(port, tmp_path, world):
     # the protocol is checked against the exact (fp64) softmax instead
     want_ids, want_p = port.argmax_rows(x), port.softmax_f64(x)
     parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    lm = wl.lm_head_case(3, 64, 500, seed=seed + 1, dtype=np.float32)
+    want_lm = port.argmax_rows(port.linear(lm["hidden"], lm["table"]))
     for p in parts:
         assert np.array_equal(p["ids"], want_ids)               # every rank holds the global winner
+        assert np.array_equal(p["lm_ids"], want_lm)
     probs = np.concatenate([p["probs"] for p in parts], axis=1)
     assert (np.abs(probs - want_p) <= 1e-5 * want_p.max(axis=1, keepdims=True)).all()
