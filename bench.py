@@ -320,6 +320,18 @@ def reference_gpu_kernels(L, lib, dev, stream):
     return out
 
 
+_REAL_STDOUT = None
+
+
+def emit(text: str) -> None:
+    """The one JSON line, to the process's original stdout."""
+    sys.stdout.flush()
+    if _REAL_STDOUT is None:
+        print(text)
+    else:
+        os.write(_REAL_STDOUT, (text + "\n").encode())
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -328,7 +340,7 @@ def reference_arm(args):
     per_step = min(1.0, 120.0 / max(1, total))
     gbs, sec, desc = cpu_baseline(per_step, steps=args.steps, warmup=args.warmup)
     desc["value"] = round(gbs, 4)
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_block(args.gpus),
@@ -351,6 +363,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--rows", type=int, default=ROWS, help=argparse.SUPPRESS)   # smaller cases for profiler captures
     args = ap.parse_args()
+    # stdout carries exactly one JSON line: anything a library prints there meanwhile (NCCL's version banner, for
+    # one) goes to stderr instead; emit() writes to the real stdout
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -492,7 +510,7 @@ def main():
         line["ops"] = op_table
     if ref_gpu is not None:
         line["reference_cuda_kernels_on_this_gpu"] = ref_gpu
-    print(json.dumps(line))
+    emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
