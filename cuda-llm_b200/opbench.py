@@ -89,6 +89,22 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
             ms = timed(calls, nreps(20 if rows >= 4096 else 100))
             record("add_rms_norm", f"{rows}x{hidden} f16", per_set + 2 * hidden, ms, rows,
                    note=None if rows >= 4096 else "latency-bound: cannot fill the GPU")
+            if rows <= 4096:
+                # launches this short are paced by the host's launch path: the same launches recorded once into a CUDA
+                # graph (24 in a row over the rotating buffer sets) and replayed give the device-side time per launch
+                try:
+                    K = 24
+                    replayed = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(replayed, stream=stream):
+                        for i in range(K):
+                            calls[i % n]()
+                    ms_g = timed([replayed.replay], nreps(10)) / K
+                    gbs_g = (per_set + 2 * hidden) / (ms_g * 1e-3) / 1e9
+                    table[-1].update({"us_graph_replay": round(ms_g * 1e3, 2), "gbs_graph_replay": round(gbs_g, 1),
+                                      "frac_measured_copy_graph_replay": round(gbs_g / peak, 4)})
+                    del replayed
+                except Exception as exc:   # a measurement aid, not a requirement
+                    table[-1]["graph_replay_error"] = str(exc)[:120]
             del bufs, calls
     if quick:
         return table
