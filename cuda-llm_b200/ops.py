@@ -399,12 +399,13 @@ def cuda_argmax_last_row(logits) -> int:
 
 
 def lm_head_argmax(hidden, table, logits_out=None, mode: Optional[str] = None, want_ids: bool = True,
-                   keys_out=None, index_base: int = 0):
+                   keys_out=None, index_base: int = 0, ids_out=None):
     """Decode-size LM head fused with the greedy pick (b2_lm_head_argmax): int32[rows] arg-max of
     hidden[rows, H] x table[V, H]^T in one pass over the table.  ``logits_out`` ([rows, V], same dtype)
     also receives the logits, as cuda_lm_head (include/llm/ops_cuda.h:157; src/ops_cuda.cu:885) would
     return them; ``keys_out`` (int64[rows]) receives the packed keys of a vocabulary-sharded table whose
-    first row has global index ``index_base``.  Replaces cuda_lm_head + cuda_argmax_last_row
+    first row has global index ``index_base``; with ``ids_out`` (int32[rows]) given nothing is allocated, so
+    the call can be recorded into a CUDA graph.  Replaces cuda_lm_head + cuda_argmax_last_row
     (src/qwen3_cuda_model.cpp:1070-1071,1339) for decode batches."""
     op = "lm_head_argmax"
     _req(hidden, op)
@@ -421,7 +422,9 @@ def lm_head_argmax(hidden, table, logits_out=None, mode: Optional[str] = None, w
         _output_req(logits_out, (rows, vocab), hidden.dtype, op)
     if keys_out is not None and (not keys_out.is_cuda or keys_out.dtype != torch.int64 or tuple(keys_out.shape) != (rows,)):
         raise ValueError(f"{op}: keys must be CUDA int64 [rows]")
-    ids = torch.empty(rows, dtype=torch.int32, device=hidden.device) if want_ids else None
+    if ids_out is not None and (not ids_out.is_cuda or ids_out.dtype != torch.int32 or tuple(ids_out.shape) != (rows,)):
+        raise ValueError(f"{op}: ids must be CUDA int32 [rows]")
+    ids = ids_out if ids_out is not None else (torch.empty(rows, dtype=torch.int32, device=hidden.device) if want_ids else None)
     m = _mode() if mode is None else {"fast": 0, "deterministic": 1}[mode]
     ws = argmax_workspace(hidden.device, max(rows, 1))
     _lib.check(_lib.load().b2_lm_head_argmax(_ptr(hidden), _ptr(table), rows, hsz, vocab, _code(hidden), m, index_base,

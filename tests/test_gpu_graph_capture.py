@@ -113,3 +113,48 @@ def test_sampling_and_the_paged_attention_prologue_replay_from_a_cuda_graph(b2):
     for a, b in zip(again, captured):
         assert torch.equal(a, b)
     assert captured[0].tolist() == [77] * batch
+
+
+@pytest.mark.parametrize("batch", [1, 3, 4])
+def test_decode_tail_replays_from_a_cuda_graph(b2, port, batch):
+    """Final norm + LM head + greedy pick, the tail of the reference's graph-captured decode step
+    (src/qwen3_cuda_model.cpp:1069-1071 followed by the argmax of :1339), as two launches in a graph."""
+    rng = np.random.default_rng(40 + batch)
+    vocab = 20000
+    hidden = torch.from_numpy(wl.normal(rng, (batch, 1024), dtype=np.float16)).to(DEV)
+    w = torch.from_numpy(wl.gamma(rng, 1024, dtype=np.float16)).to(DEV)
+    table = torch.from_numpy(wl.normal(rng, (vocab, 1024), 0.02, np.float16)).to(DEV)
+    normed = torch.zeros_like(hidden)
+    ids = torch.zeros(batch, dtype=torch.int32, device=DEV)
+
+    def tail():
+        ops.cuda_rms_norm_out(hidden, w, wl.EPS, normed)
+        ops.lm_head_argmax(normed, table, ids_out=ids)
+
+    tail()                                      # warms the library's per-device state before capture
+    torch.cuda.synchronize()
+    want = ids.clone()
+    ids.zero_()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            tail()
+    assert int(ids.abs().sum().item()) == 0     # nothing ran during capture
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(ids, want)
+    # new hidden rows, same graph; checked against the CPU operators on the normalised rows the graph produced
+    hidden.copy_(torch.from_numpy(wl.normal(rng, (batch, 1024), dtype=np.float16)).to(DEV))
+    graph.replay()
+    torch.cuda.synchronize()
+    n32 = port.decode_f16(normed.cpu().numpy().view(np.uint16)).reshape(batch, 1024)
+    t32 = port.decode_f16(table.cpu().numpy().view(np.uint16)).reshape(vocab, 1024)
+    stored = port.linear(n32, t32).astype(np.float16)
+    ours = torch.empty(batch, vocab, dtype=torch.float16, device=DEV)
+    assert torch.equal(ops.lm_head_argmax(normed, table, logits_out=ours), ids)
+    assert np.array_equal(ids.cpu().numpy(), port.argmax_rows(ours.cpu().numpy().view(np.uint16)))
+    close = np.abs(ours.cpu().numpy().astype(np.float64) - stored.astype(np.float64)) <= 2.0 ** -10 * np.maximum(np.abs(stored), 1.0)
+    assert close.all()
+

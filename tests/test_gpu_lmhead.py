@@ -216,3 +216,12 @@ def test_argument_rules(b2):
         ops.lm_head_argmax(h, t, want_ids=False)                             # no output at all
     with pytest.raises(ValueError):
         ops.lm_head_argmax(torch.zeros(1, 9000, device=DEV), torch.zeros(3, 9000, device=DEV))   # hidden_size > 8192
+    # no rows: nothing to do, nothing dereferenced (empty batches reach the C ABI as they are)
+    from cuda_llm_b200 import lib
+    ids = torch.full((1,), 7, dtype=torch.int32, device=DEV)
+    assert b2.b2_lm_head_argmax(None, None, 0, 1024, 10, lib.F32, lib.FAST, 0, None, 10, ids.data_ptr(), None, None,
+                                torch.cuda.current_stream().cuda_stream) == 0
+    assert int(ids[0]) == 7
+    assert b2.b2_lm_head_argmax(h.data_ptr(), t.data_ptr(), 2, 1024, 10, lib.F32, 5, 0, None, 10, ids.data_ptr(), None, None,
+                                torch.cuda.current_stream().cuda_stream) == -1      # unknown mode
+
