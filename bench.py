@@ -213,6 +213,11 @@ def cpu_operator_table():
           lambda: port.argmax_rows(logits), None, kind="port")
     entry("sample top_k=50 top_p=0.95 (C restatement of the device rule)", "4 x 151936 f32", 4, 151936 * 4,
           lambda: [port.sample_row(logits[r], 0.8, 50, 0.95, 7, r) for r in range(4)], None, kind="port")
+    lm_table = rng.standard_normal((16384, 1024), dtype=f) * f(0.02)
+    lm_hidden = rng.standard_normal((1, 1024), dtype=f)
+    entry("lm_head, one hidden row (unit: table rows; 16384 of the vocabulary's 151936, cost is linear in them)",
+          "1 x 1024 by 16384 x 1024 f32", 16384, 1024 * 2, lambda: ref.lm_head(lm_hidden, lm_table),
+          split(lambda t: ref.lm_head(lm_hidden, t), lm_table))
     return {"threads_available": threads, "entries": table}
 
 
