@@ -464,13 +464,10 @@ int launch_ordered(const T* hidden, const T* table, int64_t vocab, int64_t H, in
   return launch_status("lm_head_argmax (ordered)");
 }
 
-// 1 where the register-resident kernel is built for this hidden size (it then serves single rows), else 0
-template <typename T> int fast_rows_per_pass(int64_t H) {
-  // a lane keeps H / 32 fp32 registers of the hidden row and one table row's worth of 16-byte vectors
-  if (H == 1024 || H == 2048) return 1;
-  if (H == 4096) return Elem<T>::kPerVec == 8 ? 1 : 0;   // fp32 rows of 4096 do not fit the register file
-  return 0;
-}
+// 1 where the register-resident kernel is built for this hidden size (it then serves single rows), else 0.
+// Only hidden size 1024: at 2048 and 4096 a lane would keep 64-128 hidden values and a whole table row's vectors in
+// registers, one block per SM, and measured slower than the shared-memory kernel (fp16 2048: 105 us against 93).
+template <typename T> int fast_rows_per_pass(int64_t H) { return H == 1024 ? 1 : 0; }
 
 template <typename T>
 int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t H, int64_t vocab, int mode,
@@ -506,16 +503,8 @@ int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t 
 #define B2_LM_ORD(RR) \
   rc = launch_ordered<T, RR>(hp, table, vocab, H, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
     if (use_reg) {
-      constexpr int KV1 = 1024 / (kWarpSize * N), KV2 = 2 * KV1;
-      [[maybe_unused]] constexpr int KV4 = 4 * KV1;
-      if (H == 1024) {
-        B2_LM_FAST(KV1, 1, (N == 8 ? 2 : 1), true);
-      } else if (H == 2048) {
-        B2_LM_FAST(KV2, 1, 1, true);
-      } else {
-        if constexpr (N == 8) B2_LM_FAST(KV4, 1, 1, false);
-        else rc = B2_ERR_UNSUPPORTED;
-      }
+      constexpr int KV1 = 1024 / (kWarpSize * N);
+      B2_LM_FAST(KV1, 1, (N == 8 ? 2 : 1), true);
     } else if (use_smem) {
       if (R >= 3) B2_LM_SMEM(4);
       else if (R == 2) B2_LM_SMEM(2);
