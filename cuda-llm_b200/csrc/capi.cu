@@ -465,6 +465,17 @@ int b2_argmax_rows_sharded(const void* logits, int64_t rows, int64_t width, int6
   return launch_argmax_exchange(logits, rows, width, row_stride, dtype, index_base, out_ids, workspace, xa, as_stream(stream));
 }
 
+int b2_argmax_keys_exchange(const int64_t* keys, int64_t rows, int32_t* out_ids, const b2_p2p_exchange* exchange,
+                            int32_t* status, b2_stream stream) {
+  const char* op = "b2_argmax_keys_exchange";
+  B2_REQUIRE(rows >= 0 && rows < (1 << 24), op, "rows must be >= 0");
+  B2_REQUIRE(rows == 0 || (keys && out_ids), op, "null pointer");
+  ExchangeArgs xa;
+  const int rc = exchange_checks(op, exchange, rows, status, &xa);
+  if (rc != B2_OK) return rc;
+  return launch_argmax_keys_exchange(keys, rows, out_ids, xa, as_stream(stream));
+}
+
 int b2_softmax_stats_sharded(const void* x, int64_t rows, int64_t width, int dtype, float* global_max, float* global_sum,
                              const b2_p2p_exchange* exchange, int32_t* status, b2_stream stream) {
   const char* op = "b2_softmax_stats_sharded";

@@ -67,6 +67,7 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
 struct ExchangeArgs;
 int launch_argmax_exchange(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
                            int64_t index_base, int32_t* out_ids, void* workspace, const ExchangeArgs& xa, cudaStream_t s);
+int launch_argmax_keys_exchange(const int64_t* keys, int64_t rows, int32_t* out_ids, const ExchangeArgs& xa, cudaStream_t s);
 int launch_softmax_stats_exchange(const void* x, int64_t rows, int64_t width, int dtype, float* global_max,
                                   float* global_sum, const ExchangeArgs& xa, cudaStream_t s);
 

@@ -187,6 +187,20 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
   });
 }
 
+// The exchange alone, for keys that another kernel produced (the vocabulary-parallel LM head): one thread block
+// copies this GPU's keys into its exchange slot and runs the same tail as above.
+__global__ void __launch_bounds__(kArgThreads)
+argmax_keys_exchange_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids, const __grid_constant__ ExchangeArgs xa) {
+  unsigned long long* own = exchange_own_slot(xa);
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) own[r] = static_cast<unsigned long long>(keys[r]) ^ kSignBit;
+  __syncthreads();
+  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
+    unsigned long long best = 0ull;
+    for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
+    out_ids[r] = best == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(best & 0xffffffffull));
+  });
+}
+
 __global__ void argmax_decode_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids) {
   const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (r >= rows) return;
@@ -1115,6 +1129,12 @@ int launch_argmax_exchange(const void* logits, int64_t rows, int64_t width, int6
   return dtype == B2_F32
              ? launch_argmax_exchange_typed<float>(logits, rows, width, row_stride, index_base, out_ids, workspace, xa, s)
              : launch_argmax_exchange_typed<__half>(logits, rows, width, row_stride, index_base, out_ids, workspace, xa, s);
+}
+
+int launch_argmax_keys_exchange(const int64_t* keys, int64_t rows, int32_t* out_ids, const ExchangeArgs& xa, cudaStream_t s) {
+  if (rows == 0) return B2_OK;
+  argmax_keys_exchange_kernel<<<1, kArgThreads, 0, s>>>(keys, rows, out_ids, xa);
+  return launch_status("argmax_keys_exchange");
 }
 
 int launch_softmax_stats_exchange(const void* x, int64_t rows, int64_t width, int dtype, float* global_max,

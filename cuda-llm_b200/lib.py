@@ -70,6 +70,7 @@ _SIGNATURES = {
     "b2_argmax_rows": (_i, [_p, _i64, _i64, _i64, _i, _p, _p, _p]),
     "b2_argmax_rows_static": (_i, [_p, _i64, _i64, _i64, _i, _p, _p]),
     "b2_argmax_keys": (_i, [_p, _i64, _i64, _i64, _i, _i64, _p, _p, _p]),
+    "b2_argmax_keys_exchange": (_i, [_p, _i64, _p, _p, _p, _p]),
     "b2_lm_head_argmax": (_i, [_p, _p, _i64, _i64, _i64, _i, _i, _i64, _p, _i64, _p, _p, _p, _p]),
     "b2_argmax_decode_keys": (_i, [_p, _i64, _p, _p]),
     "b2_softmax_workspace_bytes": (_sz, [_i64]),

@@ -245,6 +245,23 @@ def sharded_argmax_fused(logits_shard: torch.Tensor, index_base: int, exchange: 
     return out
 
 
+def sharded_lm_head_argmax_fused(hidden: torch.Tensor, table_shard: torch.Tensor, index_base: int, exchange: PeerExchange,
+                                 keys: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sharded_lm_head_argmax without a collective library call: the LM-head kernel leaves this GPU's packed keys
+    on the device and one small kernel (b2_argmax_keys_exchange) stores them into every peer's exchange buffer over
+    NVLink, waits (bounded) for the peers' and writes the global winners' indices."""
+    rows = hidden.shape[0]
+    if keys is None:
+        keys = torch.empty(rows, dtype=torch.int64, device=hidden.device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=hidden.device)
+    _ops.lm_head_argmax(hidden, table_shard, want_ids=False, keys_out=keys, index_base=index_base)
+    import ctypes as C
+    _lib.check(_lib.load().b2_argmax_keys_exchange(keys.data_ptr(), rows, out.data_ptr(), C.byref(exchange.desc),
+                                                   exchange.status.data_ptr(), _ops._stream()))
+    return out
+
+
 def sharded_softmax_fused(logits_shard: torch.Tensor, exchange: PeerExchange, out: Optional[torch.Tensor] = None,
                           stats: Optional[torch.Tensor] = None) -> torch.Tensor:
     """sharded_softmax as two kernels per GPU and no collective library call: the statistics kernel

@@ -366,6 +366,15 @@ B2_API int b2_argmax_rows_sharded(const void* logits, int64_t rows, int64_t widt
                                   int64_t index_base, int32_t* out_ids, void* workspace,
                                   const b2_p2p_exchange* exchange, int32_t* status, b2_stream stream);
 
+/* The exchange of b2_argmax_rows_sharded alone, for keys another kernel produced (b2_argmax_keys, or
+ * b2_lm_head_argmax over this GPU's rows of a vocabulary-split embedding): this GPU's `rows` packed keys go to
+ * every peer, and out_ids[r] receives the index of the largest key of all GPUs for row r.  One small launch in
+ * place of ncclAllReduce(MAX) + b2_argmax_decode_keys; same buffers, same calling rules (a collective: every GPU
+ * makes the same sequence of calls on the exchange) and the same bounded wait as b2_argmax_rows_sharded.
+ * No reference counterpart: the reference is single-GPU. */
+B2_API int b2_argmax_keys_exchange(const int64_t* keys, int64_t rows, int32_t* out_ids,
+                                   const b2_p2p_exchange* exchange, int32_t* status, b2_stream stream);
+
 /* Row statistics of the WHOLE row from this GPU's columns: global_max[r] = max over all ranks,
  * global_sum[r] = sum over all ranks of exp(x - global_max[r]); follow with
  * b2_softmax_apply(x, out, rows, width, dtype, global_max, global_sum).

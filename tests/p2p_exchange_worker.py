@@ -52,6 +52,9 @@ def main():
         for call in range(3):
             ids = sharded.sharded_lm_head_argmax(hidden, table_shard, tlo)
             assert np.array_equal(ids.cpu().numpy(), planted), f"rank {rank} call {call}: sharded LM head"
+            ids = sharded.sharded_lm_head_argmax_fused(hidden, table_shard, tlo, ex)
+            assert np.array_equal(ids.cpu().numpy(), planted), f"rank {rank} call {call}: sharded LM head, keys exchange"
+        assert not ex.timed_out()
     finally:
         ex.close()
     dist.barrier()

@@ -75,6 +75,37 @@ def test_fused_argmax_ranks_in_turn(b2, port, world):
     assert ops.cuda_argmax_last_row(dev(x)) == int(want[-1])   # the context is fine after the timeouts
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_sharded_lm_head_keys_exchange_ranks_in_turn(b2, port, world):
+    """Vocabulary-parallel LM head: every emulated rank runs b2_lm_head_argmax over its rows of the table (keys
+    form), then b2_argmax_keys_exchange; rank 0, last, must hold the pick over the whole table."""
+    L = b2
+    rows, vocab = 5, 4096
+    c = wl.lm_head_case(rows, 1024, vocab, seed=7100 + world, dtype=np.float16)
+    f32 = lambda a: port.decode_f16(np.ascontiguousarray(a).view(np.uint16)).reshape(a.shape)
+    stored = port.linear(f32(c["hidden"]), f32(c["table"])).astype(np.float16)
+    want = port.argmax_rows(stored.view(np.uint16))
+    hidden = dev(c["hidden"])
+    shards = [dev(c["table"][slice(*wl.shard_range(vocab, world, r))]) for r in range(world)]
+    lw = LocalWorld(L, world, rows, patience_ms=3)
+    ws = ops.argmax_workspace(torch.device(DEV), rows)
+    keys = [torch.zeros(rows, dtype=torch.int64, device=DEV) for _ in range(world)]
+    outs = [torch.full((rows,), -1, dtype=torch.int32, device=DEV) for _ in range(world)]
+    for call in range(3):
+        for r in reversed(range(world)):
+            lo, hi = wl.shard_range(vocab, world, r)
+            lib.check(L.b2_lm_head_argmax(hidden.data_ptr(), shards[r].data_ptr(), rows, 1024, hi - lo, lib.F16, lib.DETERMINISTIC,
+                                          lo, None, hi - lo, None, keys[r].data_ptr(), ws.data_ptr(), stream()))
+            lib.check(L.b2_argmax_keys_exchange(keys[r].data_ptr(), rows, outs[r].data_ptr(), C.byref(lw.desc[r]),
+                                                lw.status[r].data_ptr(), stream()))
+            torch.cuda.synchronize()
+        assert int(lw.status[0].item()) == 0
+        assert np.array_equal(host(outs[0]), want), f"call {call}"
+        for r in range(1, world):
+            assert int(lw.status[r].item()) == 2          # nobody answered within its patience: reported, not hung
+        outs[0].fill_(-1)
+
+
 @pytest.mark.parametrize("world", [1, 4])
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
 def test_fused_softmax_ranks_in_turn(b2, port, world, dtype):
