@@ -134,7 +134,37 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
         _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
     if world == 1 and want("lm_head"):
         _lm_head(L, lib, dev, s, timed, record, randn, nreps)
+    if world > 1 and want("lm_head"):
+        _lm_head_sharded(lib, dev, timed, record, randn, nreps, sharded, world, rank, table)
     return table
+
+
+def _lm_head_sharded(lib, dev, timed, record, randn, nreps, sharded, world, rank, table):
+    """Vocabulary-parallel LM head + greedy pick: every GPU reads its rows of the 151936 x 1024 fp16 table once; the
+    packed keys are combined by an NCCL all-reduce (MAX) or by this library's own exchange kernel (peer stores)."""
+    H, R = 1024, 4
+    lo, hi = sharded.column_range(VOCAB, world, rank)
+    shards = [randn(hi - lo, H, sigma=0.02) for _ in range(2)]
+    hidden = randn(R, H)
+    keys = torch.empty(R, dtype=torch.int64, device=dev)
+    ids = torch.empty(R, dtype=torch.int32, device=dev)
+    local_bytes = (hi - lo) * H * 2 + R * H * 2 + 4 * R
+    shape = f"{R} x {H} by {VOCAB}/{world} x {H} f16"
+    ms = timed([(lambda t=t: sharded.sharded_lm_head_argmax(hidden, t, lo, keys=keys, out=ids)) for t in shards], nreps(40))
+    record("lm_head_argmax (vocab-parallel + all-reduce MAX of packed keys), eager launches", shape, local_bytes, ms, R,
+           sharded_over=world)
+    ex = sharded.PeerExchange(max_rows=R)
+    try:
+        ms = timed([(lambda t=t: sharded.sharded_lm_head_argmax_fused(hidden, t, lo, ex, keys=keys, out=ids)) for t in shards],
+                   nreps(40))
+        record("lm_head_argmax (vocab-parallel + keys exchange kernel, peer stores over NVLink), eager launches", shape,
+               local_bytes, ms, R, sharded_over=world, note="two launches per GPU, no collective library call")
+        if ex.timed_out():
+            table.append({"op": "vocab-parallel lm_head, keys exchange", "error": "a bounded wait for a peer ran out"})
+    except Exception as exc:
+        table.append({"op": "vocab-parallel lm_head, keys exchange", "error": str(exc)[:200]})
+    finally:
+        ex.close()
 
 
 def _lm_head(L, lib, dev, s, timed, record, randn, nreps):
