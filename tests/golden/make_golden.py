@@ -1,7 +1,7 @@
 """Generate the golden fixtures under tests/golden/ from the reference tree.
 
-Run where the reference checkout is present (default /root/reference; override with
-REFERENCE=...):   python tests/golden/make_golden.py
+Run where the reference checkout is present (REFERENCE=<its path>, see the default below):
+    python tests/golden/make_golden.py
 
 Writes
   layer0.npz            input/output activation pairs of every in-scope op of Qwen3-0.6B
