@@ -35,9 +35,9 @@ METRIC = "fused_add_rmsnorm_hbm_gbs"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu
-# capture summarised in profiles/ (None until a capture of this build exists).
-HEADLINE_TRAFFIC_BYTES = 1950959616  # 4 x (268.457 + 219.283) MB: profiles/add_rms_norm_f16_65536x4096.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from an ncu capture
+# at 16384 rows scaled to 65536 (None until a capture of this build exists).
+HEADLINE_TRAFFIC_BYTES = 1950959616  # 4 x (268.457 + 219.283) MB
 
 
 def algorithmic_bytes(rows: int, hidden: int, elem: int = 2) -> int:
@@ -471,7 +471,7 @@ def main():
 
         op_table = None
         if not args.no_ops:
-            from cuda_llm_b200 import opbench
+            import opbench
             torch.cuda.empty_cache()
             op_table = opbench.run(L, lib, dev, stream, world, rank, barrier, max_over_ranks)
         ref_gpu = None

@@ -17,7 +17,7 @@ __all__ = ["workloads", "lib", "ops", "sharded", "hostio", "build"]
 def __getattr__(name):
     # torch- and ctypes-backed modules load on first use so that `import cuda_llm_b200`
     # stays cheap; they raise if the CUDA library has not been built.
-    if name in ("lib", "ops", "sharded", "hostio", "opbench", "build"):
+    if name in ("lib", "ops", "sharded", "hostio", "build"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)

@@ -36,20 +36,38 @@ def sources():
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Build lib/libb2ops.so when it is missing or older than a source; returns its path."""
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
+    """Build lib/libb2ops.so when it is missing or older than a source; returns its path.
+    Every .cu file becomes an object of its own (compiled in parallel, and only when it or a header is newer
+    than the object), then the objects are linked."""
+    import concurrent.futures as cf
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
         [os.path.join(ROOT, "include", "b2ops.h")]
-    if not force and _newer(LIB, deps):
+    if not force and _newer(LIB, sources() + headers):
         return LIB
-    os.makedirs(LIB_DIR, exist_ok=True)
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-        ["-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB] + sources()
-    proc = subprocess.run(cmd, capture_output=True, text=True)
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src):
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        if not force and _newer(obj, [src] + headers):
+            return obj, ""
+        cmd = [nvcc] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + \
+            ["-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed on " + src + ":\n" + proc.stdout + proc.stderr)
+        return obj, proc.stderr
+
+    with cf.ThreadPoolExecutor(max(1, min(8, os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, sources()))
     if verbose:
-        sys.stderr.write(proc.stderr)
+        for _, log in results:
+            sys.stderr.write(log)
+    proc = subprocess.run([nvcc, "-shared", "-o", LIB] + [obj for obj, _ in results], capture_output=True, text=True)
     if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        raise RuntimeError("nvcc (link) failed:\n" + proc.stdout + proc.stderr)
     return LIB
 
 

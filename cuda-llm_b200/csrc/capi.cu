@@ -387,6 +387,11 @@ int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_
   }
   B2_REQUIRE(top_k >= 0 && int64_t(top_k) <= width, op, "top_k must be in [0, width]");
   B2_REQUIRE(std::isfinite(top_p) && top_p > 0.0f && top_p <= 1.0f, op, "top_p must be finite in (0, 1]");
+  if (rows > B2_SAMPLER_MAX_ROWS) {   // the row index is the grid's second dimension
+    set_error("%s: %lld rows exceed the %d rows of one call (temperature > 0); split the batch", op,
+              static_cast<long long>(rows), B2_SAMPLER_MAX_ROWS);
+    return B2_ERR_TOO_LARGE;
+  }
   return launch_sample_rows(logits, rows, width, row_stride, dtype, temperature, top_k, top_p, seed,
                             reinterpret_cast<const unsigned long long*>(draw_offsets), out_ids, workspace, as_stream(stream));
 }

@@ -47,6 +47,11 @@ void check(int status) {
 // kernel), softmax row statistics, one int32 result slot and a positions staging area.  Allocated once
 // and grown on demand with plain cudaMalloc, like the reference's DeviceBuffer (src/ops_cuda.cu:565):
 // not part of the Tensor allocation counters.
+// A first or growing call frees, allocates, clears and then waits for the whole device: the clear runs on
+// the thread's default stream, which a caller's non-blocking stream is not ordered after, so the kernel
+// that follows on that stream must not start before it has landed.  Such a call is therefore illegal
+// inside a stream capture (warm the operator up first).  One scratch per (thread, device, purpose): two
+// streams driven by ONE thread share the argmax keys and tickets, so their calls must not overlap.
 struct Scratch {
   void* ptr = nullptr;
   size_t bytes = 0;
@@ -57,7 +62,10 @@ struct Scratch {
       const size_t grown = need < 4096 ? 4096 : need * 2;
       CUDA_CHECK(cudaMalloc(&ptr, grown));
       bytes = grown;
-      if (zero) CUDA_CHECK(cudaMemset(ptr, 0, grown));
+      if (zero) {
+        CUDA_CHECK(cudaMemset(ptr, 0, grown));
+        CUDA_CHECK(cudaDeviceSynchronize());
+      }
     }
     return ptr;
   }

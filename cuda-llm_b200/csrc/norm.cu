@@ -9,7 +9,6 @@
 #include "kernels.h"
 #include "b2ops.h"
 
-#include <cstdlib>
 
 namespace b2 {
 namespace {
@@ -189,20 +188,13 @@ rms_norm_ordered_kernel(const T* x, const T* rhs, const T* __restrict__ w, T* re
 // dispatch
 // ---------------------------------------------------------------------------
 
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return v && *v ? std::atoi(v) : fallback;
-}
-
 // Vectors per thread: 1 while the whole problem is smaller than a few waves of
 // threads (latency matters, use every thread), otherwise `big` to raise the bytes
 // in flight per thread; always large enough that a row fits 256 threads.
 int pick_vpt(int64_t rows, int vecs_per_row, int big) {
-  static const int forced = env_int("B2_NORM_VPT", 0);  // tuning aid; 0 = automatic
   int vpt = 1;
   const int64_t threads_at_1 = rows * int64_t(vecs_per_row);
   if (threads_at_1 >= int64_t(sm_count()) * 2048 * 2) vpt = big;
-  if (forced > 0) vpt = forced;
   while (vpt > 1 && vecs_per_row < vpt) vpt >>= 1;          // never more vectors than the row has
   while (vpt < kMaxVpt && vecs_per_row > kRowThreads * vpt) vpt <<= 1;
   return vpt;

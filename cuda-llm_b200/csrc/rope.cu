@@ -13,7 +13,6 @@
 #include "b2ops.h"
 
 #include <cmath>
-#include <cstdlib>
 
 namespace b2 {
 namespace {
@@ -514,8 +513,6 @@ template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
 template <typename T, bool kNorm>
 bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv, int hv_shift,
                  int64_t pos_period, float eps, float theta, cudaStream_t s, const PagedTarget* paged = nullptr) {
-  static const bool enabled = [] { const char* v = std::getenv("B2_ROPE_BULK"); return !v || std::atoi(v) != 0; }();
-  if (!enabled) return false;
   constexpr int stages = 2, max_warps = kBulkWarps;   // deeper prefetch and other warp counts measured no faster
   const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = stages * stage + 2 * size_t(head_dim) * 4;
   const size_t bar_bytes = size_t(kBulkMaxStages) * 8;

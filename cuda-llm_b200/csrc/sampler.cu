@@ -621,10 +621,12 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     // logits / temperature stays a normal number near the threshold only for a moderate temperature (and a
     // moderate logit there, which the splitter kernel checks)
     const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
-    static const bool finish_ready = [] {
-      return cudaFuncSetAttribute(topk_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) == cudaSuccess;
-    }();
-    if (!finish_ready) { cudaGetLastError(); set_error("sample_rows: cannot reserve shared memory"); return B2_ERR_CUDA; }
+    // the opt-in is a per-device attribute: set on every call, as the other kernels with large shared memory do
+    if (cudaFuncSetAttribute(topk_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) != cudaSuccess) {
+      cudaGetLastError();
+      set_error("sample_rows: cannot reserve shared memory");
+      return B2_ERR_CUDA;
+    }
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
       topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow);

@@ -24,7 +24,6 @@
 #include <cfloat>
 #include <climits>
 #include <cooperative_groups.h>
-#include <cstdlib>
 #include <mutex>
 
 namespace cg = cooperative_groups;
@@ -1023,8 +1022,7 @@ int launch_softmax_typed(const void* x_, void* out_, int64_t rows, int64_t width
     // status word: the last 16 bytes of the workspace (after the 2*rows floats of the two-pass path)
     int* status = reinterpret_cast<int*>(static_cast<char*>(workspace) + softmax_workspace_bytes(rows) - 16);
     int rc;
-    static const bool reg_path = [] { const char* v = std::getenv("B2_SOFTMAX_REG"); return !v || std::atoi(v) != 0; }();
-    if (vec && reg_path && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, status, s) == B2_OK) return B2_OK;
+    if (vec && width % N == 0 && launch_softmax_reg_any<T>(x, out, rows, width, ranks, slice, status, s) == B2_OK) return B2_OK;
     if (vec && sizeof(T) == 4 && slice % 4 == 0)   // fp32 rows: shared memory holds the input's own bytes -> bulk copy
       rc = launch_softmax_cluster<T, true, true>(x, out, rows, width, ranks, slice, status, s);
     else

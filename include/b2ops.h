@@ -173,7 +173,9 @@ B2_API int b2_argmax_rows(const void* logits, int64_t rows, int64_t width, int64
  *     library, until the process exits.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call outside any stream capture.  No call
- *     uses cudaMalloc, cudaFree or any allocating routine.
+ *     uses cudaMalloc, cudaFree or any allocating routine.  The address is remembered per
+ *     device for the life of the process: do not use this entry point across a
+ *     cudaDeviceReset (or any other teardown of the device's primary context).
  *   - All calls on a device share the one array: the part a call uses is cleared on its
  *     stream first, and two calls whose kernels overlap on the GPU (different streams
  *     without ordering) race on it.  Order them, or use b2_argmax_rows with one workspace each. */
@@ -311,13 +313,15 @@ B2_API int b2_select_last_valid_rows(const void* padded, const int32_t* valid_le
  * prefix whose softmax mass reaches top_p (all when top_p == 1); then one draw u(seed, draw_offsets[r]) in
  * (0,1) picks by cumulative mass.  Sums are fp32 and added in that order, so the token is the reference's
  * bit for bit.  temperature == 0 is the row argmax (top_k, top_p and the draw are ignored).
- * temperature must be finite and >= 0; with temperature > 0: 0 <= top_k <= width and 0 < top_p <= 1.
+ * temperature must be finite and >= 0; with temperature > 0: 0 <= top_k <= width, 0 < top_p <= 1 and at most
+ * B2_SAMPLER_MAX_ROWS rows per call (more: B2_ERR_TOO_LARGE before anything is launched).
  * draw_offsets: device uint64[rows], or NULL for offset 0 on every row.
  * workspace: b2_sampler_workspace_bytes(rows, width) bytes of scratch, no initialisation needed; calls
  * that share it must not overlap on the device.
  * Replaces CudaSampler::sample_row / sample_last_row / sample_last_token_of_batch, kernels sampler_fill and
  * sampler_select and the library sort between them (include/llm/ops_cuda.h:46-74;
  * src/ops_cuda.cu:575-617,886-971), which handle one row per blocking call. */
+#define B2_SAMPLER_MAX_ROWS 65535
 B2_API size_t b2_sampler_workspace_bytes(int64_t rows, int64_t width);
 B2_API int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype,
                           float temperature, int32_t top_k, float top_p, uint64_t seed, const uint64_t* draw_offsets,

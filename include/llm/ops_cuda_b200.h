@@ -24,6 +24,11 @@ class CudaReductionModeGuard {
 CudaReductionMode cuda_reduction_mode();
 
 // ---- additions of this library (no reference counterpart)
+// cuda_argmax_rows_out and cuda_lm_head_argmax_out keep a small device scratch (keys and tickets, 12 bytes per
+// row) per calling thread and device.  The first call of a thread on a device, and any call with more rows than
+// every earlier one, allocates and clears it and waits for the device: make that call before any stream capture.
+// The scratch is shared by every stream the thread drives, so one thread's calls on different streams must not
+// overlap on the GPU; different threads never share it.
 // Row-wise argmax of [R,V] logits into a CUDA/I32 [R] tensor, on `stream`, with no host round trip.
 // (The reference reaches rows other than the last only through CudaSampler::sample_row, one blocking
 // call per row, src/ops_cuda.cu:961-971.)

@@ -1,4 +1,4 @@
-"""Per-operator throughput table of the benchmark configurations (used by bench.py).
+"""Per-operator throughput table of the benchmark configurations (used by bench.py; also runs alone).
 
 Every entry is timed with CUDA events on the launching stream after warm-up, over
 `reps` back-to-back launches.  Working sets smaller than a few times L2 are rotated
@@ -14,8 +14,11 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 VOCAB = 151936
 NOMINAL = 8000.0
@@ -23,7 +26,7 @@ NOMINAL = 8000.0
 
 def _peak():
     try:
-        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        root = os.path.dirname(os.path.abspath(__file__))
         return float(json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))["hbm_gbs"])
     except Exception:
         return 6650.0
@@ -32,7 +35,7 @@ def _peak():
 def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, only=None, reps_scale=1.0):
     """only: substring selecting one group of entries ("add_rms_norm", "headline_shape", "qk_norm_rope",
     "swiglu", "gather", "argmax", "softmax", "sampler", "kvmove", "lm_head"); reps_scale shortens the runs for profiler captures."""
-    from . import sharded
+    from cuda_llm_b200 import sharded
 
     def want(group):
         return only is None or only in group
@@ -295,14 +298,17 @@ def _config3(L, lib, dev, s, timed, record, randn, sets_for, nreps):
     F16, FAST, half = lib.F16, lib.FAST, torch.float16
     # ---- configuration 3: packed-prefill QK-norm + RoPE, T = 16384, 16 + 8 heads of 128
     T, HQ, HK, D = 16384, 16, 8, 128
-    lens = torch.randint(1, 513, (64,))
-    pos = torch.cat([torch.arange(int(n)) for n in lens])[:T]
-    pos = torch.cat([pos, torch.arange(T - pos.numel())]).to(torch.int32).to(dev)
-    gq, gk = (torch.rand(D, device=dev) + 0.5).half(), (torch.rand(D, device=dev) + 0.5).half()
+    # the seeded draw of the configuration (positions: 64 concatenated ramps; q, k ~N(0,1); gammas ~U(0.5,1.5));
+    # the further buffer sets that rotate the working set past L2 are fresh normal draws of the same shapes
+    from cuda_llm_b200 import workloads
+    c3 = workloads.config3()
+    pos = torch.from_numpy(c3["positions"]).to(dev)
+    gq, gk = torch.from_numpy(c3["gamma_q"]).to(dev), torch.from_numpy(c3["gamma_k"]).to(dev)
     per_set = 2 * T * (HQ + HK) * D * 2
     n = sets_for(per_set)
-    bufs = [(randn(T, HQ, D), randn(T, HK, D), torch.empty(T, HQ, D, device=dev, dtype=half),
-             torch.empty(T, HK, D, device=dev, dtype=half)) for _ in range(n)]
+    bufs = [(torch.from_numpy(c3["q"]).to(dev) if i == 0 else randn(T, HQ, D),
+             torch.from_numpy(c3["k"]).to(dev) if i == 0 else randn(T, HK, D),
+             torch.empty(T, HQ, D, device=dev, dtype=half), torch.empty(T, HK, D, device=dev, dtype=half)) for i in range(n)]
     calls = [(lambda b=b: lib.check(L.b2_qk_norm_rope(b[0].data_ptr(), b[1].data_ptr(), gq.data_ptr(), gk.data_ptr(),
                                                        pos.data_ptr(), b[2].data_ptr(), b[3].data_ptr(), T, HQ, HK, D,
                                                        1e-6, 1e6, F16, s))) for b in bufs]
@@ -347,7 +353,7 @@ def _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, n
 
 
 def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table):
-    from . import ops
+    from cuda_llm_b200 import ops
     F16, F32, FAST = lib.F16, lib.F32, lib.FAST
     # ---- configuration 5: LM-head reductions over [256, V], V split over the ranks
     R = 256
@@ -452,9 +458,9 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
 
 
 def main():
-    """python -m cuda_llm_b200.opbench [--only GROUP] [--reps-scale X]: the single-GPU table, one line per entry."""
+    """python opbench.py [--only GROUP] [--reps-scale X]: the single-GPU table, one line per entry."""
     import argparse
-    from . import build, lib
+    from cuda_llm_b200 import build, lib
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--reps-scale", type=float, default=1.0)

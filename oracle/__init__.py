@@ -24,10 +24,19 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 F32, F16 = 0, 1  # dtype codes, the same as the product's C ABI
 
 
+def reference_tree():
+    """Root of the reference's source tree, or None: $REFERENCE when set, else a directory named
+    ``reference`` beside this repository."""
+    path = os.environ.get("REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return path if os.path.isfile(os.path.join(path, "src", "ops_cpu.cpp")) else None
+
+
 def build(ref: bool = True) -> None:
-    """Compile oracle.c (and the reference-backed library when its sources exist)."""
-    subprocess.run(["make", "-C", _HERE, "all"] + (["ref", "refcuda", "layer"] if ref else []), check=True,
-                   stdout=subprocess.DEVNULL)
+    """Compile oracle.c and, when ``ref`` is set and the reference's source tree is found (reference_tree()),
+    the reference-backed libraries under _ref/.  Prebuilt files under _ref/ are kept otherwise."""
+    tree = reference_tree() if ref else None
+    targets = ["all"] + (["ref", "refcuda", "layer", "REFERENCE=" + tree] if tree else [])
+    subprocess.run(["make", "-C", _HERE] + targets, check=True, stdout=subprocess.DEVNULL)
 
 
 def _ptr(a: np.ndarray):

@@ -203,7 +203,11 @@ ORC_API void orc_f64_softmax(const float* x, int64_t rows, int64_t width, double
  * (src/ops_cuda.cu:562-563): start from (best = -FLT_MAX, id = 0), replace on
  * value > best or (value == best and index < id).  Scanning in ascending index
  * order makes the second clause unreachable, so: first element strictly greater
- * than everything before it; NaN, -inf and -FLT_MAX never win; nothing wins -> 0. */
+ * than everything before it; NaN, -inf and -FLT_MAX never win; nothing wins -> 0.
+ * The source writes the start value as -CUDART_INF_F.  None of the headers that file includes defines that macro
+ * (checked by preprocessing its include list with CUDA 12.9), so the file's own fallback applies: 3.402823466e+38F
+ * (src/ops_cuda.cu:21-23), i.e. FLT_MAX, not infinity.  tests/test_gpu_reference_cuda.py asks the reference's
+ * compiled kernel about rows that tell the two readings apart. */
 ORC_API int32_t orc_argmax_row_f32(const float* x, int64_t width) {
   float best = -FLT_MAX;
   int32_t best_id = 0;

@@ -36,7 +36,7 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def port():
     import oracle
-    oracle.build(ref=os.path.isdir("/root/reference"))
+    oracle.build()
     return oracle.port()
 
 

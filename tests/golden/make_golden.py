@@ -1,6 +1,6 @@
 """Generate the golden fixtures under tests/golden/ from the reference tree.
 
-Run where the reference checkout is present (REFERENCE=<its path>, see the default below):
+Run where the reference checkout is present (REFERENCE=<its path>, or a directory "reference" beside this repository):
     python tests/golden/make_golden.py
 
 Writes
@@ -24,9 +24,11 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REFERENCE = os.environ.get("REFERENCE", "/root/reference")
-
 import oracle  # noqa: E402
+
+REFERENCE = oracle.reference_tree()   # $REFERENCE, else a directory named "reference" beside this repository
+if REFERENCE is None:
+    raise SystemExit("make_golden.py: set REFERENCE to the root of the reference's source tree")
 from cuda_llm_b200 import workloads as wl  # noqa: E402
 
 

@@ -79,6 +79,22 @@ def test_gather_and_argmax_equal_reference_kernels(refcu, dtype):
     assert ops.argmax_rows(logits).tolist() == each
 
 
+def test_argmax_lowest_finite_value_against_the_reference_kernel(refcu, port):
+    """What the reference's fold starts from decides rows whose only candidates are -inf and -FLT_MAX.  Its
+    source starts at -CUDART_INF_F, and with the headers that file includes that macro is the file's own
+    fallback, 3.402823466e+38F (src/ops_cuda.cu:21-23): -FLT_MAX is the start value and never wins, so such a
+    row gives index 0.  The reference's compiled kernel on this GPU is the judge of that reading."""
+    f = np.float32
+    lowest = np.finfo(f).min
+    cases = [[-np.inf, lowest, -np.inf], [lowest, lowest, lowest], [-np.inf, lowest, np.nextafter(lowest, f(0))],
+             [np.nan, -np.inf, lowest, np.nan]]
+    for row in cases:
+        x = dev(np.asarray([row], f))
+        want = refcu.argmax_last_row(x, 1, len(row), code(x))
+        assert ops.cuda_argmax_last_row(x) == want, row
+        assert int(port.argmax_rows(np.asarray([row], f))[0]) == want, row
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
 def test_deterministic_swiglu_rope_softmax_track_reference_kernels(refcu, dtype):
     rng = np.random.default_rng(21)

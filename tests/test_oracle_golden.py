@@ -117,6 +117,8 @@ def test_argmax_known_cases(port):
     tie[0, 11], tie[0, 12345], tie[0, wl.VOCAB - 1] = 100, 101, 101
     assert int(port.argmax_rows(f16_bits(tie))[0]) == 12345   # f16 tie at 12345 vs 151935
     assert am([[np.nan, -np.inf, -3.4028235e38]]) == 0          # nothing can win -> 0
+    assert am([[-np.inf, -3.4028235e38, -np.inf]]) == 0          # -FLT_MAX is the fold's start value: it never wins
+    assert am([[-np.inf, -3.4028235e38, -3.4028233e38]]) == 2    # the next float above it does
     assert am([[np.nan, 1, np.nan, 1]]) == 1
 
 

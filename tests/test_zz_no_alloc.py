@@ -53,6 +53,19 @@ def test_static_scratch_argmax_matches_workspace_argmax_twice(b2, port):
         assert np.array_equal(got.cpu().numpy(), oracle_ids)
 
 
+def test_static_scratch_at_its_row_limit_and_with_split_rows(b2):
+    """The full 4096 rows (one thread block per row, the scratch untouched by the kernel) and the largest row
+    count whose rows are still split over several thread blocks, which then meet in the scratch's keys and tickets."""
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(100)
+    for rows, width in ((4096, 6000), (592, 8192), (4096, 257)):
+        x = torch.from_numpy(np.round(wl.normal(rng, (rows, width), 4.0) * 4) / 4).to(DEV)
+        for _ in range(2):
+            got = _static_ids(b2, x, stream)
+            torch.cuda.synchronize()
+            assert torch.equal(got, _reference_ids(b2, x, stream))
+
+
 def test_static_scratch_capacity_is_enforced(b2):
     x = torch.zeros(lib.load().b2_argmax_workspace_bytes(1), device=DEV)   # any valid pointer: never read
     out = torch.empty(1, dtype=torch.int32, device=DEV)
