@@ -325,6 +325,75 @@ def reference_gpu_kernels(L, lib, dev, stream):
     return out
 
 
+def sharded_parity(dev, world, rank, calls=3):
+    """Result check of every vocabulary-sharded form on the seeded configuration 5 (planted maxima), run by
+    bench.py with N > 1 ranks outside all timed regions: ids bit-exact against the CPU oracle's argmax, this
+    rank's columns of the softmax against the oracle's exact (fp64) softmax and its fp32 CPU operator under the
+    rule of the GPU tests, over `calls` consecutive calls (both parities of the exchange buffers).  The oracle is
+    only the checker here.  Returns {form: "ok" | "<what differed>"}, identical on every rank."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from cuda_llm_b200 import sharded, workloads as wl
+    port = oracle.port()
+    rows = 256
+    c5 = wl.config5(rows=rows)
+    x = c5["logits"]
+    want_ids = port.argmax_rows(x)
+    assert np.array_equal(want_ids, c5["planted"])
+    lo, hi = sharded.column_range(wl.VOCAB, world, rank)
+    exact = port.softmax_f64(x)
+    floor = exact.max(axis=-1, keepdims=True)
+    cpu = port.softmax(x).astype(np.float64)
+    drift = float((np.abs(cpu - exact) / np.maximum(exact, floor)).max())
+    exact, cpu = exact[:, lo:hi], cpu[:, lo:hi]
+    shard = torch.from_numpy(np.ascontiguousarray(x[:, lo:hi])).to(dev)
+    lm = wl.lm_head_case(4, 1024, wl.VOCAB, seed=6800, dtype=np.float16)
+    planted = np.array([11, wl.VOCAB // 2 - 1, wl.VOCAB // 2, wl.VOCAB - 1], np.int32)
+    for r in range(4):
+        lm["table"][planted[r]] = (lm["hidden"][r].astype(np.float32) * np.float32(0.02)).astype(np.float16)
+    hidden = torch.from_numpy(lm["hidden"]).to(dev)
+    table_shard = torch.from_numpy(np.ascontiguousarray(lm["table"][lo:hi])).to(dev)
+    del lm
+    result = {}
+
+    def ids_check(name, fn, want):
+        bad = ""
+        for call in range(calls):
+            got = fn().cpu().numpy()
+            if not np.array_equal(got, want):
+                bad = bad or f"rank {rank} call {call}: {int((got != want).sum())} of {want.size} ids differ"
+        result[name] = bad
+
+    def softmax_check(name, fn):
+        bad = ""
+        for call in range(calls):
+            got = fn().cpu().numpy().astype(np.float64)
+            e_exact = float((np.abs(got - exact) / np.maximum(exact, floor)).max())
+            e_cpu = float((np.abs(got - cpu) / np.maximum(exact, floor)).max())
+            if not (e_exact <= 1e-5 and e_cpu <= 1e-5 + drift):
+                bad = bad or f"rank {rank} call {call}: {e_exact:.2e} vs exact, {e_cpu:.2e} vs ops_cpu (its drift {drift:.2e})"
+        result[name] = bad
+
+    ex = sharded.PeerExchange(max_rows=rows)
+    try:
+        ids_check("argmax_nccl", lambda: sharded.sharded_argmax(shard, lo), want_ids)
+        ids_check("argmax_fused", lambda: sharded.sharded_argmax_fused(shard, lo, ex), want_ids)
+        softmax_check("softmax_nccl", lambda: sharded.sharded_softmax(shard))
+        softmax_check("softmax_fused", lambda: sharded.sharded_softmax_fused(shard, ex))
+        ids_check("lm_head_nccl", lambda: sharded.sharded_lm_head_argmax(hidden, table_shard, lo), planted)
+        ids_check("lm_head_fused", lambda: sharded.sharded_lm_head_argmax_fused(hidden, table_shard, lo, ex), planted)
+        if ex.timed_out():
+            result["argmax_fused"] = result["argmax_fused"] or f"rank {rank}: a bounded wait for a peer ran out"
+    finally:
+        ex.close()
+    # every rank reports the same verdict: the first complaint of any rank, or "ok"
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    return {k: next((g[k] for g in gathered if g[k]), "ok") for k in result}
+
+
 _REAL_STDOUT = None
 
 
@@ -467,13 +536,29 @@ def main():
         clocks = sampler.stop()
         e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
         e2e_value = world * alg / (e2e_ms * 1e-3) / 1e9
+        # the ceiling of that number on this box with this many ranks: the same pinned copies, no kernel
+        pipe(hx, hr, gamma, h_res, h_nrm, copies_only=True).synchronize()
+        barrier()
+        c0 = torch.cuda.Event(enable_timing=True)
+        c0.record(pipe.s_in)
+        for _ in range(e2e_steps):
+            done = pipe(hx, hr, gamma, h_res, h_nrm, copies_only=True)
+        c1 = torch.cuda.Event(enable_timing=True)
+        pipe.s_out.wait_event(done)
+        c1.record(pipe.s_out)
+        barrier()
+        copy_ms = max_over_ranks(c0.elapsed_time(c1)) / e2e_steps
         del hx, hr, h_res, h_nrm, pipe
 
-        op_table = None
+        op_table, parity_n, sharded_block = None, None, None
+        if world > 1:
+            torch.cuda.empty_cache()
+            parity_n = sharded_parity(dev, world, rank)     # outside every timed region
         if not args.no_ops:
             import opbench
             torch.cuda.empty_cache()
             op_table = opbench.run(L, lib, dev, stream, world, rank, barrier, max_over_ranks)
+            sharded_block = opbench.sharded_summary(op_table, world)
         ref_gpu = None
         if world == 1 and not args.no_ops and not args.no_cpu:
             torch.cuda.empty_cache()
@@ -482,9 +567,12 @@ def main():
             except Exception as exc:      # a reported baseline, never required for our numbers
                 ref_gpu = {"error": str(exc)}
 
+    failed = parity_n is not None and any(v != "ok" for v in parity_n.values())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
+        if failed:
+            raise SystemExit(3)
         return
     peak, peak_kind = measured_peak()
     line = {
@@ -498,7 +586,9 @@ def main():
                      "algorithmic_bytes_per_launch": alg, "kernel": "rms_norm_rows_kernel<__half, 2, true>"},
         "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": 2 * rows * HIDDEN * 2,
                 "d2h_bytes_per_step": 2 * rows * HIDDEN * 2, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
-                "how": "pinned host buffers; 8 row chunks; H2D, kernel and D2H overlapped on three streams"},
+                "how": "pinned host buffers; 8 row chunks; H2D, kernel and D2H overlapped on three streams",
+                "host_copies_only_ms_per_step": round(copy_ms, 3),
+                "frac_of_host_copy_ceiling": round(copy_ms / e2e_ms, 4)},
         "gpu_launches": args.steps, "clocks": clocks,
     }
     if world == 1 and not args.no_cpu:
@@ -515,9 +605,16 @@ def main():
         line["ops"] = op_table
     if ref_gpu is not None:
         line["reference_cuda_kernels_on_this_gpu"] = ref_gpu
+    # last, so that they are what the end of the line shows: the multi-GPU numbers and result checks
+    if sharded_block is not None:
+        line["sharded"] = sharded_block
+    if parity_n is not None:
+        line["parity_n"] = parity_n
     emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("bench.py: a multi-GPU result differs from the CPU oracle: " + json.dumps(parity_n))
 
 
 if __name__ == "__main__":

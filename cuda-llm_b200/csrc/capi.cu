@@ -454,6 +454,7 @@ static int exchange_checks(const char* op, const b2_p2p_exchange* x, int64_t row
   out->max_rows = x->max_rows;
   out->timeout_ns = static_cast<unsigned long long>(x->timeout_ms ? x->timeout_ms : 2000u) * 1000000ull;
   out->status = status;
+  out->trace = reinterpret_cast<unsigned long long*>(x->trace);
   return B2_OK;
 }
 

@@ -125,9 +125,15 @@ argmax_rows_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t c
   if (out_ids != nullptr) out_ids[row] = key == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(key & 0xffffffffull));
 }
 
-// Vocabulary-sharded form with the exchange fused into the kernel's tail: the same fold of this
-// GPU's columns to one key per row, then the CTA that finishes the last row pushes the keys to
-// every peer, waits (bounded) for theirs and writes the global winners' indices.
+// Vocabulary-sharded form with the exchange fused into the kernel: the same fold of this GPU's columns to
+// one key per row; the thread block that finishes a row sends its key to every peer at once (the stores
+// cross NVLink while the other rows are still being read), and the thread block that finishes the last
+// row waits (bounded) for the peers' keys and writes the global winners' indices.
+__device__ __forceinline__ int32_t winner_index(unsigned long long best) {   // 0 = no shard saw a candidate: index 0, like the reference
+  return best == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(best & 0xffffffffull));
+}
+constexpr int32_t kInvalidIndex = -1;   // written for rows whose exchange did not complete in time
+
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kArgThreads)
 argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_t row_stride, int64_t chunk, int chunks,
@@ -135,7 +141,10 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
                             const __grid_constant__ ExchangeArgs xa) {
   __shared__ float warp_v[kArgThreads / kWarpSize];
   __shared__ int warp_i[kArgThreads / kWarpSize];
-  __shared__ int run_tail;
+  __shared__ unsigned long long row_key;
+  __shared__ uint32_t call_epoch;   // read by thread 0 BEFORE it takes the row's ticket: the last row's tail rewrites the stored epoch
+  __shared__ int state;   // 0: this row is not finished yet, 1: finished (send its key), 2: and it was the last row
+  exchange_trace_start(xa);
   const int64_t row = blockIdx.x / chunks;
   const int c = int(blockIdx.x - row * chunks);
   const int64_t lo = int64_t(c) * chunk;
@@ -170,33 +179,43 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
         tickets[row] = 0u;
       }
     }
-    int tail = 0;
+    int st = 0;
     if (row_finished) {
-      exchange_own_slot(xa)[row] = key;
-      tail = exchange_row_done(xa, rows) ? 1 : 0;
+      const uint32_t epoch = exchange_call_epoch(xa);
+      row_key = key;
+      call_epoch = epoch;
+      exchange_send(xa, epoch, xa.rank, row, key);
+      st = exchange_row_done(xa, rows) ? 2 : 1;
     }
-    run_tail = tail;
+    state = st;
   }
   __syncthreads();
-  if (!run_tail) return;
-  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
-    unsigned long long best = 0ull;               // 0 = no shard saw a candidate: index 0, like the reference
+  if (state == 0) return;
+  // threads 1 .. world-1: one peer each
+  if (threadIdx.x > 0 && threadIdx.x < xa.world) exchange_send(xa, call_epoch, (xa.rank + threadIdx.x) % xa.world, row, row_key);
+  if (state != 2) return;
+  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
+    unsigned long long best = 0ull;
     for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
-    out_ids[r] = best == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(best & 0xffffffffull));
+    out_ids[r] = complete ? winner_index(best) : kInvalidIndex;
   });
 }
 
 // The exchange alone, for keys that another kernel produced (the vocabulary-parallel LM head): one thread block
-// copies this GPU's keys into its exchange slot and runs the same tail as above.
+// sends this GPU's keys to every GPU's exchange buffer and runs the same wait-and-combine as above.
 __global__ void __launch_bounds__(kArgThreads)
 argmax_keys_exchange_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids, const __grid_constant__ ExchangeArgs xa) {
-  unsigned long long* own = exchange_own_slot(xa);
-  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) own[r] = static_cast<unsigned long long>(keys[r]) ^ kSignBit;
-  __syncthreads();
-  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
+  exchange_trace_start(xa);
+  const uint32_t epoch = exchange_call_epoch(xa);
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    const unsigned long long key = static_cast<unsigned long long>(keys[r]) ^ kSignBit;
+    for (int g = 0; g < xa.world; ++g) exchange_send(xa, epoch, (xa.rank + g) % xa.world, r, key);
+  }
+  __syncthreads();   // nobody rewrites the stored epoch (end of the tail) before every thread has read it
+  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
     unsigned long long best = 0ull;
     for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
-    out_ids[r] = best == 0ull ? 0 : int32_t(0xffffffffu - uint32_t(best & 0xffffffffull));
+    out_ids[r] = complete ? winner_index(best) : kInvalidIndex;
   });
 }
 
@@ -661,9 +680,10 @@ softmax_stats_kernel(const T* x, int64_t width, float* row_max, float* row_sum) 
   if (threadIdx.x == 0) { row_max[row] = big; row_sum[row] = s; }
 }
 
-// Vocabulary-sharded row statistics with the exchange fused into the tail: (max, sum) of this GPU's
-// columns per row, pushed to every peer; the CTA that finishes the last row waits (bounded) for the
-// peers' pairs and writes the statistics of the WHOLE row, ready for softmax_apply_kernel.
+// Vocabulary-sharded row statistics with the exchange fused into the kernel: (max, sum) of this GPU's
+// columns per row, sent to every peer as soon as the row is done; the thread block that finishes the last
+// row waits (bounded) for the peers' pairs and writes the statistics of the WHOLE row, ready for
+// softmax_apply_kernel.
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kSoftThreads)
 softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* global_max, float* global_sum,
@@ -671,6 +691,8 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
   constexpr int N = Elem<T>::kPerVec;
   __shared__ float scratch[32];
   __shared__ int run_tail;
+  __shared__ uint32_t call_epoch;
+  exchange_trace_start(xa);
   const int64_t row = blockIdx.x;
   const T* src = x + row * width;
   const int64_t step = blockDim.x;
@@ -698,13 +720,19 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
   const float big = block_max(m, scratch);
   s = m2 == -INFINITY ? 0.0f : s * fast_exp2(m2 - big * kLog2e);
   s = block_sum(s, scratch);
+  // every thread holds the row's (max, sum): thread 0 stores this GPU's own slot and takes the ticket, threads
+  // 1 .. world-1 send the pair to one peer each
+  const unsigned long long pair = (static_cast<unsigned long long>(__float_as_uint(s)) << 32) | __float_as_uint(big);
   if (threadIdx.x == 0) {
-    exchange_own_slot(xa)[row] = (static_cast<unsigned long long>(__float_as_uint(s)) << 32) | __float_as_uint(big);
+    const uint32_t epoch = exchange_call_epoch(xa);   // before the ticket: the last row's tail rewrites the stored epoch
+    call_epoch = epoch;
+    exchange_send(xa, epoch, xa.rank, row, pair);
     run_tail = exchange_row_done(xa, rows) ? 1 : 0;
   }
   __syncthreads();
+  if (threadIdx.x > 0 && threadIdx.x < xa.world) exchange_send(xa, call_epoch, (xa.rank + threadIdx.x) % xa.world, row, pair);
   if (!run_tail) return;
-  exchange_tail(xa, rows, [&](int64_t r, auto partial_of) {
+  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
     float top = -INFINITY;
     for (int g = 0; g < xa.world; ++g) top = fmaxf(top, __uint_as_float(uint32_t(partial_of(g))));
     const float top2 = top * kLog2e;
@@ -714,8 +742,9 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
       const float pm = __uint_as_float(uint32_t(p)), ps = __uint_as_float(uint32_t(p >> 32));
       if (pm != -INFINITY) total += ps * fast_exp2(fmaf(pm, kLog2e, -top2));
     }
-    global_max[r] = top;
-    global_sum[r] = total;
+    const float invalid = __int_as_float(0x7fc00000);   // a row whose exchange did not complete in time: NaN statistics
+    global_max[r] = complete ? top : invalid;
+    global_sum[r] = complete ? total : invalid;
   });
 }
 

@@ -26,9 +26,11 @@ class AddRmsNormHostPipeline:
         self.code = _lib.F16 if dtype == torch.float16 else _lib.F32
         self.L = _lib.load()
 
-    def __call__(self, hx, hr, gamma, h_res, h_nrm, eps=1e-6, mode=_lib.FAST):
+    def __call__(self, hx, hr, gamma, h_res, h_nrm, eps=1e-6, mode=_lib.FAST, copies_only=False):
         """hx, hr, h_res, h_nrm: pinned host tensors [rows, hidden]; gamma: device tensor [hidden].
-        Returns the event that marks the last device->host copy; nothing blocks the host."""
+        Returns the event that marks the last device->host copy; nothing blocks the host.
+        copies_only: the same copies in the same order without the kernel between them (what the host's
+        PCIe and memory path alone allow: the ceiling of the end-to-end number)."""
         last = None
         for c, (lo, hi) in enumerate(self.bounds):
             with torch.cuda.stream(self.s_in):
@@ -41,9 +43,10 @@ class AddRmsNormHostPipeline:
                 if self.done_out[c] is not None:      # the previous call's results of this chunk have left the device
                     self.s_k.wait_event(self.done_out[c])
                 n = hi - lo
-                _lib.check(self.L.b2_add_rms_norm(self.x[lo:hi].data_ptr(), self.r[lo:hi].data_ptr(), gamma.data_ptr(),
-                                                  self.res[lo:hi].data_ptr(), self.nrm[lo:hi].data_ptr(), n, self.hidden,
-                                                  eps, self.code, mode, self.s_k.cuda_stream))
+                if not copies_only:
+                    _lib.check(self.L.b2_add_rms_norm(self.x[lo:hi].data_ptr(), self.r[lo:hi].data_ptr(), gamma.data_ptr(),
+                                                      self.res[lo:hi].data_ptr(), self.nrm[lo:hi].data_ptr(), n,
+                                                      self.hidden, eps, self.code, mode, self.s_k.cuda_stream))
                 computed = torch.cuda.Event()
                 computed.record(self.s_k)
             with torch.cuda.stream(self.s_out):

@@ -41,7 +41,7 @@ P2P_MAX_WORLD = 16
 class P2PExchange(C.Structure):
     """b2_p2p_exchange of include/b2ops.h."""
     _fields_ = [("buffers", C.c_void_p * P2P_MAX_WORLD), ("world", C.c_int32), ("rank", C.c_int32),
-                ("max_rows", C.c_int64), ("timeout_ms", C.c_uint32)]
+                ("max_rows", C.c_int64), ("timeout_ms", C.c_uint32), ("trace", C.c_void_p)]
 
 
 def declared_symbols(header: str = HEADER):

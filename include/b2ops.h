@@ -330,11 +330,14 @@ B2_API int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64
 /* ---- vocabulary-sharded reductions with the exchange fused into the kernel ------ */
 
 /* One process per GPU, all GPUs on one NVLink node.  Instead of reduce kernel -> collective
- * library -> finishing kernel, the reduction kernel's last thread block stores this GPU's
- * per-row partial results straight into every peer's exchange buffer (peer-mapped device
- * memory), publishes them with a release flag, waits -- bounded -- for the peers' flags in
- * its own buffer and finishes the row results there.  One launch per GPU and no host
- * round trip.  No reference counterpart: the reference is single-GPU.
+ * library -> finishing kernel, the reduction kernel does the exchange itself: the thread
+ * block that finishes a row stores that row's 8-byte partial result straight into every
+ * peer's exchange buffer (peer-mapped device memory) while the other rows are still being
+ * reduced -- as two 64-bit words that each carry the call's epoch, so a word that shows the
+ * epoch is valid data and no fence or separate flag crosses NVLink -- and the thread block
+ * that finishes the last row waits -- bounded -- for the peers' words in its own buffer and
+ * writes the final row results.  One launch per GPU and no host round trip.  No reference
+ * counterpart: the reference is single-GPU.
  *
  * Set-up, once per group of GPUs:
  *   1. every process: buffer = b2_alloc(b2_p2p_exchange_bytes(world, max_rows));
@@ -346,8 +349,12 @@ B2_API int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64
  *   4. a host barrier, so that every buffer is initialised before the first call.
  * Every rank must then make the same sequence of fused calls (they are collectives); calls
  * on one buffer must not overlap on a GPU.  timeout_ms bounds the wait for the peers (0 means
- * 2000): when it runs out the kernel still ends normally, ORs 2 into *status, and the results
- * of that call are invalid; every rank then re-initialises its buffer before further use.
+ * 2000): when it runs out the kernel still ends normally, ORs 2 into *status, and the rows
+ * whose partials were incomplete are marked in the output itself (index -1; NaN statistics);
+ * every rank then re-initialises its buffer before further use.
+ * trace: NULL, or device uint64[4 + world] that receives the nanosecond timer of this GPU at the
+ * kernel's start, at the start of the wait, when all partials were present and at the end, then
+ * when each GPU's first row was seen (a measuring aid; costs nothing when NULL).
  * Tear-down: b2_ipc_close(peer_pointer) for each opened handle, then b2_free(buffer). */
 #define B2_P2P_MAX_WORLD 16
 typedef struct {
@@ -355,6 +362,7 @@ typedef struct {
   int32_t world, rank;
   int64_t max_rows;
   uint32_t timeout_ms;
+  uint64_t* trace;
 } b2_p2p_exchange;
 B2_API size_t b2_p2p_exchange_bytes(int world, int64_t max_rows);
 B2_API int b2_p2p_exchange_init(void* buffer, int world, int64_t max_rows, b2_stream stream);

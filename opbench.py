@@ -119,7 +119,7 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
     if want("swiglu") or want("gather"):
         _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, nreps)
     if want("argmax") or want("softmax"):
-        _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table)
+        _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table, barrier)
     if world == 1 and want("copy"):
         # a yardstick measured in the same run with the same harness: plain device-to-device copies (torch's kernel, not
         # ours) of 1 GiB and of the byte counts of the two small configurations
@@ -352,7 +352,64 @@ def _config4(L, lib, dev, s, timed, record, randn, sharded, world, rank, want, n
 
 
 
-def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table):
+def _exchange_phases(lib, sharded, ex, logits, c_lo, ids_out, world, barrier, calls=24):
+    """Medians, over `calls` separate launches that all ranks enter together, of the phases of b2_argmax_rows_sharded
+    on this rank: launch to last local row done, waiting for the peers' keys, combining; and when each peer's first
+    key was seen, relative to the start of the wait."""
+    import ctypes as C
+    import statistics
+    dev = logits[0].device
+    trace = torch.zeros(4 + world, dtype=torch.int64, device=dev)
+    ex.desc.trace = trace.data_ptr()
+    local, wait, combine, total, peers = [], [], [], [], [[] for _ in range(world)]
+    try:
+        for i in range(calls):
+            barrier()
+            sharded.sharded_argmax_fused(logits[i % len(logits)], c_lo, ex, out=ids_out)
+            torch.cuda.synchronize()
+            t = trace.tolist()
+            local.append(t[1] - t[0]); wait.append(t[2] - t[1]); combine.append(t[3] - t[2]); total.append(t[3] - t[0])
+            for g in range(world):
+                peers[g].append(t[4 + g] - t[1])
+    finally:
+        ex.desc.trace = None
+    med = lambda v: round(statistics.median(v) / 1e3, 2)
+    return {"op": "fused exchange, phases of one b2_argmax_rows_sharded call on rank 0 (device timer, medians)",
+            "calls": calls, "us_first_block_to_last_row_done": med(local), "us_waiting_for_peers": med(wait),
+            "us_combine_and_finish": med(combine), "us_kernel_total": med(total),
+            "us_peer_first_key_seen_after_wait_began": [med(p) for p in peers],
+            "note": "ranks enter each call from a host barrier, so the wait includes the launch skew between processes"}
+
+
+def sharded_summary(table, world):
+    """The multi-GPU numbers of the table in one small block: microseconds per call (max over ranks)."""
+    def us(fragment, shape_fragment=""):
+        for e in table:
+            if fragment in e.get("op", "") and shape_fragment in e.get("shape", "") and "us" in e:
+                return e["us"]
+        return None
+    out = {"n_gpus": world, "swiglu_3072_us": us("swiglu", "I=3072"), "swiglu_12288_us": us("swiglu", "I=12288"),
+           "gather_us": us("embedding_gather")}
+    if world == 1:
+        out.update({"argmax_us": us("argmax_rows"), "softmax_us": us("softmax_rows"),
+                    "lm_head_4rows_us": us("lm_head_argmax (ids only)", "4 x 1024 by 151936 x 1024 f16")})
+    else:
+        out.update({"argmax_fused_us": us("argmax (vocab-sharded, exchange fused into the kernel), eager"),
+                    "argmax_fused_graph_us": us("argmax (vocab-sharded, exchange fused into the kernel), CUDA-graph"),
+                    "argmax_nccl_us": us("argmax (vocab-sharded + all-reduce MAX of packed keys), eager"),
+                    "argmax_nccl_graph_us": us("argmax (vocab-sharded + all-reduce MAX of packed keys), CUDA-graph"),
+                    "softmax_fused_us": us("softmax (vocab-sharded, exchange fused into the statistics kernel), eager"),
+                    "softmax_fused_graph_us": us("softmax (vocab-sharded, exchange fused into the statistics kernel), CUDA-graph"),
+                    "softmax_nccl_us": us("softmax (vocab-sharded + all-reduce MAX, SUM), eager"),
+                    "softmax_nccl_graph_us": us("softmax (vocab-sharded + all-reduce MAX, SUM), CUDA-graph"),
+                    "lm_head_fused_us": us("lm_head_argmax (vocab-parallel + keys exchange"),
+                    "lm_head_nccl_us": us("lm_head_argmax (vocab-parallel + all-reduce"),
+                    "argmax_one_gpu_us": us("argmax_rows, whole vocabulary on one GPU"),
+                    "softmax_one_gpu_us": us("softmax_rows, whole vocabulary on one GPU")})
+    return out
+
+
+def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, rank, want, nreps, table, barrier=None):
     from cuda_llm_b200 import ops
     F16, F32, FAST = lib.F16, lib.F32, lib.FAST
     # ---- configuration 5: LM-head reductions over [256, V], V split over the ranks
@@ -376,6 +433,18 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
         ms = timed(calls, nreps(40))
         record("softmax_rows", f"{R}x{VOCAB} f32", 2 * per_set, ms, R)
     else:
+        # the yardstick of the sharded forms, in the same run: the whole vocabulary on one GPU (every rank alike, no exchange)
+        full = [randn(R, VOCAB, sigma=4.0, dtype=torch.float32) for _ in range(4)]
+        full_out = [torch.empty(R, VOCAB, device=dev) for _ in range(2)]
+        ids_full = torch.empty(R, dtype=torch.int32, device=dev)
+        ws_full, sws_full = ops.argmax_workspace(dev, R), ops.softmax_workspace(dev, R)
+        ms = timed([(lambda x=x: lib.check(L.b2_argmax_rows(x.data_ptr(), R, VOCAB, VOCAB, F32, ids_full.data_ptr(),
+                                                             ws_full.data_ptr(), s))) for x in full], nreps(40))
+        record("argmax_rows, whole vocabulary on one GPU (yardstick of the sharded forms)", f"{R}x{VOCAB} f32", R * VOCAB * 4 + 4 * R, ms, R)
+        ms = timed([(lambda x=x, i=i: lib.check(L.b2_softmax_rows(x.data_ptr(), full_out[i % 2].data_ptr(), R, VOCAB, F32, FAST,
+                                                                   sws_full.data_ptr(), s))) for i, x in enumerate(full)], nreps(40))
+        record("softmax_rows, whole vocabulary on one GPU (yardstick of the sharded forms)", f"{R}x{VOCAB} f32", 2 * R * VOCAB * 4, ms, R)
+        del full, full_out
         # eager: every launch and the collective are issued from Python, which dominates at this size
         calls = [(lambda x=x: sharded.sharded_argmax(x, c_lo)) for x in logits]
         ms = timed(calls, nreps(40))
@@ -403,25 +472,32 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
             record("softmax (vocab-sharded, exchange fused into the statistics kernel), eager launches",
                    f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
             table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            # device-side time per call, free of the host's launch pacing: 16 calls over the rotating buffers recorded
+            # into ONE graph and replayed
             stream = torch.cuda.current_stream()
-            graphs_a, graphs_s = [], []
-            for i, x in enumerate(logits):
-                ga = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(ga, stream=stream):
-                    sharded.sharded_argmax_fused(x, c_lo, ex, out=ids_f)
-                graphs_a.append(ga)
-                gs = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gs, stream=stream):
-                    sharded.sharded_softmax_fused(x, ex, out=outs[i % len(outs)], stats=stats_f)
-                graphs_s.append(gs)
-            ms = timed([g.replay for g in graphs_a], nreps(40))
+            K = 16
+            ga = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(ga, stream=stream):
+                for i in range(K):
+                    sharded.sharded_argmax_fused(logits[i % n], c_lo, ex, out=ids_f)
+            ms = timed([ga.replay], nreps(10)) / K
             record("argmax (vocab-sharded, exchange fused into the kernel), CUDA-graph replay", f"{R}x{VOCAB}/{world} f32",
-                   per_set + 4 * R, ms, R, sharded_over=world)
+                   per_set + 4 * R, ms, R, sharded_over=world, note=f"{K} calls per graph")
             table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
-            ms = timed([g.replay for g in graphs_s], nreps(40))
+            gs = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gs, stream=stream):
+                for i in range(K):
+                    sharded.sharded_softmax_fused(logits[i % n], ex, out=outs[i % len(outs)], stats=stats_f)
+            ms = timed([gs.replay], nreps(10)) / K
             record("softmax (vocab-sharded, exchange fused into the statistics kernel), CUDA-graph replay",
-                   f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
+                   f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world, note=f"{K} calls per graph")
             table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            del ga, gs
+            # where the time of one fused argmax call goes on this GPU: the kernel's own stamps of its nanosecond timer
+            try:
+                table.append(_exchange_phases(lib, sharded, ex, logits, c_lo, ids_f, world, barrier))
+            except Exception as exc:
+                table.append({"op": "fused exchange, phases of one call", "error": str(exc)[:200]})
             if ex.timed_out():
                 table.append({"op": "vocab-sharded reductions, fused exchange", "error": "a bounded wait for a peer ran out"})
         except Exception as exc:

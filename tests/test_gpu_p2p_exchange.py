@@ -5,7 +5,7 @@ On one GPU the ranks cannot run side by side (kernels that wait for one another 
 a GPU), so they run ONE AFTER THE OTHER over exchange buffers that all live on this GPU: ranks
 world-1 .. 1 go first with a few milliseconds of patience, push their partials into every buffer,
 find nobody answering and report it through the status word (the bounded wait doing its job);
-rank 0 goes last, finds every peer's flag already published and must produce the global result.
+rank 0 goes last, finds every peer's partials already in its buffer and must produce the global result.
 The real thing, two processes on two GPUs, runs when the box has them."""
 import ctypes as C
 import os
@@ -155,6 +155,7 @@ def test_wait_for_a_silent_peer_runs_out_and_is_reported(b2, port):
                                        C.byref(lw.desc[0]), lw.status[0].data_ptr(), stream()))
     torch.cuda.synchronize()
     assert int(lw.status[0].item()) == 2
+    assert (host(out) == -1).all()                      # and the rows themselves say that they are not results
     assert np.array_equal(host(ops.argmax_rows(t)), port.argmax_rows(x))
     # argument errors
     bad = lib.P2PExchange()
