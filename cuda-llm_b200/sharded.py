@@ -282,3 +282,54 @@ def sharded_softmax_fused(logits_shard: torch.Tensor, exchange: PeerExchange, ou
     _lib.check(L.b2_softmax_apply(logits_shard.data_ptr(), out.data_ptr(), rows, width, code, stats[0].data_ptr(),
                                   stats[1].data_ptr(), _ops._stream()))
     return out
+
+
+# ---------------------------------------------------------------- bound calls
+
+def _bound(fn, args):
+    """fn(*args) as a zero-argument callable, the arguments converted to their C types once."""
+    converted = [t(a) for t, a in zip(fn.argtypes, args)]
+    check = _lib.check
+
+    def call():
+        rc = fn(*converted)
+        if rc:
+            check(rc)
+    call.keepalive = args
+    return call
+
+
+def bind_argmax_fused(logits_shard: torch.Tensor, index_base: int, exchange: PeerExchange, out: torch.Tensor):
+    """sharded_argmax_fused(logits_shard, index_base, exchange, out) as a callable that launches on the stream
+    current NOW with every pointer fixed: for a decode loop that calls the same buffers every step, where the
+    interpreter's per-call work (checks, pointer and stream look-ups) would otherwise cost more than the 10 us
+    kernel.  The tensors must stay alive and in place; `out` receives the ids."""
+    _ops._logits_req(logits_shard, "bind_argmax_fused")
+    rows, width = logits_shard.shape
+    ws = _ops.argmax_workspace(logits_shard.device, rows)
+    import ctypes as C
+    call = _bound(_lib.load().b2_argmax_rows_sharded,
+                  (logits_shard.data_ptr(), rows, width, width, _ops._code(logits_shard), index_base, out.data_ptr(),
+                   ws.data_ptr(), C.addressof(exchange.desc), exchange.status.data_ptr(), _ops._stream()))
+    call.keepalive = (logits_shard, out, ws, exchange)
+    return call
+
+
+def bind_softmax_fused(logits_shard: torch.Tensor, exchange: PeerExchange, out: torch.Tensor, stats: torch.Tensor):
+    """sharded_softmax_fused with every pointer fixed (see bind_argmax_fused): two launches per call."""
+    _ops._logits_req(logits_shard, "bind_softmax_fused")
+    rows, width = logits_shard.shape
+    L = _lib.load()
+    code = _ops._code(logits_shard)
+    import ctypes as C
+    first = _bound(L.b2_softmax_stats_sharded, (logits_shard.data_ptr(), rows, width, code, stats[0].data_ptr(),
+                                               stats[1].data_ptr(), C.addressof(exchange.desc), exchange.status.data_ptr(),
+                                               _ops._stream()))
+    second = _bound(L.b2_softmax_apply, (logits_shard.data_ptr(), out.data_ptr(), rows, width, code, stats[0].data_ptr(),
+                                         stats[1].data_ptr(), _ops._stream()))
+
+    def call():
+        first()
+        second()
+    call.keepalive = (logits_shard, out, stats, exchange)
+    return call

@@ -395,10 +395,12 @@ def sharded_summary(table, world):
                     "lm_head_4rows_us": us("lm_head_argmax (ids only)", "4 x 1024 by 151936 x 1024 f16")})
     else:
         out.update({"argmax_fused_us": us("argmax (vocab-sharded, exchange fused into the kernel), eager"),
+                    "argmax_fused_bound_us": us("argmax (vocab-sharded, exchange fused into the kernel), eager launch through"),
                     "argmax_fused_graph_us": us("argmax (vocab-sharded, exchange fused into the kernel), CUDA-graph"),
                     "argmax_nccl_us": us("argmax (vocab-sharded + all-reduce MAX of packed keys), eager"),
                     "argmax_nccl_graph_us": us("argmax (vocab-sharded + all-reduce MAX of packed keys), CUDA-graph"),
                     "softmax_fused_us": us("softmax (vocab-sharded, exchange fused into the statistics kernel), eager"),
+                    "softmax_fused_bound_us": us("softmax (vocab-sharded, exchange fused into the statistics kernel), eager launches through"),
                     "softmax_fused_graph_us": us("softmax (vocab-sharded, exchange fused into the statistics kernel), CUDA-graph"),
                     "softmax_nccl_us": us("softmax (vocab-sharded + all-reduce MAX, SUM), eager"),
                     "softmax_nccl_graph_us": us("softmax (vocab-sharded + all-reduce MAX, SUM), CUDA-graph"),
@@ -470,6 +472,17 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
                      for i, x in enumerate(logits)]
             ms = timed(calls, nreps(40))
             record("softmax (vocab-sharded, exchange fused into the statistics kernel), eager launches",
+                   f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            # the same launches with the interpreter's per-call work (argument checks, pointer and stream look-ups) done once
+            calls = [sharded.bind_argmax_fused(x, c_lo, ex, ids_f) for x in logits]
+            ms = timed(calls, nreps(40))
+            record("argmax (vocab-sharded, exchange fused into the kernel), eager launch through a bound call",
+                   f"{R}x{VOCAB}/{world} f32", per_set + 4 * R, ms, R, sharded_over=world)
+            table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
+            calls = [sharded.bind_softmax_fused(x, ex, outs[i % len(outs)], stats_f) for i, x in enumerate(logits)]
+            ms = timed(calls, nreps(40))
+            record("softmax (vocab-sharded, exchange fused into the statistics kernel), eager launches through a bound call",
                    f"{R}x{VOCAB}/{world} f32", 2 * per_set, ms, R, sharded_over=world)
             table[-1]["rows_per_s"] = round(R / (ms * 1e-3), 1)
             # device-side time per call, free of the host's launch pacing: 16 calls over the rotating buffers recorded
