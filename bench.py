@@ -298,7 +298,7 @@ def reference_gpu_kernels(L, lib, dev, stream):
     row(f"softmax {R}x{vocab} f32", ref.time_softmax(logits, R, vocab, 0, 1),
         ours(lambda: lib.check(L.b2_softmax_rows(logits.data_ptr(), sout.data_ptr(), R, vocab, lib.F32, lib.FAST, sws.data_ptr(), s))))
     # decode tail: the reference's cuda_lm_head (library GEMM into a fresh logits tensor) + cuda_argmax_last_row
-    for R in (1, 4):
+    for R in (1, 4, 64):
         hid = torch.randn(R, 1024, device=dev).to(half)
         emb = (torch.randn(vocab, 1024, device=dev) * 0.02).to(half)
         lm_ids = torch.empty(R, dtype=torch.int32, device=dev)

@@ -51,6 +51,12 @@ int launch_lm_head_argmax(const void* hidden, const void* table, int64_t rows, i
                           int dtype, int mode, int64_t index_base, void* logits_out, int64_t logits_stride,
                           int32_t* out_ids, int64_t* out_keys, void* workspace, cudaStream_t s);
 
+// lmhead_mma.cu: the same product on the tensor cores (tcgen05), fp16, up to 64 hidden rows per pass over the table
+bool lm_head_mma_supported(const void* hidden, const void* table, int64_t hidden_size, int64_t vocab);
+int launch_lm_head_mma(const void* hidden, const void* table, int64_t rows, int64_t hidden_size, int64_t vocab,
+                       int64_t index_base, void* logits_out, int64_t logits_stride, int32_t* out_ids, int64_t* out_keys,
+                       unsigned long long* keys, unsigned int* ticket, cudaStream_t s);
+
 // kvmove.cu: mode 0 = decode batch (one block table and one position per token), 1 = packed prefill (token t at
 // slot t of one block table), 2 = single decode (*positions is the cache length after the append)
 int launch_paged_kv_write(int mode, const void* key, const void* value, void* storage, const int32_t* block_tables,

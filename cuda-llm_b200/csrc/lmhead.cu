@@ -29,6 +29,7 @@ namespace {
 constexpr int kLmThreads = 256;
 constexpr int kLmWarps = kLmThreads / kWarpSize;
 constexpr int kLmNone = INT_MAX;
+constexpr int64_t kMmaMinRows = 5;   // fp16 batches from this size on go to the tensor-core kernel (lmhead_mma.cu)
 constexpr unsigned long long kLmSignBit = 0x8000000000000000ull;
 
 __device__ __forceinline__ bool lm_beats(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
@@ -586,6 +587,14 @@ int launch_typed(const void* hidden_, const void* table_, int64_t rows, int64_t 
     int32_t* ip = out_ids ? out_ids + r0 : nullptr;
     int64_t* kp = out_keys ? out_keys + r0 : nullptr;
     int rc;
+    if (sizeof(T) == 2 && mode == B2_FAST && left >= kMmaMinRows && lm_head_mma_supported(hp, table, H, vocab)) {
+      // more rows than the matrix-vector kernels take in one pass: tensor cores, up to 64 rows per pass over the table
+      const int64_t take = left < 64 ? left : 64;
+      rc = launch_lm_head_mma(hp, table, take, H, vocab, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s);
+      if (rc != B2_OK) return rc;
+      r0 += take;
+      continue;
+    }
 #define B2_LM_FAST(KV, RR, JJ, AH) \
   rc = launch_fast<T, KV, RR, JJ, AH>(hp, table, vocab, index_base, lp, logits_stride, ip, kp, keys + r0, tickets + r0, s)
 #define B2_LM_SMEM(RR) \

@@ -225,3 +225,88 @@ def test_argument_rules(b2):
     assert b2.b2_lm_head_argmax(h.data_ptr(), t.data_ptr(), 2, 1024, 10, lib.F32, 5, 0, None, 10, ids.data_ptr(), None, None,
                                 torch.cuda.current_stream().cuda_stream) == -1      # unknown mode
 
+
+
+# ---- more rows than the matrix-vector kernels take: the tensor-core kernel (fp16, fast mode) ----------------------
+
+MMA_SHAPES = [(5, 1024, 700), (8, 1024, 128), (16, 1024, 129), (17, 1024, 1000), (32, 1024, 4097), (33, 2048, 300),
+              (64, 1024, 2500), (65, 1024, 513), (100, 1024, 260), (8, 64, 1000), (12, 192, 555), (64, 4096, 384),
+              (16, 1024, 19000)]
+
+
+@pytest.mark.parametrize("rows,hidden,vocab", MMA_SHAPES)
+def test_many_rows_tensor_core_kernel_within_tolerance(b2, port, rows, hidden, vocab):
+    """Same rules as the fast mode above; 65 and 100 rows take two passes over the table."""
+    c = wl.lm_head_case(rows, hidden, vocab, seed=6700 + rows + hidden + vocab, dtype=np.float16)
+    want32, scale = _oracle(port, c["hidden"], c["table"])
+    ids, logits = _run(c["hidden"], c["table"], "fast")
+    bound = RTOL * np.maximum(np.abs(want32.astype(np.float64)), scale) + ulp16(want32)
+    err = np.abs(logits.astype(np.float64) - want32.astype(np.float64))
+    assert (err <= bound).all(), f"worst error / bound = {(err / bound).max():.3f}"
+    assert np.array_equal(ids, _argmax(port, logits))            # the reference's rule on the stored logits
+    for _ in range(2):                                           # scratch left clean; without the logits the same ids
+        ids_only, _ = _run(c["hidden"], c["table"], "fast", with_logits=False)
+        assert np.array_equal(ids_only, ids)
+    want = want32.astype(np.float16).astype(np.float64)
+    want_ids = _argmax(port, want32.astype(np.float16))
+    for r in range(rows):
+        others = np.delete(want[r], want_ids[r])
+        margin = want[r, want_ids[r]] - (others.max() if others.size else -np.inf)
+        if margin > 4 * bound[r].max():
+            assert ids[r] == want_ids[r]
+
+
+@pytest.mark.parametrize("rows", [8, 16, 64])
+def test_many_rows_full_vocabulary_planted_winners(b2, port, rows):
+    """151936 x 1024 fp16, one pass over the table for all rows: planted winners, and the logits of a sample of
+    table rows (among them the first and last tiles) against the CPU operator."""
+    c, planted = _planted(rows, 1024, wl.VOCAB, np.float16, seed=6900 + rows)
+    ids, _ = _run(c["hidden"], c["table"], "fast", with_logits=False)
+    assert np.array_equal(ids, planted)
+    ids, logits = _run(c["hidden"], c["table"], "fast", with_logits=True)
+    assert np.array_equal(ids, planted)
+    rng = np.random.default_rng(rows)
+    sample = np.unique(np.concatenate([np.arange(130), np.arange(wl.VOCAB - 130, wl.VOCAB), rng.integers(0, wl.VOCAB, 700)]))
+    want32, scale = _oracle(port, c["hidden"], c["table"][sample])
+    bound = RTOL * np.maximum(np.abs(want32.astype(np.float64)), scale) + ulp16(want32)
+    err = np.abs(logits[:, sample].astype(np.float64) - want32.astype(np.float64))
+    assert (err <= bound).all(), f"worst error / bound = {(err / bound).max():.3f}"
+    assert np.array_equal(ids, _argmax(port, logits))
+
+
+def test_many_rows_ties_and_special_values(b2, port):
+    """The pick of the tensor-core kernel follows the reference's rule: ties to the lowest index (within a thread's
+    rows, across the threads of a tile and across thread blocks), NaN never wins, a row of nothing comparable gives 0."""
+    rows, vocab = 8, 1000
+    hidden = np.zeros((rows, 1024), np.float16)
+    for r in range(rows):
+        hidden[r, r] = 1.0                               # logits of row r = table[:, r]
+    table = np.zeros((vocab, 1024), np.float16)
+    table[:, 0] = -5.0
+    table[[17, 17 + 128, 900], 0] = 7.0                  # a tie inside one thread (rows 17 and 145), and across tiles
+    table[:, 1] = 2.5                                    # all equal -> 0
+    table[:, 2] = -65504.0                               # fp16's lowest finite value is an ordinary logit -> 0
+    table[999, 4] = 1.0                                  # last row of the last (partial) tile
+    table[300, 7], table[301, 7] = 3.0, 3.0
+    table[:, 5] = -1.0
+    table[[511, 512], 5] = 0.5                           # last thread of one tile, first of the next
+    ids, logits = _run(hidden, table, "fast")
+    assert ids.tolist() == [17, 0, 0, 0, 999, 511, 0, 300]
+    assert np.array_equal(ids, _argmax(port, logits))
+    # values that never win.  (A zero of the hidden row times an infinity or a NaN of the table is a NaN, so these
+    # cases use one column only and every hidden row is a multiple of the first unit vector.)
+    hidden = np.zeros((rows, 1024), np.float16)
+    hidden[:, 0] = [1.0, -1.0, 2.0, 0.5, 1.0, 1.0, 1.0, 1.0]
+    table = np.zeros((vocab, 1024), np.float16)
+    table[:, 0] = np.nan
+    table[640, 0] = -3.0                                 # the only comparable logit of every row
+    ids, logits = _run(hidden, table, "fast")
+    assert (ids == 640).all() and np.isnan(logits[0, 0]) and logits[1, 640] == np.float16(3.0)
+    table[:, 0] = -np.inf                                # -inf never wins -> 0
+    ids, logits = _run(hidden, table, "fast")
+    assert ids.tolist() == [0, 0, 0, 0, 0, 0, 0, 0] and logits[1, 5] == np.inf and logits[0, 5] == -np.inf
+    assert np.array_equal(ids, _argmax(port, logits))
+    hidden[:, 0] = np.float16(65504.0)
+    table[:, 0] = 2.0                                    # overflow to +inf everywhere: all equal -> 0
+    ids, logits = _run(hidden, table, "fast")
+    assert (ids == 0).all() and np.isinf(logits).all()
