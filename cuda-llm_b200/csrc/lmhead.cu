@@ -29,7 +29,7 @@ namespace {
 constexpr int kLmThreads = 256;
 constexpr int kLmWarps = kLmThreads / kWarpSize;
 constexpr int kLmNone = INT_MAX;
-constexpr int64_t kMmaMinRows = 5;   // fp16 batches from this size on go to the tensor-core kernel (lmhead_mma.cu)
+constexpr int64_t kMmaMinRows = 3;   // fp16 batches from this size on go to the tensor-core kernel (lmhead_mma.cu)
 constexpr unsigned long long kLmSignBit = 0x8000000000000000ull;
 
 __device__ __forceinline__ bool lm_beats(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }

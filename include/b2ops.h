@@ -193,12 +193,13 @@ B2_API int b2_argmax_keys(const void* logits, int64_t rows, int64_t width, int64
                           int64_t index_base, int64_t* keys, void* workspace, b2_stream stream);
 B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out_ids, b2_stream stream);
 
-/* Decode-size LM head fused with the greedy pick: logits[r, j] = sum_k hidden[r, k] * table[j, k]
- * and, per row, the arg-max over j, in one pass over the table; the pick never reads the logits
- * back from memory.  Meant for decode batches (1-4 rows, any count accepted): there the product is
- * bound by reading the table once, not by arithmetic, so it runs on the CUDA cores like the other
- * streaming operators (every 4 rows, 2 above hidden size 4096, cost one more pass over the table;
- * prefill-sized row counts belong to a GEMM).
+/* LM head fused with the greedy pick: logits[r, j] = sum_k hidden[r, k] * table[j, k] and, per row, the
+ * arg-max over j, in one pass over the table; the pick never reads the logits back from memory.
+ * Any row count is accepted.  One or two rows (and every fp32 call) are a matrix-vector product, bound by
+ * reading the table once: they run on the CUDA cores like the other streaming operators (fp32: every 4 rows,
+ * 2 above hidden size 4096, cost one more pass over the table).  Three or more fp16 rows in B2_FAST go to the
+ * tensor cores (tcgen05.mma, accumulators in tensor memory, the arg-max in the epilogue): up to 64 rows per
+ * pass over the table, still at the table's read rate.
  * hidden: rows x hidden_size; table: vocab x hidden_size (the tied embedding); same dtype.
  * logits_out: NULL, or rows x vocab of that dtype, consecutive rows `logits_stride` elements apart.
  * out_ids: NULL or int32[rows]; out_keys: NULL or int64[rows] packed as by b2_argmax_keys with
@@ -207,12 +208,15 @@ B2_API int b2_argmax_decode_keys(const int64_t* keys, int64_t rows, int32_t* out
  * The logit is rounded to the storage type before it is compared, and the pick follows
  * b2_argmax_rows' rule.  B2_DETERMINISTIC adds the products in ascending k with separately
  * rounded multiplies (the reference's CPU `linear`, and for fp16 its linear_f16_reference kernel);
- * B2_FAST splits k over a warp in a fixed order.  B2_FAST needs 16-byte aligned pointers and a
- * hidden size that is a multiple of 1024 (fp16) or 512 (fp32) elements; other shapes (hidden_size
- * up to 8192) take the ordered kernel in both modes.
+ * B2_FAST splits k over a warp in a fixed order, or leaves the order to the tensor cores (fp32
+ * accumulation; run-to-run identical).  B2_FAST needs 16-byte aligned pointers and a hidden size that is a
+ * multiple of 1024 (fp16 on the CUDA cores), 512 (fp32) or 64 (fp16 on the tensor cores) elements; other
+ * shapes (hidden_size up to 8192) take the ordered kernel in both modes.
+ * Should a bounded wait inside the tensor-core kernel ever run out (a copy that never lands), every id of the
+ * call reads -1 (keys: INT64_MIN) instead of a result.
  * workspace: as for b2_argmax_rows (b2_argmax_workspace_bytes(rows), zero-filled once).
- * Replaces, for decode, cuda_lm_head / cuda_linear_out followed by cuda_argmax_last_row
- * (include/llm/ops_cuda.h:154,157; src/ops_cuda.cu:885,101-111; src/qwen3_cuda_model.cpp:1070-1071,
+ * Replaces cuda_lm_head / cuda_linear_out followed by cuda_argmax_last_row
+ * (include/llm/ops_cuda.h:154,157; src/ops_cuda.cu:637-671,885,101-111; src/qwen3_cuda_model.cpp:1070-1071,
  * 1339); CPU twin lm_head = linear (include/llm/ops.h:12; src/ops_cpu.cpp:9,17). */
 B2_API int b2_lm_head_argmax(const void* hidden, const void* table, int64_t rows, int64_t hidden_size,
                              int64_t vocab, int dtype, int mode, int64_t index_base, void* logits_out,

@@ -43,7 +43,7 @@ void cuda_qk_norm_rope_out(const Tensor& q, const Tensor& k, const Tensor& q_wei
 // over the tied embedding, the logits never read back; `logits` (optional, [rows, vocab], same dtype) also receives
 // what cuda_lm_head would return.  One launch for the reference's cuda_lm_head / cuda_linear_out followed by
 // cuda_argmax_last_row (src/ops_cuda.cu:885; src/qwen3_cuda_model.cpp:1070-1071,1339).  Arguments are checked as
-// cuda_lm_head checks them.  Meant for decode batches: every 4 rows cost one more pass over the embedding.
+// cuda_lm_head checks them.  Three or more fp16 rows run on the tensor cores, up to 64 rows per pass over the embedding.
 void cuda_lm_head_argmax_out(const Tensor& hidden_states_cuda, const Tensor& tied_embedding_cuda, Tensor& ids_i32,
                              Tensor* logits = nullptr, cudaStream_t stream = 0);
 

@@ -137,6 +137,7 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
         _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
     if world == 1 and want("lm_head"):
         _lm_head(L, lib, dev, s, timed, record, randn, nreps)
+        _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps)
     if world > 1 and want("lm_head"):
         _lm_head_sharded(lib, dev, timed, record, randn, nreps, sharded, world, rank, table)
     return table
@@ -205,6 +206,21 @@ def _lm_head(L, lib, dev, s, timed, record, randn, nreps):
             record("library GEMM into logits + argmax_rows (two launches, yardstick)", f"{R} x {H} by {VOCAB} x {H} {name}",
                    VOCAB * H * e + R * H * e + 4 * R + 2 * R * VOCAB * e, ms, R)
         del tables
+
+
+def _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps):
+    """The LM head at the other hidden sizes of the configurations (2048, 4096), fp16: one table each (622 MB / 1.24 GB > L2)."""
+    ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    for H in (2048, 4096):
+        table = randn(VOCAB, H, sigma=0.02)
+        for R in (1, 4, 16, 64):
+            hidden = randn(R, H)
+            ids = torch.empty(R, dtype=torch.int32, device=dev)
+            call = lambda: lib.check(L.b2_lm_head_argmax(hidden.data_ptr(), table.data_ptr(), R, H, VOCAB, lib.F16, lib.FAST, 0,
+                                                         None, VOCAB, ids.data_ptr(), None, ws.data_ptr(), s))
+            ms = timed([call], nreps(10))
+            record("lm_head_argmax (ids only)", f"{R} x {H} by {VOCAB} x {H} f16", VOCAB * H * 2 + R * H * 2 + 4 * R, ms, R)
+        del table
 
 
 def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
