@@ -276,7 +276,7 @@ def reference_gpu_kernels(L, lib, dev, stream):
               ref.time_rope_token_positions(q, pos, T, 16, 1e6, 3) + ref.time_rope_token_positions(k, pos, T, 8, 1e6, 3))
     row("qk_norm + rope, T=16384, 16+8 heads x 128 f16", ref_ms,
         ours(lambda: lib.check(L.b2_qk_norm_rope(q.data_ptr(), k.data_ptr(), g128.data_ptr(), g128.data_ptr(), pos.data_ptr(),
-                                                 qo.data_ptr(), ko.data_ptr(), T, 16, 8, 128, 1e-6, 1e6, lib.F16, s))),
+                                                 qo.data_ptr(), ko.data_ptr(), T, 16, 8, 128, 1e-6, 1e6, lib.F16, None, s))),
         note="reference: its four launches (rms_norm x2, rope_token_positions x2); ours: one fused launch")
     del q, k, qo, ko
     vocab, tokens = 151936, 262144
@@ -310,6 +310,13 @@ def reference_gpu_kernels(L, lib, dev, stream):
                 note="reference: cuda_lm_head (cuBLASLt GEMM, allocates the logits) + cuda_argmax_last_row (last row only, "
                      "blocking, 2 cudaMalloc + 2 cudaFree); ours: one launch, every row, ids stay on the device")
         del hid, emb
+    # the launch-paced regime: one decoder layer's in-scope operators back to back (the reference's eight launches)
+    if hasattr(ref.lib, "refcu_time_decode_chain"):
+        for tokens in (1, 4, 64):
+            out[f"decode layer chain, {tokens} tokens (reference: 8 launches)"] = {
+                "reference_us_eager": round(ref.time_decode_chain(tokens, 1e-6, 1e6, 0, 200) * 1e3, 2),
+                "reference_us_graph_replay": round(ref.time_decode_chain(tokens, 1e-6, 1e6, 1, 200) * 1e3, 2),
+                "note": "ours: the `decode layer chain` entries of `ops` (5 launches)"}
     # sampling: the reference draws one token per blocking call; ours draws all rows in one call
     sampler_ws = torch.empty(L.b2_sampler_workspace_bytes(R, vocab), dtype=torch.uint8, device=dev)
     offs = torch.arange(R, dtype=torch.int64, device=dev)

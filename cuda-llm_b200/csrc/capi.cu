@@ -17,7 +17,10 @@ namespace b2 {
 
 namespace {
 thread_local char g_error[512] = "";
+thread_local bool g_programmatic_launch = false;
 }
+
+bool programmatic_launch_enabled() { return g_programmatic_launch; }
 
 void set_error(const char* fmt, ...) {
   va_list args;
@@ -126,7 +129,7 @@ int b2_swiglu(const void* gate, const void* up, void* out, int64_t count, int dt
 }
 
 int b2_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads, int64_t head_dim,
-            float theta, int dtype, int mode, b2_stream stream) {
+            float theta, int dtype, int mode, int32_t* status, b2_stream stream) {
   const char* op = "b2_rope";
   B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
   B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
@@ -135,11 +138,11 @@ int b2_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, 
   B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
   B2_REQUIRE(theta > 0.0f, op, "theta must be positive");
   B2_REQUIRE(tokens == 0 || (x && positions && out), op, "null pointer");
-  return launch_rope(x, positions, out, tokens, heads, head_dim, 0, theta, dtype, mode, as_stream(stream));
+  return launch_rope(x, positions, out, tokens, heads, head_dim, 0, theta, dtype, mode, status, as_stream(stream));
 }
 
 int b2_rope_batched(const void* x, const int32_t* positions, void* out, int64_t batch, int64_t seq, int64_t heads,
-                    int64_t head_dim, float theta, int dtype, int mode, b2_stream stream) {
+                    int64_t head_dim, float theta, int dtype, int mode, int32_t* status, b2_stream stream) {
   const char* op = "b2_rope_batched";
   B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
   B2_REQUIRE(mode_ok(mode), op, "mode must be B2_FAST or B2_DETERMINISTIC");
@@ -149,12 +152,13 @@ int b2_rope_batched(const void* x, const int32_t* positions, void* out, int64_t 
   B2_REQUIRE(head_dim % 2 == 0, op, "head_dim must be even");
   B2_REQUIRE(theta > 0.0f, op, "theta must be positive");
   B2_REQUIRE(batch == 0 || (x && positions && out), op, "null pointer");
-  return launch_rope(x, positions, out, batch * seq, heads, head_dim, seq, theta, dtype, mode, as_stream(stream));
+  return launch_rope(x, positions, out, batch * seq, heads, head_dim, seq, theta, dtype, mode, status, as_stream(stream));
 }
 
 int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
                     const int32_t* positions, void* q_out, void* k_out, int64_t tokens, int64_t q_heads,
-                    int64_t k_heads, int64_t head_dim, float eps, float theta, int dtype, b2_stream stream) {
+                    int64_t k_heads, int64_t head_dim, float eps, float theta, int dtype, int32_t* status,
+                    b2_stream stream) {
   const char* op = "b2_qk_norm_rope";
   B2_REQUIRE(dtype_ok(dtype), op, "dtype must be B2_F32 or B2_F16");
   B2_REQUIRE(tokens >= 0 && q_heads > 0 && k_heads >= 0 && head_dim > 0 &&
@@ -166,7 +170,7 @@ int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, const vo
   B2_REQUIRE(tokens == 0 || (q && q_weight && q_out && positions), op, "null pointer");
   B2_REQUIRE(tokens == 0 || k_heads == 0 || (k && k_weight && k_out), op, "null key pointer with k_heads > 0");
   return launch_qk_norm_rope(q, k, q_weight, k_weight, positions, q_out, k_out, tokens, q_heads, k_heads, head_dim,
-                             eps, theta, dtype, as_stream(stream));
+                             eps, theta, dtype, status, as_stream(stream));
 }
 
 int b2_embedding_gather(const void* table, const int32_t* ids, void* out, int64_t count, int64_t hidden,
@@ -178,6 +182,9 @@ int b2_embedding_gather(const void* table, const int32_t* ids, void* out, int64_
   B2_REQUIRE(count == 0 || (table && ids && out), op, "null pointer");
   return launch_gather(table, ids, out, count, hidden, vocab, dtype, status, as_stream(stream));
 }
+
+void b2_set_programmatic_launch(int enabled) { g_programmatic_launch = enabled != 0; }
+int b2_get_programmatic_launch(void) { return g_programmatic_launch ? 1 : 0; }
 
 int b2_bulk_copy_timeouts(uint32_t* count) {
   if (count == nullptr) return invalid("b2_bulk_copy_timeouts", "null pointer");

@@ -113,7 +113,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return total;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------
+// A kernel launched with the "programmatic stream serialization" attribute may start while the kernel before it on
+// the stream is still running; griddepcontrol.wait then blocks until that kernel has completed and its writes are
+// visible, and griddepcontrol.launch_dependents lets the NEXT kernel's blocks be scheduled early in the same way.
+// Kernels of a decode step last a few microseconds, about as long as the gap between two launches: with both
+// instructions at the top of a kernel the gap is spent under the previous kernel.  Without the launch attribute
+// both instructions do nothing.
+__device__ __forceinline__ void dependent_launch_prologue() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- host-side launch helpers -------------------------------------------------
+
+bool programmatic_launch_enabled();   // the calling thread's b2_set_programmatic_launch switch
+
+// kernel<<<grid, block, smem, s>>>(args...), with the programmatic-serialization attribute when the switch is on
+template <typename... Params, typename... Args>
+inline void launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  if (!programmatic_launch_enabled()) {
+    kernel<<<grid, block, smem, s>>>(args...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);   // errors are picked up by launch_status()
+}
 
 int sm_count();                       // SMs of the current device (cached per device)
 void set_error(const char* fmt, ...);  // records the calling thread's last error message

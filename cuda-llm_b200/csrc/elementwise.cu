@@ -40,6 +40,7 @@ template <typename T, typename Op, int kUnroll>
 __global__ void __launch_bounds__(kThreads)
 binary_stream_kernel(const T* a, const T* b, T* out, int64_t n_vec, int tail, Op op) {
   constexpr int N = Elem<T>::kPerVec;
+  dependent_launch_prologue();
   const uint4* av = reinterpret_cast<const uint4*>(a);
   const uint4* bv = reinterpret_cast<const uint4*>(b);
   uint4* ov = reinterpret_cast<uint4*>(out);
@@ -91,7 +92,7 @@ int launch_binary(const void* a_, const void* b_, void* out_, int64_t n, Op op, 
     const int64_t n_vec = n / N;
     const int64_t tiles = (n_vec + int64_t(kThreads) * kUnroll - 1) / (int64_t(kThreads) * kUnroll);
     const unsigned grid = unsigned(tiles < 1 ? 1 : (tiles < 0x7fffffffll ? tiles : 0x7fffffffll));
-    binary_stream_kernel<T, Op, kUnroll><<<grid, kThreads, 0, s>>>(a, b, out, n_vec, int(n % N), op);
+    launch_kernel(binary_stream_kernel<T, Op, kUnroll>, dim3(grid), dim3(kThreads), 0, s, a, b, out, n_vec, int(n % N), op);
   } else {
     const int64_t blocks = (n + kThreads - 1) / kThreads, cap = int64_t(sm_count()) * kCtasPerSm;
     binary_scalar_kernel<T, Op><<<unsigned(blocks < cap ? blocks : cap), kThreads, 0, s>>>(a, b, out, n, op);

@@ -106,8 +106,9 @@ __device__ __forceinline__ void exchange_trace_start(const ExchangeArgs& xa) {
 }
 
 // Step 3, run by every thread of the thread block that finished the last row.  combine(row, complete, partial_of)
-// is called for rows handed out thread by thread; partial_of(g) returns GPU g's partial of that row; `complete` is
-// false when some GPU's partial had not arrived when the time ran out (the row's result must then be marked invalid).
+// is called for rows handed out thread by thread; partial_of(g), g a compile-time-unrolled or runtime index below
+// `world`, returns GPU g's partial of that row; `complete` is false when some GPU's partial had not arrived when the
+// time ran out (the row's result must then be marked invalid, and the partials of the missing GPUs are undefined).
 template <typename Combine>
 __device__ __forceinline__ void exchange_tail(const ExchangeArgs& xa, int64_t rows, Combine&& combine) {
   unsigned char* own = xa.buf[xa.rank];
@@ -125,17 +126,22 @@ __device__ __forceinline__ void exchange_tail(const ExchangeArgs& xa, int64_t ro
   }
   int all_complete = 1;
   for (int64_t r = tid; r < rows; r += threads) {
-    bool complete = true;
-    for (int g = 0; g < xa.world && complete; ++g) {
-      unsigned long long ignored;
-      complete = slot_wait(exchange_slot(own, parity, g, xa.world, xa.max_rows, r), epoch, start, xa.timeout_ns, &ignored);
+    // all peers' slots of the row are asked for at once (the loads are independent: one trip to L2, not `world`),
+    // again and again until every one carries the epoch or the time is up
+    unsigned long long value[kMaxWorld];
+    unsigned int missing = xa.world >= 32 ? 0xffffffffu : ((1u << xa.world) - 1u);
+    for (int spin = 0; missing != 0u && spin < (1 << 26); ++spin) {
+#pragma unroll
+      for (int g = 0; g < kMaxWorld; ++g) {
+        if (g < xa.world && (missing >> g & 1u) &&
+            slot_load(exchange_slot(own, parity, g, xa.world, xa.max_rows, r), epoch, &value[g]))
+          missing &= ~(1u << g);
+      }
+      if ((spin & 63) == 63 && global_timer_ns() - start > xa.timeout_ns) break;
     }
+    const bool complete = missing == 0u;
     if (xa.trace != nullptr && r == rows - 1) xa.trace[2] = global_timer_ns();
-    combine(r, complete, [&](int g) {
-      unsigned long long value;
-      slot_load(exchange_slot(own, parity, g, xa.world, xa.max_rows, r), epoch, &value);
-      return value;
-    });
+    combine(r, complete, [&](int g) { return value[g]; });
     if (!complete) all_complete = 0;
   }
   all_complete = __syncthreads_and(all_complete);

@@ -27,6 +27,7 @@ template <typename unit_t>
 __global__ void __launch_bounds__(kThreads)
 gather_rows_kernel(const unit_t* __restrict__ table, const int32_t* __restrict__ ids, unit_t* __restrict__ out,
                    int64_t count, int64_t units_per_row, int64_t vocab, int32_t* status) {
+  dependent_launch_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t warps = int64_t(gridDim.x) * (kThreads / kWarpSize);
   for (int64_t t = int64_t(blockIdx.x) * (kThreads / kWarpSize) + (threadIdx.x >> 5); t < count; t += warps) {
@@ -57,8 +58,8 @@ int launch_units(const void* table, const int32_t* ids, void* out, int64_t count
   // one row per warp and no cap on the grid short of its limit: blocks dispatched in order walk the output in
   // order, which measured 6 % faster than a persistent grid striding over the rows
   const int64_t blocks = (count + warps_per_cta - 1) / warps_per_cta, cap = 0x7fffffffll;
-  gather_rows_kernel<unit_t><<<unsigned(blocks < cap ? blocks : cap), kThreads, 0, s>>>(
-      static_cast<const unit_t*>(table), ids, static_cast<unit_t*>(out), count, units_per_row, vocab, status);
+  launch_kernel(gather_rows_kernel<unit_t>, dim3(unsigned(blocks < cap ? blocks : cap)), dim3(kThreads), 0, s,
+                static_cast<const unit_t*>(table), ids, static_cast<unit_t*>(out), count, units_per_row, vocab, status);
   return launch_status("embedding_gather");
 }
 

@@ -17,10 +17,10 @@ int launch_add(const void* a, const void* b, void* out, int64_t n, int dtype, cu
 int launch_swiglu(const void* g, const void* u, void* out, int64_t n, int dtype, int mode, cudaStream_t s);
 // rope.cu: x is [tokens, heads, head_dim]; position of token t is positions[pos_period ? t % pos_period : t]
 int launch_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
-                int64_t head_dim, int64_t pos_period, float theta, int dtype, int mode, cudaStream_t s);
+                int64_t head_dim, int64_t pos_period, float theta, int dtype, int mode, int32_t* status, cudaStream_t s);
 int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
                         void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads,
-                        int64_t head_dim, float eps, float theta, int dtype, cudaStream_t s);
+                        int64_t head_dim, float eps, float theta, int dtype, int32_t* status, cudaStream_t s);
 int rope_bulk_timeouts(unsigned int* out);   // blocking read of a device counter
 int launch_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* qw, const void* kw,
                               const int32_t* positions, void* q_out, void* storage, const int32_t* block_tables,

@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(kThreads)
 paged_kv_write_kernel(const unsigned char* key, const unsigned char* value, unsigned char* storage,
                       const int32_t* block_tables, const int32_t* positions, int64_t tokens, int64_t max_blocks,
                       int64_t layer, PoolShape pool, int32_t* status) {
+  dependent_launch_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t warps = int64_t(gridDim.x) * kWarps;
   for (int64_t w = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5); w < tokens * 2; w += warps) {
@@ -124,11 +125,11 @@ int launch_paged_kv_write(int mode, const void* key, const void* value, void* st
   auto v = static_cast<const unsigned char*>(value);
   auto st = static_cast<unsigned char*>(storage);
   if (mode == 0)
-    paged_kv_write_kernel<0><<<grid, kThreads, 0, s>>>(k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
+    launch_kernel(paged_kv_write_kernel<0>, dim3(grid), dim3(kThreads), 0, s, k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
   else if (mode == 1)
-    paged_kv_write_kernel<1><<<grid, kThreads, 0, s>>>(k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
+    launch_kernel(paged_kv_write_kernel<1>, dim3(grid), dim3(kThreads), 0, s, k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
   else
-    paged_kv_write_kernel<2><<<grid, kThreads, 0, s>>>(k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
+    launch_kernel(paged_kv_write_kernel<2>, dim3(grid), dim3(kThreads), 0, s, k, v, st, block_tables, positions, tokens, max_blocks, layer, pool, status);
   return launch_status("paged_kv_write");
 }
 

@@ -167,6 +167,31 @@ Tensor cuda_swiglu(const Tensor& gate, const Tensor& up) {
 // ---------------------------------------------------------------- rotary embedding
 
 namespace {
+// The rotary-embedding kernels bound their waits on on-chip copies and say so in a status word if one ever runs out.
+// The reference would have surfaced such a failure as a CUDA error at the caller's next call; so does this: the word
+// is one pinned, device-visible int32 per thread and device, read by the host (no synchronisation) at the start of
+// every rotary-embedding call, and a set bit becomes the runtime_error of that call.  The first call of a thread on a
+// device allocates the word: make it outside any stream capture.
+int32_t* rope_status_word() {
+  thread_local std::map<int, int32_t*> words;   // leaked at thread exit on purpose
+  int device = 0;
+  CUDA_CHECK(cudaGetDevice(&device));
+  int32_t*& word = words[device];
+  if (word == nullptr) {
+    CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&word), sizeof(int32_t), cudaHostAllocMapped | cudaHostAllocPortable));
+    *word = 0;
+  }
+  return word;
+}
+int32_t* checked_rope_status(const char* op) {
+  int32_t* word = rope_status_word();
+  if (*static_cast<volatile int32_t*>(word) != 0) {
+    *word = 0;
+    throw std::runtime_error(std::string("CUDA error: ") + op +
+                             ": an earlier rotary-embedding launch gave up waiting for an on-chip copy; its output is incomplete");
+  }
+  return word;
+}
 // host positions -> the thread's device staging area (the reference allocates and frees a buffer
 // per call, src/ops_cuda.cu:707; the copy is blocking in both)
 const int32_t* stage_positions(const std::vector<int32_t>& positions) {
@@ -185,7 +210,8 @@ Tensor cuda_rope(const Tensor& x, const std::vector<int32_t>& positions, float t
   if (s[0] == 0 || s[1] == 0 || s[2] == 0 || s[2] % 2 || positions.empty() || positions.size() != size_t(s[0]) || !(theta > 0))
     reject(op, "invalid or empty shape/positions/theta");
   Tensor out(x.dtype(), s, DeviceType::CUDA);
-  check(b2_rope(x.data(), stage_positions(positions), out.data(), s[0], s[1], s[2], theta, dtype_code(x), mode_code(), 0));
+  check(b2_rope(x.data(), stage_positions(positions), out.data(), s[0], s[1], s[2], theta, dtype_code(x), mode_code(),
+                checked_rope_status(op), 0));
   return out;
 }
 
@@ -199,7 +225,7 @@ Tensor cuda_rope_batched(const Tensor& x, const std::vector<int32_t>& positions,
     reject(op, "invalid shape/positions/theta");
   Tensor out(x.dtype(), s, DeviceType::CUDA);
   check(b2_rope_batched(x.data(), stage_positions(positions), out.data(), s[0], s[1], s[2], s[3], theta, dtype_code(x),
-                        mode_code(), 0));
+                        mode_code(), checked_rope_status(op), 0));
   return out;
 }
 
@@ -215,7 +241,7 @@ void cuda_rope_batched_out(const Tensor& x, const Tensor& positions_device, floa
     reject(op, "positions buffer must be CUDA/F32/contiguous and large enough");
   require_output(out, s, x.dtype(), op);
   check(b2_rope_batched(x.data(), static_cast<const int32_t*>(positions_device.data()), out.data(), s[0], s[1], s[2], s[3],
-                        theta, dtype_code(x), mode_code(), 0));
+                        theta, dtype_code(x), mode_code(), checked_rope_status(op), 0));
 }
 
 namespace {
@@ -228,7 +254,7 @@ void rope_rows(const char* op, const Tensor& x, const Tensor& positions, float t
     reject(op, "expected CUDA F32/F16 [T,H,D] with even D and CUDA/I32 positions [T]");
   require_output(out, x.shape(), x.dtype(), op);
   check(b2_rope(x.data(), static_cast<const int32_t*>(positions.data()), out.data(), x.shape()[0], x.shape()[1],
-                x.shape()[2], theta, dtype_code(x), mode_code(), stream));
+                x.shape()[2], theta, dtype_code(x), mode_code(), checked_rope_status(op), stream));
 }
 }  // namespace
 
@@ -255,7 +281,8 @@ void cuda_qk_norm_rope_out(const Tensor& q, const Tensor& k, const Tensor& qw, c
   require_output(q_out, q.shape(), q.dtype(), op);
   require_output(k_out, k.shape(), k.dtype(), op);
   check(b2_qk_norm_rope(q.data(), k.data(), qw.data(), kw.data(), static_cast<const int32_t*>(positions.data()), q_out.data(),
-                        k_out.data(), q.shape()[0], q.shape()[1], k.shape()[1], q.shape()[2], eps, theta, dtype_code(q), stream));
+                        k_out.data(), q.shape()[0], q.shape()[1], k.shape()[1], q.shape()[2], eps, theta, dtype_code(q),
+                        checked_rope_status(op), stream));
 }
 
 // ---------------------------------------------------------------- softmax

@@ -29,6 +29,7 @@ rms_norm_rows_kernel(const T* x, const T* rhs, const T* __restrict__ w, T* resid
                      int64_t rows, int vecs_per_row, int tpr_shift, float hidden_f, float eps) {
   constexpr int N = Elem<T>::kPerVec;
   __shared__ float warp_part[kRowThreads / kWarpSize];
+  dependent_launch_prologue();
 
   const int tpr = 1 << tpr_shift;
   const int lane_in_row = threadIdx.x & (tpr - 1);
@@ -209,8 +210,8 @@ void launch_rows_vpt(const T* x, const T* rhs, const T* w, T* residual, T* out, 
   while ((1 << shift) < tpr) ++shift;
   const int rows_per_cta = kRowThreads >> shift;
   const unsigned grid = unsigned((rows + rows_per_cta - 1) / rows_per_cta);
-  rms_norm_rows_kernel<T, VPT, kAdd><<<grid, kRowThreads, 0, s>>>(x, rhs, w, residual, out, rows, vecs, shift,
-                                                                 float(hidden), eps);
+  launch_kernel(rms_norm_rows_kernel<T, VPT, kAdd>, dim3(grid), dim3(kRowThreads), 0, s, x, rhs, w, residual, out, rows, vecs,
+                shift, float(hidden), eps);
 }
 
 template <typename T, bool kAdd>

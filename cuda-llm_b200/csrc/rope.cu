@@ -166,6 +166,7 @@ rope_tokens_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, 
                    int hv_shift, int64_t pos_period, float eps, float theta, const __grid_constant__ InvFreq freq) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ float table[];    // per warp: cos[half] then sin[half]
+  dependent_launch_prologue();
   const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* cos_row = table + warp * head_dim;
   float* sin_row = cos_row + half;
@@ -302,9 +303,10 @@ template <typename T, bool kNorm, int kHv, bool kPaged>
 __global__ void __launch_bounds__(kBulkWarps * kWarpSize, kBulkCtasPerSm)
 rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positions, int64_t tokens, int head_dim, int hv,
                         int hv_shift, int64_t pos_period, float eps, float theta, int stages,
-                        const __grid_constant__ InvFreq freq, const __grid_constant__ PagedTarget paged) {
+                        const __grid_constant__ InvFreq freq, const __grid_constant__ PagedTarget paged, int32_t* status) {
   constexpr int N = Elem<T>::kPerVec;
   extern __shared__ __align__(128) unsigned char bulk_smem[];
+  dependent_launch_prologue();
   const int half = head_dim >> 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int vecs_per_head = 2 * hv;
   const int q_heads = q.heads, k_heads = k.heads;
@@ -394,7 +396,10 @@ rope_tokens_bulk_kernel(HeadSet q, HeadSet k, const int32_t* __restrict__ positi
     // the whole warp takes one decision (a lane whose wait succeeded at the last moment must not part from the rest)
     if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(&bars[stage], round & 1u))) {
       // never expected: record it, give every stage's copy one more bounded chance to land, and stop
-      if (lane == 0) atomicAdd(&g_rope_bulk_timeouts, 1u);
+      if (lane == 0) {
+        atomicAdd(&g_rope_bulk_timeouts, 1u);
+        if (status != nullptr) atomicOr(status, kPaged ? 2 : 1);   // this call's outputs are incomplete
+      }
       for (int i = 0; i < stages && t + i * stride < tokens; ++i) {   // copies in flight: tokens t .. t_ahead
         const bool wrapped = stage + i >= stages;
         mbarrier_wait_bounded(&bars[wrapped ? stage + i - stages : stage + i], (wrapped ? round + 1u : round) & 1u);
@@ -512,7 +517,7 @@ template <typename T> bool vector_shape_ok(int64_t head_dim, int* hv_out) {
 
 template <typename T, bool kNorm>
 bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv, int hv_shift,
-                 int64_t pos_period, float eps, float theta, cudaStream_t s, const PagedTarget* paged = nullptr) {
+                 int64_t pos_period, float eps, float theta, int32_t* status, cudaStream_t s, const PagedTarget* paged = nullptr) {
   constexpr int stages = 2, max_warps = kBulkWarps;   // deeper prefetch and other warp counts measured no faster
   const size_t stage = size_t(q.heads + k.heads) * size_t(2 * hv) * 16, per_warp = stages * stage + 2 * size_t(head_dim) * 4;
   const size_t bar_bytes = size_t(kBulkMaxStages) * 8;
@@ -534,43 +539,42 @@ bool launch_bulk(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens,
     return false;
   }
   const int64_t ctas = (tokens + warps - 1) / warps, cap = int64_t(sm_count()) * kBulkCtasPerSm;
-  kernel<<<unsigned(ctas < cap ? ctas : cap), warps * kWarpSize, smem, s>>>(q, k, positions, tokens, int(head_dim), hv,
-                                                                          hv_shift, pos_period, eps, theta, stages,
-                                                                          make_table(head_dim, theta),
-                                                                          paged != nullptr ? *paged : PagedTarget{});
+  launch_kernel(kernel, dim3(unsigned(ctas < cap ? ctas : cap)), dim3(warps * kWarpSize), smem, s, q, k, positions, tokens,
+                int(head_dim), hv, hv_shift, pos_period, eps, theta, stages, make_table(head_dim, theta),
+                paged != nullptr ? *paged : PagedTarget{}, paged != nullptr ? paged->status : status);
   return true;
 }
 
 template <typename T, bool kNorm, bool kOrdered>
 int launch_vector(HeadSet q, HeadSet k, const int32_t* positions, int64_t tokens, int64_t head_dim, int hv,
-                  int64_t pos_period, float eps, float theta, cudaStream_t s, const char* what) {
+                  int64_t pos_period, float eps, float theta, int32_t* status, cudaStream_t s, const char* what) {
   if (!kOrdered) {
     int shift = 0;
     while ((1 << shift) < hv) ++shift;
-    if (launch_bulk<T, kNorm>(q, k, positions, tokens, head_dim, hv, shift, pos_period, eps, theta, s)) return launch_status(what);
+    if (launch_bulk<T, kNorm>(q, k, positions, tokens, head_dim, hv, shift, pos_period, eps, theta, status, s)) return launch_status(what);
   }
   const int64_t ctas = (tokens + kWarpsPerCta - 1) / kWarpsPerCta, cap = int64_t(sm_count()) * 64;
   const unsigned grid = unsigned(ctas < cap ? ctas : cap);
   const size_t smem = size_t(kWarpsPerCta) * size_t(head_dim) * sizeof(float);
   int hv_shift = 0;
   while ((1 << hv_shift) < hv) ++hv_shift;
-  rope_tokens_kernel<T, kNorm, kOrdered><<<grid, kThreads, smem, s>>>(
-      q, k, positions, tokens, int(head_dim), hv, hv_shift, pos_period, eps, theta, make_table(head_dim, theta));
+  launch_kernel(rope_tokens_kernel<T, kNorm, kOrdered>, dim3(grid), dim3(kThreads), smem, s, q, k, positions, tokens,
+                int(head_dim), hv, hv_shift, pos_period, eps, theta, make_table(head_dim, theta));
   return launch_status(what);
 }
 
 template <typename T>
 int launch_rope_typed(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
-                      int64_t head_dim, int64_t pos_period, float theta, int mode, cudaStream_t s) {
+                      int64_t head_dim, int64_t pos_period, float theta, int mode, int32_t* status, cudaStream_t s) {
   if (tokens == 0 || heads == 0 || head_dim == 0) return B2_OK;
   int hv = 0;
   const bool vec = vector_shape_ok<T>(head_dim, &hv) && aligned16(x) && aligned16(out) && heads <= (1 << 20);
   if (vec) {
     HeadSet q{x, nullptr, out, int(heads)}, none{nullptr, nullptr, nullptr, 0};
     return mode == B2_DETERMINISTIC
-               ? launch_vector<T, false, true>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, s,
+               ? launch_vector<T, false, true>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, status, s,
                                                "rope (deterministic)")
-               : launch_vector<T, false, false>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, s,
+               : launch_vector<T, false, false>(q, none, positions, tokens, head_dim, hv, pos_period, 0.f, theta, status, s,
                                                 "rope");
   }
   const int64_t total = tokens * heads * (head_dim / 2);
@@ -589,7 +593,7 @@ int launch_rope_typed(const void* x, const int32_t* positions, void* out, int64_
 template <typename T>
 int launch_qk_typed(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
                     void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads, int64_t head_dim,
-                    float eps, float theta, cudaStream_t s) {
+                    float eps, float theta, int32_t* status, cudaStream_t s) {
   if (tokens == 0 || head_dim == 0 || q_heads + k_heads == 0) return B2_OK;
   int hv = 0;
   const bool vec = vector_shape_ok<T>(head_dim, &hv) && aligned16(q) && aligned16(q_out) && aligned16(qw) &&
@@ -597,7 +601,7 @@ int launch_qk_typed(const void* q, const void* k, const void* qw, const void* kw
                    q_heads + k_heads <= (1 << 20);
   if (vec) {
     HeadSet qs{q, qw, q_out, int(q_heads)}, ks{k, kw, k_out, int(k_heads)};
-    return launch_vector<T, true, false>(qs, ks, positions, tokens, head_dim, hv, 0, eps, theta, s, "qk_norm_rope");
+    return launch_vector<T, true, false>(qs, ks, positions, tokens, head_dim, hv, 0, eps, theta, status, s, "qk_norm_rope");
   }
   const InvFreq table = make_table(head_dim, theta);
   const int warps_per_cta = kThreads / kWarpSize;
@@ -620,19 +624,19 @@ int rope_bulk_timeouts(unsigned int* out) {
 }
 
 int launch_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads, int64_t head_dim,
-                int64_t pos_period, float theta, int dtype, int mode, cudaStream_t s) {
+                int64_t pos_period, float theta, int dtype, int mode, int32_t* status, cudaStream_t s) {
   return dtype == B2_F32
-             ? launch_rope_typed<float>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, s)
-             : launch_rope_typed<__half>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, s);
+             ? launch_rope_typed<float>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, status, s)
+             : launch_rope_typed<__half>(x, positions, out, tokens, heads, head_dim, pos_period, theta, mode, status, s);
 }
 
 int launch_qk_norm_rope(const void* q, const void* k, const void* qw, const void* kw, const int32_t* positions,
                         void* q_out, void* k_out, int64_t tokens, int64_t q_heads, int64_t k_heads, int64_t head_dim,
-                        float eps, float theta, int dtype, cudaStream_t s) {
+                        float eps, float theta, int dtype, int32_t* status, cudaStream_t s) {
   return dtype == B2_F32 ? launch_qk_typed<float>(q, k, qw, kw, positions, q_out, k_out, tokens, q_heads, k_heads,
-                                                  head_dim, eps, theta, s)
+                                                  head_dim, eps, theta, status, s)
                          : launch_qk_typed<__half>(q, k, qw, kw, positions, q_out, k_out, tokens, q_heads, k_heads,
-                                                   head_dim, eps, theta, s);
+                                                   head_dim, eps, theta, status, s);
 }
 
 // Fused form that leaves the keys and values in the paged KV cache.  Only the vector (bulk-copy) kernel has it:
@@ -654,11 +658,11 @@ int launch_qk_norm_rope_paged(const void* q, const void* k, const void* v, const
   if (dtype == B2_F32) {
     if (aligned && vector_shape_ok<float>(head_dim, &hv)) {
       while ((1 << shift) < hv) ++shift;
-      launched = launch_bulk<float, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, s, &paged);
+      launched = launch_bulk<float, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, status, s, &paged);
     }
   } else if (aligned && vector_shape_ok<__half>(head_dim, &hv)) {
     while ((1 << shift) < hv) ++shift;
-    launched = launch_bulk<__half, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, s, &paged);
+    launched = launch_bulk<__half, true>(qs, ks, positions, tokens, head_dim, hv, shift, 0, eps, theta, status, s, &paged);
   }
   if (!launched) {
     set_error("b2_qk_norm_rope_paged: this shape or alignment has no fused kernel; use b2_qk_norm_rope and b2_paged_kv_write_*");

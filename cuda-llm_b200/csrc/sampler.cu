@@ -12,7 +12,7 @@
 //   sort     when 0 < top_k <= 2048 only the k largest keys matter: a threshold taken from a sorted sample of
 //            the row, ONE pass over the logits that gathers the few hundred tokens above it, and a one-block
 //            sort of those (checked; a call whose sample misled it is redone by a radix select over all 64
-//            key bits); otherwise a bitonic network sorts the whole row (keys in registers, 4096-key tiles,
+//            key bits, one more launch that otherwise returns at once); otherwise a bitonic network sorts the whole row (keys in registers, 4096-key tiles,
 //            wider steps in global memory)
 //   select   one thread block per row: the exponentials of a 2048-token chunk are computed in
 //            parallel, one thread adds them in order (the only serial part left) and records the
@@ -48,9 +48,9 @@ __device__ __forceinline__ int32_t key_index(unsigned long long key) { return in
 template <typename T>
 __global__ void __launch_bounds__(256)
 sampler_keys_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature,
-                    unsigned long long* keys, const int* only_if) {
-  if (only_if != nullptr && *only_if == 0) return;   // a stage of the exact fallback that this call does not need
+                    unsigned long long* keys, const int* only_rows) {
   const int64_t row = blockIdx.y;
+  if (only_rows != nullptr && only_rows[row] == 0) return;   // this row was settled without the whole-row sort
   const T* src = logits + row * row_stride;
   unsigned long long* dst = keys + row * padded;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < padded; i += int64_t(gridDim.x) * blockDim.x)
@@ -67,9 +67,10 @@ __device__ __forceinline__ void compare_exchange(unsigned long long& a, unsigned
 // this sorts the tile from scratch; with k_first == k_last it finishes a merge whose wide steps ran in
 // global memory.
 __global__ void __launch_bounds__(kSortThreads)
-bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t k_first, int64_t k_last) {
+bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t k_first, int64_t k_last, const int* only_rows) {
   extern __shared__ unsigned long long tile_keys[];
   const int64_t row = blockIdx.y;
+  if (only_rows != nullptr && only_rows[row] == 0) return;
   unsigned long long* base = keys + row * padded + int64_t(blockIdx.x) * tile;
   const int64_t global0 = int64_t(blockIdx.x) * tile;
   for (int i = threadIdx.x; i < tile; i += kSortThreads) tile_keys[i] = base[i];
@@ -90,8 +91,9 @@ bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t 
 // One step with j >= tile: partners sit in different tiles, so it runs in global memory (the keys of a
 // few hundred rows fit the L2).
 __global__ void __launch_bounds__(256)
-bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j) {
+bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const int* only_rows) {
   const int64_t row = blockIdx.y;
+  if (only_rows != nullptr && only_rows[row] == 0) return;
   unsigned long long* base = keys + row * padded;
   for (int64_t p = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; p < padded / 2; p += int64_t(gridDim.x) * blockDim.x) {
     const int64_t i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
@@ -169,9 +171,10 @@ __device__ __forceinline__ void layout_s_to_b(unsigned long long (&key)[kRegKeys
 // k_first == 2: sorts every 4096-key tile from scratch (phases 2 .. 4096).  k_first == k_last > 4096: the steps
 // j = 2048 .. 1 that finish a merge whose wide steps ran in global memory.
 __global__ void __launch_bounds__(kRegThreads)
-bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last) {
+bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last, const int* only_rows) {
   __shared__ unsigned long long tile[kTile];
   const int64_t row = blockIdx.y, tile_global = int64_t(blockIdx.x) * kTile;
+  if (only_rows != nullptr && only_rows[row] == 0) return;
   unsigned long long* base = keys + row * padded + tile_global;
   const int t = threadIdx.x, lane = t & 31;
   const int64_t first_global = tile_global + int64_t(t) * kRegKeys;   // layout B: global index of register 0
@@ -205,8 +208,9 @@ bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t 
 // Two wide steps (j and j/2, both >= the tile) in one pass over global memory: the four elements that the two
 // steps connect are loaded once.
 __global__ void __launch_bounds__(256)
-bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j) {
+bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const int* only_rows) {
   const int64_t row = blockIdx.y, h = j >> 1;
+  if (only_rows != nullptr && only_rows[row] == 0) return;
   unsigned long long* base = keys + row * padded;
   for (int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < padded / 4; q += int64_t(gridDim.x) * blockDim.x) {
     const int64_t i = ((q & ~(h - 1)) << 2) | (q & (h - 1));   // bits j and j/2 clear
@@ -220,112 +224,79 @@ bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, in
   }
 }
 
-// ---- small top_k: radix select of the k-th largest key over all 64 bits (six digits of 11, 11, 11, 11,
-// 11 and 9 bits, most significant first).  Keys are unique (they carry the token index), so "every key
-// >= the k-th largest" is exactly k keys and the tie rule needs no special case.
+// ---- small top_k, exact fallback: radix select of the k-th largest key over all 64 bits (six digits of 11, 11,
+// 11, 11, 11 and 9 bits, most significant first), one thread block per row, in ONE launch that returns at once
+// unless the sampled-threshold path below raised its flag.  Keys are recomputed from the logits in every pass
+// (no key array); they are unique (they carry the token index), so "every key >= the k-th largest" is exactly k
+// keys and the tie rule needs no special case.  Seven passes over the row by one thread block: slow, and rare.
 constexpr int kSelectBins = 2048;
 constexpr int kSelectRounds = 6;
 constexpr int kMaxSelectK = 2048;
+constexpr int kExactThreads = 1024;
 
-struct SelectState {                 // per row, in the workspace
-  unsigned long long prefix;         // the digits fixed so far, in place
-  unsigned int remaining;            // how many of the wanted k still lie inside the open bin
-  unsigned int taken;                // compaction cursor
-};
-
-__global__ void select_init_kernel(SelectState* state, int64_t rows, unsigned int k, const int* only_if) {
-  if (only_if != nullptr && *only_if == 0) return;
-  const int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (r < rows) { state[r].prefix = 0ull; state[r].remaining = k; state[r].taken = 0u; }
-}
-
-// Histogram of one digit over the keys whose higher digits equal the prefix found so far.
-__global__ void __launch_bounds__(256)
-select_histogram_kernel(const unsigned long long* keys, int64_t width, int64_t padded, int shift, int bits,
-                        unsigned long long mask_above, const SelectState* state, unsigned int* histograms,
-                        const int* only_if) {
-  __shared__ unsigned int local[kSelectBins];
-  if (only_if != nullptr && *only_if == 0) return;
-  const int64_t row = blockIdx.y;
-  const int bins = 1 << bits;
-  for (int b = threadIdx.x; b < bins; b += blockDim.x) local[b] = 0u;
-  __syncthreads();
-  const unsigned long long prefix = state[row].prefix;
-  const unsigned long long* src = keys + row * padded;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
-    const unsigned long long key = src[i];
-    if ((key & mask_above) == prefix) atomicAdd(&local[unsigned(key >> shift) & unsigned(bins - 1)], 1u);
-  }
-  __syncthreads();
-  unsigned int* out = histograms + row * kSelectBins;
-  for (int b = threadIdx.x; b < bins; b += blockDim.x)
-    if (local[b] != 0u) atomicAdd(&out[b], local[b]);
-}
-
-// Walks the histogram from the top bin down until the wanted count is covered: fixes the next digit of the
-// prefix, updates what is still wanted from inside that bin, and clears the histogram for the next round.
-__global__ void __launch_bounds__(256)
-select_scan_kernel(int shift, int bits, SelectState* state, unsigned int* histograms, const int* only_if) {
+template <typename T>
+__global__ void __launch_bounds__(kExactThreads)
+topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature, int top_k,
+                  unsigned long long* keys, const int* only_if) {
   __shared__ unsigned int counts[kSelectBins];
-  if (only_if != nullptr && *only_if == 0) return;
+  __shared__ unsigned long long survivors[kMaxSelectK];
+  __shared__ unsigned long long prefix_s;
+  __shared__ unsigned int remaining_s, taken_s;
+  if (*only_if == 0) return;
   const int64_t row = blockIdx.x;
-  const int bins = 1 << bits;
-  unsigned int* hist = histograms + row * kSelectBins;
-  for (int b = threadIdx.x; b < bins; b += blockDim.x) { counts[b] = hist[b]; hist[b] = 0u; }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned int want = state[row].remaining;
-    unsigned long long digit = 0;
-    for (int b = bins - 1; b >= 0; --b) {
-      if (counts[b] >= want) { digit = static_cast<unsigned long long>(b); break; }
-      want -= counts[b];
+  const T* src = logits + row * row_stride;
+  const int tid = threadIdx.x;
+  if (tid == 0) { prefix_s = 0ull; remaining_s = unsigned(top_k); taken_s = 0u; }
+  const int shifts[kSelectRounds] = {53, 42, 31, 20, 9, 0}, widths[kSelectRounds] = {11, 11, 11, 11, 11, 9};
+  unsigned long long mask_above = 0ull;
+  for (int round = 0; round < kSelectRounds; ++round) {
+    const int shift = shifts[round], bins = 1 << widths[round];
+    for (int b = tid; b < bins; b += kExactThreads) counts[b] = 0u;
+    __syncthreads();
+    const unsigned long long prefix = prefix_s;
+    for (int64_t i = tid; i < width; i += kExactThreads) {
+      const unsigned long long key = sample_key(__fdiv_rn(Elem<T>::load(src + i), temperature), uint32_t(i));
+      if ((key & mask_above) == prefix) atomicAdd(&counts[unsigned(key >> shift) & unsigned(bins - 1)], 1u);
     }
-    state[row].prefix |= digit << shift;
-    state[row].remaining = want;
+    __syncthreads();
+    if (tid == 0) {   // from the top bin down until the wanted count is covered: the next digit of the k-th largest key
+      unsigned int want = remaining_s;
+      unsigned long long digit = 0;
+      for (int b = bins - 1; b >= 0; --b) {
+        if (counts[b] >= want) { digit = static_cast<unsigned long long>(b); break; }
+        want -= counts[b];
+      }
+      prefix_s = prefix | (digit << shift);
+      remaining_s = want;
+    }
+    mask_above |= ((1ull << widths[round]) - 1ull) << shift;
+    __syncthreads();
   }
-}
-
-// After the last round state.prefix IS the k-th largest key: gather every key >= it (exactly k of them).
-__global__ void __launch_bounds__(256)
-select_compact_kernel(const unsigned long long* keys, int64_t width, int64_t padded, SelectState* state,
-                      unsigned long long* survivors, const int* only_if) {
-  if (only_if != nullptr && *only_if == 0) return;
-  const int64_t row = blockIdx.y;
-  const unsigned long long* src = keys + row * padded;
-  const unsigned long long cut = state[row].prefix;
-  unsigned long long* out = survivors + row * int64_t(kMaxSelectK);
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < width; i += int64_t(gridDim.x) * blockDim.x) {
-    const unsigned long long key = src[i];
+  // prefix_s IS the k-th largest key: gather every key >= it (exactly top_k of them), sort, keep
+  const unsigned long long cut = prefix_s;
+  for (int64_t i = tid; i < width; i += kExactThreads) {
+    const unsigned long long key = sample_key(__fdiv_rn(Elem<T>::load(src + i), temperature), uint32_t(i));
     if (key >= cut) {
-      const unsigned int slot = atomicAdd(&state[row].taken, 1u);
-      if (slot < unsigned(kMaxSelectK)) out[slot] = key;
+      const unsigned int slot = atomicAdd(&taken_s, 1u);
+      if (slot < unsigned(kMaxSelectK)) survivors[slot] = key;
     }
   }
-}
-
-// Sorts one row's survivors in shared memory, descending, into the front of the row's key area.
-__global__ void __launch_bounds__(kSortThreads)
-select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const unsigned long long* survivors,
-                     const int* only_if) {
-  __shared__ unsigned long long buf[kMaxSelectK];
-  if (only_if != nullptr && *only_if == 0) return;
-  const int64_t row = blockIdx.x;
-  const unsigned long long* in = survivors + row * int64_t(kMaxSelectK);
-  int n = 1;
+  __syncthreads();
+  int n = 2;
   while (n < top_k) n <<= 1;
-  for (int i = threadIdx.x; i < n; i += kSortThreads) buf[i] = i < top_k ? in[i] : 0ull;
+  for (int i = tid; i < n; i += kExactThreads) if (i >= top_k) survivors[i] = 0ull;
   __syncthreads();
   for (int k = 2; k <= n; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int p = threadIdx.x; p < n / 2; p += kSortThreads) {
+      for (int p = tid; p < n / 2; p += kExactThreads) {
         const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
-        compare_exchange(buf[i], buf[i | j], (i & k) == 0);
+        compare_exchange(survivors[i], survivors[i | j], (i & k) == 0);
       }
       __syncthreads();
     }
   }
   unsigned long long* dst = keys + row * padded;
-  for (int i = threadIdx.x; i < top_k; i += kSortThreads) dst[i] = buf[i];
+  for (int i = tid; i < top_k; i += kExactThreads) dst[i] = survivors[i];
 }
 
 // ---- small top_k, the usual case: ONE pass over the logits and no key array.
@@ -338,7 +309,7 @@ select_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const 
 // The result is exact or the call is redone: when a row ends with fewer than top_k or more than kCandidates
 // candidates (unlucky sample, long runs of equal logits), or when logits / temperature could overflow or lose
 // precision near the threshold (then equal scores may hide behind different logits), a flag is raised and the
-// radix select over all 64 key bits above redoes every row; its stages are launched in any case and return at
+// radix select over all 64 key bits above redoes every row; that kernel is launched in any case and returns at
 // once when the flag is down.  The margin covers the tokens whose score can equal the top_k-th score although
 // their logit is smaller: scores are logits / temperature, a monotonic map with a relative rounding error of
 // 2^-24.  A NaN logit also sends the call to the exact select (whose key order ranks NaNs as the reference's sort does).
@@ -382,9 +353,10 @@ __device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& 
 template <typename T>
 __global__ void __launch_bounds__(256)
 topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int top_k, int safe, CutState* cut,
-                     int* overflow) {
+                     int* overflow, int overflow_stride) {   // the flag of row r is overflow[r * overflow_stride]: stride 0 = one flag per call
   __shared__ uint32_t sample[kSplitSamples];
   const int64_t row = blockIdx.x;
+  overflow += row * overflow_stride;
   const T* src = logits + row * row_stride;
   for (int s = threadIdx.x; s < kSplitSamples; s += 256) {
     const float x = Elem<T>::load(src + (int64_t(s) * width) / kSplitSamples);   // width > kSplitSamples: distinct tokens
@@ -421,9 +393,10 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
 template <typename T>
 __global__ void __launch_bounds__(256)
 topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, CutState* cut,
-                   unsigned long long* candidates, const int* overflow) {
-  if (*overflow != 0) return;                      // the call is being redone by the exact select anyway
+                   unsigned long long* candidates, const int* overflow, int overflow_stride) {
   const int64_t row = blockIdx.y;
+  overflow += row * overflow_stride;
+  if (*overflow != 0) return;                      // the row (or the call) is being redone by the exact path anyway
   const float threshold = cut[row].threshold;
   unsigned long long* out = candidates + row * int64_t(kCandidates);
   bool strange = false;
@@ -478,11 +451,13 @@ __device__ __forceinline__ unsigned long long sampler_hash(unsigned long long x)
 
 __global__ void __launch_bounds__(kSelectThreads)
 sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padded, int top_k, float top_p,
-                    unsigned long long seed, const unsigned long long* draw_offsets, float* running, int32_t* out_ids) {
+                    unsigned long long seed, const unsigned long long* draw_offsets, float* running, int32_t* out_ids,
+                    const int* only_rows) {
   __shared__ float stage[kChunk];
   __shared__ float carry;
   __shared__ int found;
   const int64_t row = blockIdx.x;
+  if (only_rows != nullptr && only_rows[row] == 0) return;
   const unsigned long long* sorted = keys + row * padded;
   float* cum = running + row * padded;
   const int64_t limit = top_k == 0 ? width : (int64_t(top_k) < width ? int64_t(top_k) : width);
@@ -564,6 +539,294 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
   if (tid == 0) out_ids[row] = key_index(sorted[best]);
 }
 
+// ---- top_p < 1 over the whole vocabulary without sorting it.
+// The reference sorts all scores and walks them with one thread (src/ops_cuda.cu:575-617): `total` is the fp32 sum
+// of every exponential in descending order, then the top-p prefix and the pick walk the head of that order.  Only
+// the HEAD needs the order.  For the rest, the running sum S = M * 2^(k-23) (M a 24-bit integer) is already large
+// against every term e that is left, and S + e rounds to (M + round(e / 2^(k-23))) * 2^(k-23) -- an integer increment
+// that does not depend on M -- unless e / 2^(k-23) falls exactly on a half (a tie: the parity of M decides) or the
+// sum reaches the next power of two (the grid of the rounding doubles).  Integer increments commute, so away from
+// those two events the ORDER of the terms does not matter, only their multiset:
+//   head    the few thousand largest logits, found as in the top-k path (sampled threshold, one pass), sorted in
+//           one thread block, summed in order by one thread with the running sums kept: S_head, and its power of
+//           two k
+//   tail    one pass over the other logits: every term's increment for k and for k + 1 is added into one of 2048
+//           buckets by score (a monotonic map, so the buckets partition the descending order into consecutive
+//           runs); ties are flagged per bucket
+//   finish  one thread walks the buckets: M += bucket sum.  A bucket with a tie, or in which M would pass 2^24, is
+//           the only place where the order matters: its terms (tens) are gathered, sorted and added one by one in
+//           fp32.  That yields `total` bit for bit.  The top-p walk and the pick then run over the head exactly as
+//           the reference's single thread does.
+// A row that breaks an assumption (fewer than 64 or more than 8192 head candidates, a NaN, the sum growing by more
+// than one power of two in the tail, a bucket of more than 2048 terms, a prefix that does not end inside the head)
+// raises its flag and is redone by the whole-row sort; those kernels are launched in any case and return at once for
+// the rows whose flag is down.
+constexpr int kTailBuckets = 2048;
+constexpr unsigned int kHeadTarget = 2000;     // the splitter's threshold then leaves about 3000 head candidates of 150k tokens
+constexpr int kMinHead = 64;
+
+struct HeadState {          // per row
+  float sum;                // S_head
+  float max_score;          // score of the first token of the order
+  float low_score;          // score of the last head token
+  int count;
+};
+
+// increment of a term e under a sum whose unit in the last place is 2^(k-23), and whether it is a tie
+__device__ __forceinline__ void term_increment(float e, int k, unsigned int& r, bool& tie) {
+  const uint32_t b = __float_as_uint(e);
+  const uint32_t field = b >> 23;                                   // e > 0: no sign bit
+  const uint32_t m = field != 0u ? ((b & 0x7fffffu) | 0x800000u) : (b & 0x7fffffu);
+  const int d = k - (field != 0u ? int(field) - 127 : -126);      // e = m * 2^(E-23), increment = m / 2^d
+  if (d >= 25 || m == 0u) { r = 0u; tie = false; return; }
+  if (d < 1) { r = 0xffffffffu; tie = true; return; }                // a term as large as the sum: never in a tail
+  r = (m + (1u << (d - 1))) >> d;
+  tie = (m & ((1u << d) - 1u)) == (1u << (d - 1));
+}
+__device__ __forceinline__ int exponent_of(float s) { return int((__float_as_uint(s) >> 23) & 0xffu) - 127; }
+
+__device__ __forceinline__ int tail_bucket(float score, float low_score, float scale) {
+  const float t = (low_score - score) * scale;                      // >= 0 for every tail term; monotonic in the score
+  const int b = t >= float(kTailBuckets - 1) ? kTailBuckets - 1 : int(t);
+  return b < 0 ? 0 : b;
+}
+// buckets per unit of score: the tail terms that can still move the sum lie within (k - 26) * ln 2 of the maximum
+__device__ __forceinline__ float tail_scale(const HeadState& h) {
+  const float lowest = h.max_score + float(exponent_of(h.sum) - 26) * 0.6931471805599453f;
+  const float span = h.low_score - lowest;
+  return span > 1e-6f ? float(kTailBuckets) / span : 0.0f;
+}
+
+// head: sort the row's candidates (all of them), leave them at the front of the row's key area, and add their
+// exponentials in order, keeping every running sum
+__global__ void __launch_bounds__(kSortThreads)
+topp_head_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
+                 float* running, unsigned int* tails, HeadState* heads, int* row_flags) {
+  extern __shared__ unsigned long long buf[];
+  __shared__ float stage[kChunk];
+  __shared__ float carry;
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  // the tail pass adds into these: they start at zero
+  unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+  for (int i = tid; i < 3 * kTailBuckets; i += kSortThreads) tail[i] = 0u;
+  if (row_flags[row] != 0) return;
+  const unsigned int count = cut[row].taken;
+  if (count < unsigned(kMinHead) || count > unsigned(kCandidates)) {
+    if (tid == 0) row_flags[row] = 1;
+    return;
+  }
+  const unsigned long long* in = candidates + row * int64_t(kCandidates);
+  int n = 2;
+  while (n < int(count)) n <<= 1;
+  for (int i = tid; i < n; i += kSortThreads) buf[i] = unsigned(i) < count ? in[i] : 0ull;
+  __syncthreads();
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int p = tid; p < n / 2; p += kSortThreads) {
+        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+        compare_exchange(buf[i], buf[i | j], (i & k) == 0);
+      }
+      __syncthreads();
+    }
+  }
+  unsigned long long* dst = keys + row * padded;
+  for (int i = tid; i < int(count); i += kSortThreads) dst[i] = buf[i];
+  const float maximum = key_score(buf[0]);
+  float* cum = running + row * padded;
+  if (tid == 0) carry = 0.0f;
+  __syncthreads();
+  for (int base = 0; base < int(count); base += kChunk) {
+    const int m = int(count) - base < kChunk ? int(count) - base : kChunk;
+    for (int j = tid; j < m; j += kSortThreads) stage[j] = expf(key_score(buf[base + j]) - maximum);
+    __syncthreads();
+    if (tid == 0) {
+      float sum = carry;
+      for (int j = 0; j < m; ++j) { sum += stage[j]; stage[j] = sum; }
+      carry = sum;
+    }
+    __syncthreads();
+    for (int j = tid; j < m; j += kSortThreads) cum[base + j] = stage[j];
+    __syncthreads();
+  }
+  if (tid == 0) heads[row] = HeadState{carry, maximum, key_score(buf[count - 1]), int(count)};
+}
+
+// tail: increments of every term below the head, per bucket, for the head's power of two and the next one.
+// Per bucket three words: sum of increments under k, under k + 1, and (terms << 2 | tie under k + 1 << 1 | tie under k).
+template <typename T>
+__global__ void __launch_bounds__(256)
+topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, const CutState* cut,
+                 const HeadState* heads, unsigned int* tails, int* row_flags) {
+  __shared__ unsigned int local[3 * kTailBuckets];
+  const int64_t row = blockIdx.y;
+  if (row_flags[row] != 0) return;
+  for (int i = threadIdx.x; i < 3 * kTailBuckets; i += 256) local[i] = 0u;
+  __syncthreads();
+  const HeadState h = heads[row];
+  const float threshold = cut[row].threshold, scale = tail_scale(h);
+  const int k = exponent_of(h.sum);
+  bool broken = false;
+  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t) {
+    if (x >= threshold) return;                                   // a head token (a NaN would have raised the row's flag)
+    const float score = __fdiv_rn(x, temperature);
+    const float e = expf(score - h.max_score);
+    unsigned int r0, r1;
+    bool t0, t1;
+    term_increment(e, k, r0, t0);
+    term_increment(e, k + 1, r1, t1);
+    if (r0 == 0xffffffffu) { broken = true; return; }
+    if ((r0 | r1) == 0u && !t0 && !t1) return;                    // cannot move the sum under either power of two
+    const int b = tail_bucket(score, h.low_score, scale);
+    if (r0 != 0u) atomicAdd(&local[b], r0);
+    if (r1 != 0u) atomicAdd(&local[kTailBuckets + b], r1);
+    atomicAdd(&local[2 * kTailBuckets + b], 4u);
+    if (t0 || t1) atomicOr(&local[2 * kTailBuckets + b], (t0 ? 1u : 0u) | (t1 ? 2u : 0u));
+  });
+  if (broken) row_flags[row] = 1;
+  __syncthreads();
+  unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+  for (int i = threadIdx.x; i < 2 * kTailBuckets; i += 256)
+    if (local[i] != 0u) atomicAdd(&tail[i], local[i]);
+  for (int i = 2 * kTailBuckets + threadIdx.x; i < 3 * kTailBuckets; i += 256) {
+    const unsigned int v = local[i];
+    if (v != 0u) { atomicAdd(&tail[i], v & ~3u); if (v & 3u) atomicOr(&tail[i], v & 3u); }
+  }
+}
+
+// finish: the walk over the buckets (exact where the order matters), then the reference's top-p walk and pick over the head
+template <typename T>
+__global__ void __launch_bounds__(kSortThreads)
+topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, const CutState* cut,
+                   const unsigned long long* keys, int64_t padded, const float* running, const unsigned int* tails,
+                   const HeadState* heads, float top_p, unsigned long long seed, const unsigned long long* draw_offsets,
+                   int32_t* out_ids, int* row_flags) {
+  __shared__ unsigned long long bucket_keys[kTailBuckets];
+  __shared__ float stage[kChunk];
+  __shared__ float carry;
+  __shared__ unsigned int walk_m;
+  __shared__ int walk_k, walk_bucket, found, give_up;
+  __shared__ unsigned int gathered;
+  const int64_t row = blockIdx.x;
+  if (row_flags[row] != 0) return;
+  const int tid = threadIdx.x;
+  const HeadState h = heads[row];
+  const unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+  const float threshold = cut[row].threshold, scale = tail_scale(h);
+  const int k0 = exponent_of(h.sum);
+  const T* src = logits + row * row_stride;
+  if (tid == 0) {
+    walk_m = (__float_as_uint(h.sum) & 0x7fffffu) | 0x800000u;
+    walk_k = k0;
+    walk_bucket = 0;
+    give_up = 0;
+  }
+  __syncthreads();
+  for (;;) {
+    if (tid == 0) {
+      unsigned int m = walk_m;
+      int k = walk_k, b = walk_bucket;
+      for (; b < kTailBuckets; ++b) {
+        const unsigned int info = tail[2 * kTailBuckets + b];
+        if (info == 0u) continue;
+        if (k > k0 + 1) { give_up = 1; break; }
+        const unsigned int r = k == k0 ? tail[b] : tail[kTailBuckets + b];
+        const bool tie = (info & (k == k0 ? 1u : 2u)) != 0u;
+        if (tie || static_cast<unsigned long long>(m) + r > (1ull << 24)) break;   // the order inside this bucket matters
+        m += r;
+        if (m == (1u << 24)) { m = 1u << 23; ++k; }
+      }
+      walk_m = m; walk_k = k; walk_bucket = b;
+      gathered = 0u;
+    }
+    __syncthreads();
+    if (give_up != 0) { if (tid == 0) row_flags[row] = 1; return; }
+    const int b = walk_bucket;
+    if (b >= kTailBuckets) break;
+    // gather the terms of bucket b that can move the sum, sort them into the reference's order, add them one by one
+    for (int64_t i = tid; i < width; i += kSortThreads) {
+      const float x = Elem<T>::load(src + i);
+      if (x >= threshold) continue;
+      const float score = __fdiv_rn(x, temperature);
+      if (tail_bucket(score, h.low_score, scale) != b) continue;
+      const float e = expf(score - h.max_score);
+      unsigned int r0, r1;
+      bool t0, t1;
+      term_increment(e, k0, r0, t0);
+      term_increment(e, k0 + 1, r1, t1);
+      if ((r0 | r1) == 0u && !t0 && !t1) continue;
+      const unsigned int slot = atomicAdd(&gathered, 1u);
+      if (slot < unsigned(kTailBuckets)) bucket_keys[slot] = sample_key(score, uint32_t(i));
+    }
+    __syncthreads();
+    const unsigned int count = gathered;
+    if (count > unsigned(kTailBuckets)) { if (tid == 0) row_flags[row] = 1; return; }
+    int n = 2;
+    while (n < int(count)) n <<= 1;
+    for (int i = int(count) + tid; i < n; i += kSortThreads) bucket_keys[i] = 0ull;
+    __syncthreads();
+    for (int k = 2; k <= n; k <<= 1) {
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        for (int p = tid; p < n / 2; p += kSortThreads) {
+          const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+          compare_exchange(bucket_keys[i], bucket_keys[i | j], (i & k) == 0);
+        }
+        __syncthreads();
+      }
+    }
+    if (tid == 0) {
+      float sum = __uint_as_float((uint32_t(walk_k + 127) << 23) | (walk_m & 0x7fffffu));
+      for (unsigned int i = 0; i < count; ++i) sum += expf(key_score(bucket_keys[i]) - h.max_score);
+      walk_m = (__float_as_uint(sum) & 0x7fffffu) | 0x800000u;
+      walk_k = exponent_of(sum);
+      walk_bucket = b + 1;
+    }
+    __syncthreads();
+  }
+  const float total = __uint_as_float((uint32_t(walk_k + 127) << 23) | (walk_m & 0x7fffffu));
+
+  // the reference's top-p walk (src/ops_cuda.cu:596-603) over the head; it must end strictly above the head's lowest score
+  const unsigned long long* sorted = keys + row * padded;
+  const float* cum = running + row * padded;
+  const int limit = h.count;
+  if (tid == 0) { carry = 0.0f; found = -1; }
+  __syncthreads();
+  int prefix = -1;
+  for (int base = 0; base < limit; base += kChunk) {
+    const int m = limit - base < kChunk ? limit - base : kChunk;
+    for (int j = tid; j < m; j += kSortThreads) stage[j] = __fdiv_rn(expf(key_score(sorted[base + j]) - h.max_score), total);
+    __syncthreads();
+    if (tid == 0) {
+      float cumulative = carry;
+      for (int j = 0; j < m; ++j) {
+        cumulative += stage[j];
+        if (cumulative >= top_p) { found = j; break; }
+      }
+      carry = cumulative;
+    }
+    __syncthreads();
+    if (found >= 0) { prefix = base + found + 1; break; }
+  }
+  if (prefix < 0 || !(key_score(sorted[prefix - 1]) > h.low_score)) {   // not settled inside the head: the whole-row path decides
+    if (tid == 0) row_flags[row] = 1;
+    return;
+  }
+  const float prefix_total = cum[prefix - 1];
+  const unsigned long long offset = draw_offsets != nullptr ? draw_offsets[row] : 0ull;
+  const unsigned long long bits = sampler_hash(seed ^ (offset * 0xd1342543de82ef95ULL));
+  const float u = (static_cast<float>((bits >> 11) & 0x1fffffffffffffULL) + 0.5f) / 9007199254740992.0f;
+  const float target = u * prefix_total;
+  __shared__ unsigned long long best;
+  if (tid == 0) best = static_cast<unsigned long long>(prefix - 1);
+  __syncthreads();
+  unsigned long long mine = static_cast<unsigned long long>(prefix - 1);
+  for (int i = tid; i < prefix; i += kSortThreads)
+    if (target < cum[i]) { mine = static_cast<unsigned long long>(i); break; }
+  atomicMin(&best, mine);
+  __syncthreads();
+  if (tid == 0) out_ids[row] = key_index(sorted[best]);
+}
+
 int64_t padded_width(int64_t width) {
   int64_t p = 1;
   while (p < width) p <<= 1;
@@ -572,12 +835,12 @@ int64_t padded_width(int64_t width) {
 
 }  // namespace
 
-// per row: padded keys (8 B each), padded running sums (4 B each), the candidates / survivors of the top-k
-// paths, a histogram and the two small state records; one flag for the whole call
+// per row: padded keys (8 B each), padded running sums (4 B each), the candidates of the top-k / top-p paths, the
+// tail buckets of the top-p path and three small records; one flag for the whole call
 size_t sampler_workspace_bytes(int64_t rows, int64_t width) {
   const int64_t padded = padded_width(width);
-  const size_t per_row = size_t(padded) * 12 + size_t(kCandidates) * 8 + size_t(kSelectBins) * 4 + sizeof(SelectState) +
-                         sizeof(CutState);
+  const size_t per_row = size_t(padded) * 12 + size_t(kCandidates) * 8 + size_t(3 * kTailBuckets) * 4 + sizeof(CutState) +
+                         sizeof(HeadState) + sizeof(int);
   return (size_t(rows) * per_row + 16 + 255) / 256 * 256;
 }
 
@@ -587,40 +850,27 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
   if (rows == 0) return B2_OK;
   const int64_t padded = padded_width(width);
   auto* keys = static_cast<unsigned long long*>(workspace);
-  auto* candidates = keys + rows * padded;                                   // kCandidates per row (>= kMaxSelectK)
-  auto* state = reinterpret_cast<SelectState*>(candidates + rows * int64_t(kCandidates));
-  auto* running = reinterpret_cast<float*>(state + rows);
-  auto* histograms = reinterpret_cast<unsigned int*>(running + rows * padded);
-  auto* cut = reinterpret_cast<CutState*>(histograms + rows * int64_t(kSelectBins));
-  int* overflow = reinterpret_cast<int*>(cut + rows);
-
-  // thread blocks per row for the passes over a row: enough to fill the GPU over all rows and no more (each block
-  // of the histogram passes clears and flushes a 2048-bin histogram, and an unneeded stage of the fallback should
-  // cost one short wave of empty blocks)
+  auto* candidates = keys + rows * padded;                                   // kCandidates per row
+  auto* running = reinterpret_cast<float*>(candidates + rows * int64_t(kCandidates));
+  auto* tails = reinterpret_cast<unsigned int*>(running + rows * padded);
+  auto* heads = reinterpret_cast<HeadState*>(tails + rows * int64_t(3 * kTailBuckets));
+  auto* cut = reinterpret_cast<CutState*>(heads + rows);
+  int* row_flags = reinterpret_cast<int*>(cut + rows);
+  int* overflow = row_flags + rows;
+  // thread blocks per row for a pass over the logits: enough to fill the GPU over all rows and no more
   int64_t spread64 = (int64_t(sm_count()) * 8 + rows - 1) / rows;
   if (spread64 > padded / 1024) spread64 = padded / 1024;
   if (spread64 < 1) spread64 = 1;
-  const unsigned spread = unsigned(spread64);
-  const dim3 row_grid(spread, unsigned(rows));
-  // the whole-row sort has no empty stages and little per-block overhead: more, smaller blocks
-  const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), unsigned(rows));
-  auto make_keys = [&](const int* only_if) {
-    const dim3 grid = only_if != nullptr ? row_grid : wide_grid;
-    if (dtype == B2_F32)
-      sampler_keys_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
-                                                         temperature, keys, only_if);
-    else
-      sampler_keys_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
-                                                      temperature, keys, only_if);
-  };
+  const dim3 row_grid = dim3(unsigned(spread64), unsigned(rows), 1);
+  // logits / temperature stays a normal number near a threshold only for a moderate temperature (and a moderate
+  // logit there, which the splitter kernel checks)
+  const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
+  const int* only_rows = nullptr;   // the rows the whole-row sort below has to do (null: all of them)
 
   if (top_k > 0 && top_k <= kMaxSelectK && width > kTile) {
-    // only the k largest keys matter: a sampled threshold, one pass over the logits, a small sort ...
-    if (cudaMemsetAsync(histograms, 0, size_t(rows) * (size_t(kSelectBins) * 4 + sizeof(CutState)) + 16, s) != cudaSuccess)
-      return launch_status("sample_rows");
-    // logits / temperature stays a normal number near the threshold only for a moderate temperature (and a
-    // moderate logit there, which the splitter kernel checks)
-    const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
+    // only the k largest keys matter: a sampled threshold, one pass over the logits, a small sort: five launches and
+    // a four-byte clear
+    if (cudaMemsetAsync(overflow, 0, sizeof(int), s) != cudaSuccess) return launch_status("sample_rows");
     // the opt-in is a per-device attribute: set on every call, as the other kernels with large shared memory do
     if (cudaFuncSetAttribute(topk_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) != cudaSuccess) {
       cudaGetLastError();
@@ -629,45 +879,74 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     }
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
-      topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow);
-      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow);
+      topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
     } else {
       const __half* x = static_cast<const __half*>(logits);
-      topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow);
-      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow);
+      topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
     }
     topk_finish_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, top_k, cut, candidates, overflow);
-    // ... unless that could not be trusted: then (and only then) the radix select over all 64 key bits runs
-    make_keys(overflow);
-    select_init_kernel<<<unsigned((rows + 255) / 256), 256, 0, s>>>(state, rows, unsigned(top_k), overflow);
-    const int shifts[kSelectRounds] = {53, 42, 31, 20, 9, 0}, widths[kSelectRounds] = {11, 11, 11, 11, 11, 9};
-    unsigned long long mask_above = 0ull;
-    for (int round = 0; round < kSelectRounds; ++round) {
-      select_histogram_kernel<<<row_grid, 256, 0, s>>>(keys, width, padded, shifts[round], widths[round], mask_above, state,
-                                                      histograms, overflow);
-      select_scan_kernel<<<unsigned(rows), 256, 0, s>>>(shifts[round], widths[round], state, histograms, overflow);
-      mask_above |= ((1ull << widths[round]) - 1ull) << shifts[round];
-    }
-    select_compact_kernel<<<row_grid, 256, 0, s>>>(keys, width, padded, state, candidates, overflow);
-    select_finish_kernel<<<unsigned(rows), kSortThreads, 0, s>>>(keys, padded, top_k, candidates, overflow);
+    // ... unless that could not be trusted: then (and only then) the radix select over all 64 key bits redoes every row
+    if (dtype == B2_F32)
+      topk_exact_kernel<float><<<unsigned(rows), kExactThreads, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
+                                                                        temperature, top_k, keys, overflow);
+    else
+      topk_exact_kernel<__half><<<unsigned(rows), kExactThreads, 0, s>>>(static_cast<const __half*>(logits), width, row_stride,
+                                                                         padded, temperature, top_k, keys, overflow);
   } else {
-    make_keys(nullptr);
+    if (top_k == 0 && top_p < 1.0f && width >= 4 * kCandidates) {
+      // top-p over the whole vocabulary: head sorted, tail summed by buckets; rows that do not fit that scheme raise
+      // their flag and are the only ones the whole-row sort below still works on
+      if (cudaMemsetAsync(row_flags, 0, size_t(rows) * sizeof(int), s) != cudaSuccess) return launch_status("sample_rows");
+      if (cudaFuncSetAttribute(topp_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("sample_rows: cannot reserve shared memory");
+        return B2_ERR_CUDA;
+      }
+      if (dtype == B2_F32) {
+        const float* x = static_cast<const float*>(logits);
+        topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, kHeadTarget, safe, cut, row_flags, 1);
+        topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
+        topp_head_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, cut, candidates, running, tails, heads, row_flags);
+        topp_tail_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
+        topp_finish_kernel<float><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
+                                                                          tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
+      } else {
+        const __half* x = static_cast<const __half*>(logits);
+        topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, kHeadTarget, safe, cut, row_flags, 1);
+        topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
+        topp_head_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, cut, candidates, running, tails, heads, row_flags);
+        topp_tail_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
+        topp_finish_kernel<__half><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
+                                                                           tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
+      }
+      only_rows = row_flags;
+    }
+    // the whole-row sort has little per-block overhead: many small blocks
+    const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), unsigned(rows));
+    if (dtype == B2_F32)
+      sampler_keys_kernel<float><<<wide_grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
+                                                            temperature, keys, only_rows);
+    else
+      sampler_keys_kernel<__half><<<wide_grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
+                                                           temperature, keys, only_rows);
     const int tile = int(padded < kTile ? padded : kTile);
     const dim3 tile_grid(unsigned(padded / tile), unsigned(rows));
     if (tile < kTile) {
-      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile);   // the whole row is one small tile
+      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile, only_rows);   // the whole row is one small tile
     } else {
-      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile);
+      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile, only_rows);
       for (int64_t k = int64_t(kTile) * 2; k <= padded; k <<= 1) {
         int64_t j = k >> 1;
-        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);   // steps j and j/2
-        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j);                         // one step left over
-        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k);
+        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, only_rows);   // steps j and j/2
+        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, only_rows);              // one step left over
+        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k, only_rows);
       }
     }
   }
   sampler_pick_kernel<<<unsigned(rows), kSelectThreads, 0, s>>>(keys, width, padded, top_k, top_p, seed, draw_offsets, running,
-                                                                out_ids);
+                                                                out_ids, only_rows);
   return launch_status("sample_rows");
 }
 

@@ -134,13 +134,13 @@ __device__ __forceinline__ int32_t winner_index(unsigned long long best) {   // 
 }
 constexpr int32_t kInvalidIndex = -1;   // written for rows whose exchange did not complete in time
 
-template <typename T, bool kVec>
-__global__ void __launch_bounds__(kArgThreads)
+template <typename T, bool kVec, int kBlock>
+__global__ void __launch_bounds__(kBlock)
 argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_t row_stride, int64_t chunk, int chunks,
                             int64_t index_base, int32_t* out_ids, unsigned long long* keys, unsigned int* tickets,
                             const __grid_constant__ ExchangeArgs xa) {
-  __shared__ float warp_v[kArgThreads / kWarpSize];
-  __shared__ int warp_i[kArgThreads / kWarpSize];
+  __shared__ float warp_v[kBlock / kWarpSize];
+  __shared__ int warp_i[kBlock / kWarpSize];
   __shared__ unsigned long long row_key;
   __shared__ uint32_t call_epoch;   // read by thread 0 BEFORE it takes the row's ticket: the last row's tail rewrites the stored epoch
   __shared__ int state;   // 0: this row is not finished yet, 1: finished (send its key), 2: and it was the last row
@@ -165,7 +165,7 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
   if (lane == 0) { warp_v[warp] = bv; warp_i[warp] = bi; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int k = 1; k < kArgThreads / kWarpSize; ++k)
+    for (int k = 1; k < kBlock / kWarpSize; ++k)
       if (beats(warp_v[k], warp_i[k], bv, bi)) { bv = warp_v[k]; bi = warp_i[k]; }
     unsigned long long key = bi == kNoIndex ? 0ull : pack_key(bv, uint32_t(index_base + bi));
     bool row_finished = true;
@@ -196,7 +196,9 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
   if (state != 2) return;
   exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
     unsigned long long best = 0ull;
-    for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
+#pragma unroll
+    for (int g = 0; g < kMaxWorld; ++g)
+      if (g < xa.world) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
     out_ids[r] = complete ? winner_index(best) : kInvalidIndex;
   });
 }
@@ -214,7 +216,9 @@ argmax_keys_exchange_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids,
   __syncthreads();   // nobody rewrites the stored epoch (end of the tail) before every thread has read it
   exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
     unsigned long long best = 0ull;
-    for (int g = 0; g < xa.world; ++g) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
+#pragma unroll
+    for (int g = 0; g < kMaxWorld; ++g)
+      if (g < xa.world) { const unsigned long long k = partial_of(g); best = k > best ? k : best; }
     out_ids[r] = complete ? winner_index(best) : kInvalidIndex;
   });
 }
@@ -734,13 +738,18 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
   if (!run_tail) return;
   exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
     float top = -INFINITY;
-    for (int g = 0; g < xa.world; ++g) top = fmaxf(top, __uint_as_float(uint32_t(partial_of(g))));
+#pragma unroll
+    for (int g = 0; g < kMaxWorld; ++g)
+      if (g < xa.world) top = fmaxf(top, __uint_as_float(uint32_t(partial_of(g))));
     const float top2 = top * kLog2e;
     float total = 0.0f;                             // rank order: the same sum on every GPU
-    for (int g = 0; g < xa.world; ++g) {
-      const unsigned long long p = partial_of(g);
-      const float pm = __uint_as_float(uint32_t(p)), ps = __uint_as_float(uint32_t(p >> 32));
-      if (pm != -INFINITY) total += ps * fast_exp2(fmaf(pm, kLog2e, -top2));
+#pragma unroll
+    for (int g = 0; g < kMaxWorld; ++g) {
+      if (g < xa.world) {
+        const unsigned long long p = partial_of(g);
+        const float pm = __uint_as_float(uint32_t(p)), ps = __uint_as_float(uint32_t(p >> 32));
+        if (pm != -INFINITY) total += ps * fast_exp2(fmaf(pm, kLog2e, -top2));
+      }
     }
     const float invalid = __int_as_float(0x7fc00000);   // a row whose exchange did not complete in time: NaN statistics
     global_max[r] = complete ? top : invalid;
@@ -1071,6 +1080,21 @@ int launch_argmax_exchange_typed(const void* logits_, int64_t rows, int64_t widt
                                  int32_t* out_ids, void* workspace, const ExchangeArgs& xa, cudaStream_t s) {
   const T* logits = static_cast<const T*>(logits_);
   constexpr int N = Elem<T>::kPerVec;
+  auto* keys = static_cast<unsigned long long*>(workspace);
+  auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
+  const bool vec = rows_vector_ok<T>(logits, row_stride);
+  // A shard of the vocabulary is short (19 k columns at eight GPUs): with enough rows to occupy the GPU, one
+  // 1024-thread block per row fetches the whole row in one or two rounds of loads and needs no key merge, no
+  // ticket and no fence -- the three dependent trips to L2 that otherwise end every block cost more than the row.
+  if (rows >= sm_count() / 2 && width <= int64_t(1024) * 16 * N) {
+    if (vec)
+      argmax_rows_exchange_kernel<T, true, 1024><<<unsigned(rows), 1024, 0, s>>>(logits, rows, width, row_stride, width, 1, index_base,
+                                                                               out_ids, keys, tickets, xa);
+    else
+      argmax_rows_exchange_kernel<T, false, 1024><<<unsigned(rows), 1024, 0, s>>>(logits, rows, width, row_stride, width, 1,
+                                                                                index_base, out_ids, keys, tickets, xa);
+    return launch_status("argmax_rows_sharded");
+  }
   const int64_t target = int64_t(sm_count()) * 8;
   int64_t chunks = target / rows;
   const int64_t most = (width + kMinChunk - 1) / kMinChunk;
@@ -1079,15 +1103,13 @@ int launch_argmax_exchange_typed(const void* logits_, int64_t rows, int64_t widt
   int64_t chunk = (width + chunks - 1) / chunks;
   chunk = (chunk + 4 * N - 1) / (4 * N) * (4 * N);  // chunk starts stay 16-byte aligned
   chunks = (width + chunk - 1) / chunk;
-  auto* keys = static_cast<unsigned long long*>(workspace);
-  auto* tickets = reinterpret_cast<unsigned int*>(keys + rows);
   const unsigned grid = unsigned(rows * chunks);
-  if (rows_vector_ok<T>(logits, row_stride))
-    argmax_rows_exchange_kernel<T, true><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk, int(chunks),
-                                                                     index_base, out_ids, keys, tickets, xa);
+  if (vec)
+    argmax_rows_exchange_kernel<T, true, kArgThreads><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk, int(chunks),
+                                                                                  index_base, out_ids, keys, tickets, xa);
   else
-    argmax_rows_exchange_kernel<T, false><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk, int(chunks),
-                                                                      index_base, out_ids, keys, tickets, xa);
+    argmax_rows_exchange_kernel<T, false, kArgThreads><<<grid, kArgThreads, 0, s>>>(logits, rows, width, row_stride, chunk,
+                                                                                   int(chunks), index_base, out_ids, keys, tickets, xa);
   return launch_status("argmax_rows_sharded");
 }
 

@@ -60,10 +60,12 @@ _SIGNATURES = {
     "b2_add_rms_norm": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _i, _i, _p]),
     "b2_add": (_i, [_p, _p, _p, _i64, _i, _p]),
     "b2_swiglu": (_i, [_p, _p, _p, _i64, _i, _i, _p]),
-    "b2_rope": (_i, [_p, _p, _p, _i64, _i64, _i64, _f, _i, _i, _p]),
-    "b2_rope_batched": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
-    "b2_qk_norm_rope": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _f, _i, _p]),
+    "b2_rope": (_i, [_p, _p, _p, _i64, _i64, _i64, _f, _i, _i, _p, _p]),
+    "b2_rope_batched": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _p]),
+    "b2_qk_norm_rope": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _f, _i, _p, _p]),
     "b2_bulk_copy_timeouts": (_i, [C.POINTER(C.c_uint32)]),
+    "b2_set_programmatic_launch": (None, [_i]),
+    "b2_get_programmatic_launch": (_i, []),
     "b2_embedding_gather": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p, _p]),
     "b2_argmax_workspace_bytes": (_sz, [_i64]),
     "b2_argmax_workspace_init": (_i, [_p, _i64, _p]),

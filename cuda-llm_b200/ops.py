@@ -169,15 +169,35 @@ def cuda_swiglu(gate, up, mode: Optional[str] = None):
 
 # ---------------------------------------------------------------- rotary embedding
 
+_rope_status_words = {}
+
+
+def rope_status_word(device) -> torch.Tensor:
+    """The int32 device word that the rotary-embedding calls of this module hand to the C ABI as `status` (one per
+    device, created zeroed).  Bit 0 set: a bounded wait inside a kernel ran out and some call's output is incomplete."""
+    key = torch.device(device).index
+    w = _rope_status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _rope_status_words[key] = w
+    return w
+
+
+def rope_status(device) -> int:
+    """Blocking read of rope_status_word(device): 0 in a healthy run."""
+    return int(rope_status_word(device).item())
+
+
 def _rope_call(x, positions, theta, out, mode, batched_seq=None):
     m = _mode() if mode is None else {"fast": 0, "deterministic": 1}[mode]
     L = _lib.load()
+    status = rope_status_word(x.device).data_ptr()
     if batched_seq is None:
         t, h, d = x.shape
-        _lib.check(L.b2_rope(_ptr(x), _ptr(positions), _ptr(out), t, h, d, theta, _code(x), m, _stream()))
+        _lib.check(L.b2_rope(_ptr(x), _ptr(positions), _ptr(out), t, h, d, theta, _code(x), m, status, _stream()))
     else:
         b, s, h, d = x.shape
-        _lib.check(L.b2_rope_batched(_ptr(x), _ptr(positions), _ptr(out), b, s, h, d, theta, _code(x), m, _stream()))
+        _lib.check(L.b2_rope_batched(_ptr(x), _ptr(positions), _ptr(out), b, s, h, d, theta, _code(x), m, status, _stream()))
 
 
 def cuda_rope(x, positions: Sequence[int], theta: float, mode: Optional[str] = None):
@@ -262,7 +282,7 @@ def qk_norm_rope_out(q, k, q_weight, k_weight, positions_device, eps: float, the
     t, hq, d = q.shape
     _lib.check(_lib.load().b2_qk_norm_rope(_ptr(q), _ptr(k), _ptr(q_weight), _ptr(k_weight), _ptr(positions_device),
                                            _ptr(q_out), _ptr(k_out), t, hq, k_heads, d, eps, theta, _code(q),
-                                           _stream()))
+                                           rope_status_word(q.device).data_ptr(), _stream()))
 
 
 # ---------------------------------------------------------------- embedding gather

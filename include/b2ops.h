@@ -93,24 +93,39 @@ B2_API int b2_add(const void* a, const void* b, void* out, int64_t count, int dt
 B2_API int b2_swiglu(const void* gate, const void* up, void* out, int64_t count, int dtype, int mode,
                      b2_stream stream);
 
+/* ---- launch pacing ------------------------------------------------------------ */
+
+/* Programmatic dependent launch for the calling thread's later calls (off by default).  When on, the short
+ * operators of a decode step (RMSNorm family, add, SwiGLU, RoPE family, paged-KV writes, gather) are launched
+ * with the "programmatic stream serialization" attribute: each may be scheduled while the kernel before it on
+ * the stream is still running and waits, on the device, for that kernel's completion before it touches memory.
+ * Results are unchanged; what shrinks is the idle gap between two launches, which at one to a few dozen token
+ * rows is as long as the kernels themselves.  The same launches are valid inside stream capture.  No reference
+ * counterpart (the reference launches every kernel fully serialised). */
+B2_API void b2_set_programmatic_launch(int enabled);
+B2_API int b2_get_programmatic_launch(void);
+
 /* ---- rotary embedding (NeoX rotate-half) ----------------------------------- */
 
 /* x, out: [tokens, heads, head_dim]; positions: int32[tokens], one per token row.
  * Pairs (i, i + head_dim/2) are rotated by angle positions[t] * theta^(-2i/head_dim).
  * head_dim must be even, theta > 0.
+ * status (here and in the two entry points below): NULL, or a device (or mapped host) int32 into which
+ * bit 0 is OR-ed if one of the kernel's bounded waits on an on-chip bulk copy ran out -- never expected;
+ * the call still returns normally, but some tokens of its output were not written.
  * Replaces cuda_rope (after its host->device copy of the positions),
  * cuda_rope_batched_positions_out and cuda_rope_token_positions_out, kernels ropek<T>
  * and rope_decode_batched_kernel<T> (include/llm/ops_cuda.h:80,126-131;
  * src/ops_cuda.cu:133,135,707,972-990,1083-1102). */
 B2_API int b2_rope(const void* x, const int32_t* positions, void* out, int64_t tokens, int64_t heads,
-                   int64_t head_dim, float theta, int dtype, int mode, b2_stream stream);
+                   int64_t head_dim, float theta, int dtype, int mode, int32_t* status, b2_stream stream);
 
 /* x, out: [batch, seq, heads, head_dim]; positions: int32[seq], shared by every
  * batch entry.  Replaces cuda_rope_batched / cuda_rope_batched_out and kernel
  * rope_batched_kernel<T> (include/llm/ops_cuda.h:81,123-125; src/ops_cuda.cu:134,708-709). */
 B2_API int b2_rope_batched(const void* x, const int32_t* positions, void* out, int64_t batch,
                            int64_t seq, int64_t heads, int64_t head_dim, float theta, int dtype,
-                           int mode, b2_stream stream);
+                           int mode, int32_t* status, b2_stream stream);
 
 /* Fused per-head RMSNorm + RoPE for the query and key projections of one layer:
  * q [tokens, q_heads, head_dim] with q_weight[head_dim], k [tokens, k_heads,
@@ -122,12 +137,12 @@ B2_API int b2_rope_batched(const void* x, const int32_t* positions, void* out, i
 B2_API int b2_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
                            const int32_t* positions, void* q_out, void* k_out, int64_t tokens,
                            int64_t q_heads, int64_t k_heads, int64_t head_dim, float eps, float theta,
-                           int dtype, b2_stream stream);
+                           int dtype, int32_t* status, b2_stream stream);
 
 /* Health check for the kernels that stage rows through on-chip bulk copies: every wait on such a
  * copy is bounded, and *count (host memory) receives how many waits have run out on the current
  * device since the library was loaded.  0 in a healthy run; anything else means outputs of some
- * earlier b2_rope / b2_qk_norm_rope call are invalid.  Blocking (it copies a device counter to
+ * earlier b2_rope / b2_qk_norm_rope call are invalid (the status argument of those calls says which).  Blocking (it copies a device counter to
  * the host).  No reference counterpart. */
 B2_API int b2_bulk_copy_timeouts(uint32_t* count);
 
@@ -291,7 +306,8 @@ B2_API int b2_paged_kv_prefill_copy(const void* key, const void* value, void* st
  *   (decode batch: tokens_per_table = 1, slot_positions = positions; one packed sequence: tokens_per_table =
  *   tokens, slot_positions = NULL).
  * Results are bit-identical to b2_qk_norm_rope followed by b2_paged_kv_write_*.  Bad block ids or positions:
- * that token's K/V are skipped and bit 0 of *status is raised.  Returns B2_ERR_UNSUPPORTED for head sizes or
+ * that token's K/V are skipped and bit 0 of *status is raised; bit 1 says that a bounded wait on a bulk copy ran
+ * out (never expected) and some tokens were not written.  Returns B2_ERR_UNSUPPORTED for head sizes or
  * alignments that only the scalar kernels take (use the separate calls then).  Fast mode only. */
 B2_API int b2_qk_norm_rope_paged(const void* q, const void* k, const void* v, const void* q_weight,
                                  const void* k_weight, const int32_t* positions, void* q_out, void* storage,

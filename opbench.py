@@ -32,9 +32,9 @@ def _peak():
         return 6650.0
 
 
-def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, only=None, reps_scale=1.0):
+def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, only=None, reps_scale=1.0, sampler_rows=256):
     """only: substring selecting one group of entries ("add_rms_norm", "headline_shape", "qk_norm_rope",
-    "swiglu", "gather", "argmax", "softmax", "sampler", "kvmove", "lm_head"); reps_scale shortens the runs for profiler captures."""
+    "swiglu", "gather", "argmax", "softmax", "sampler", "kvmove", "lm_head", "decode_chain"); reps_scale shortens the runs for profiler captures."""
     from cuda_llm_b200 import sharded
 
     def want(group):
@@ -134,7 +134,9 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
             record("device copy (library kernel, yardstick only)", label, 2 * nbytes, ms)
             del bufs
     if world == 1 and (want("sampler") or want("kvmove")):
-        _next_rows(L, lib, dev, s, timed, record, randn, want, nreps)
+        _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows)
+    if world == 1 and want("decode_chain"):
+        _decode_chain(L, lib, dev, stream, timed, table)
     if world == 1 and want("lm_head"):
         _lm_head(L, lib, dev, s, timed, record, randn, nreps)
         _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps)
@@ -208,6 +210,50 @@ def _lm_head(L, lib, dev, s, timed, record, randn, nreps):
         del tables
 
 
+def _decode_chain(L, lib, dev, stream, timed, table):
+    """The launch-paced regime: the in-scope operators of ONE decoder layer of a decode step, back to back on one
+    stream, Qwen3-0.6B shapes, fp16 -- residual add + norm, QK-norm + RoPE (one launch for the reference's four),
+    residual add + norm, SwiGLU, residual add: five launches where the reference's layer makes eight
+    (src/qwen3_layer_cuda.cu:285-292,319-325).  The projections and the attention between them are not on this path.
+    Microseconds per chain, launched call by call or replayed from a CUDA graph, with and without programmatic
+    dependent launch (b2_set_programmatic_launch)."""
+    s = stream.cuda_stream
+    half = torch.float16
+    F16, FAST = lib.F16, lib.FAST
+    for tokens in (1, 4, 64):
+        z = lambda *shape: torch.zeros(*shape, device=dev, dtype=half)
+        x, r, g, res, nrm, out = z(tokens, 1024), z(tokens, 1024), torch.ones(1024, device=dev, dtype=half), z(tokens, 1024), z(tokens, 1024), z(tokens, 1024)
+        q, k, g128, qo, ko = z(tokens, 16, 128), z(tokens, 8, 128), torch.ones(128, device=dev, dtype=half), z(tokens, 16, 128), z(tokens, 8, 128)
+        gate, up, act = z(tokens, 3072), z(tokens, 3072), z(tokens, 3072)
+        pos = torch.zeros(tokens, dtype=torch.int32, device=dev)
+        p = lambda t: t.data_ptr()
+
+        def chain():
+            lib.check(L.b2_add_rms_norm(p(x), p(r), p(g), p(res), p(nrm), tokens, 1024, 1e-6, F16, FAST, s))
+            lib.check(L.b2_qk_norm_rope(p(q), p(k), p(g128), p(g128), p(pos), p(qo), p(ko), tokens, 16, 8, 128, 1e-6, 1e6, F16, None, s))
+            lib.check(L.b2_add_rms_norm(p(res), p(nrm), p(g), p(x), p(r), tokens, 1024, 1e-6, F16, FAST, s))
+            lib.check(L.b2_swiglu(p(gate), p(up), p(act), tokens * 3072, F16, FAST, s))
+            lib.check(L.b2_add(p(x), p(r), p(out), tokens * 1024, F16, s))
+        entry = {"op": "decode layer chain of the in-scope operators (5 launches)", "shape": f"{tokens} tokens, hidden 1024, 16+8 heads x 128, I=3072 f16"}
+        for pdl in (0, 1):
+            L.b2_set_programmatic_launch(pdl)
+            try:
+                tag = "_pdl" if pdl else ""
+                entry["us_eager" + tag] = round(timed([chain], 200, warm=10) * 1e3, 2)
+                K = 20
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for _ in range(K):
+                        chain()
+                entry["us_graph_replay" + tag] = round(timed([graph.replay], 20) / K * 1e3, 2)
+                del graph
+            except Exception as exc:
+                entry["error" + ("_pdl" if pdl else "")] = str(exc)[:160]
+            finally:
+                L.b2_set_programmatic_launch(0)
+        table.append(entry)
+
+
 def _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps):
     """The LM head at the other hidden sizes of the configurations (2048, 4096), fp16: one table each (622 MB / 1.24 GB > L2)."""
     ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
@@ -223,11 +269,11 @@ def _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps):
         del table
 
 
-def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
+def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows=256):
     """The callers either side of the path: sampling over the LM-head logits, paged-KV row writes, last-valid-row gather."""
     F16, F32 = lib.F16, lib.F32
     if want("sampler"):
-        R = 256
+        R = sampler_rows
         logits = [randn(R, VOCAB, sigma=4.0, dtype=torch.float32) for _ in range(2)]
         ids = torch.empty(R, dtype=torch.int32, device=dev)
         offs = torch.arange(R, dtype=torch.int64, device=dev)
@@ -281,7 +327,7 @@ def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps):
 
         def separate():
             lib.check(L.b2_qk_norm_rope(q.data_ptr(), kk.data_ptr(), g.data_ptr(), g.data_ptr(), rpos.data_ptr(), qo.data_ptr(),
-                                        ko.data_ptr(), Tq, 16, kv_heads, head_dim, 1e-6, 1e6, F16, s))
+                                        ko.data_ptr(), Tq, 16, kv_heads, head_dim, 1e-6, 1e6, F16, None, s))
             lib.check(L.b2_paged_kv_prefill_copy(ko.data_ptr(), vv.data_ptr(), storage.data_ptr(), table.data_ptr(), Tq,
                                                  table.numel(), 1, layers, total_blocks, block_size, kv_heads, head_dim, F16, None, s))
         ms = timed([separate], nreps(40))
@@ -308,7 +354,16 @@ def _headline_shape_ops(L, lib, dev, s, timed, record, randn, nreps):
     record("rms_norm", f"{rows}x{hidden} f16", 2 * rows * hidden * 2 + 2 * hidden, ms, rows)
     ms = timed([lambda: lib.check(L.b2_add(a.data_ptr(), b_.data_ptr(), o.data_ptr(), rows * hidden, F16, s))], nreps(20))
     record("add", f"{rows}x{hidden} f16", 3 * rows * hidden * 2, ms, rows)
-    del a, b_, o
+    ms = timed([lambda: lib.check(L.b2_swiglu(a.data_ptr(), b_.data_ptr(), o.data_ptr(), rows * hidden, F16, FAST, s))], nreps(20))
+    record("swiglu", f"{rows}x{hidden} f16", 3 * rows * hidden * 2, ms, rows)
+    # the deterministic (reference-order) form of the fused add + norm: one warp per row, fp64 index-order sum
+    o2 = torch.empty_like(o)
+    small = 4096
+    ms = timed([lambda: lib.check(L.b2_add_rms_norm(a.data_ptr(), b_.data_ptr(), g.data_ptr(), o.data_ptr(), o2.data_ptr(), small,
+                                                    hidden, 1e-6, F16, lib.DETERMINISTIC, s))], nreps(20))
+    record("add_rms_norm, deterministic (fp64 sum in index order)", f"{small}x{hidden} f16", 4 * small * hidden * 2 + 2 * hidden, ms, small,
+           note="133 MB working set: L2-assisted")
+    del a, b_, o, o2
 
 
 
@@ -329,15 +384,15 @@ def _config3(L, lib, dev, s, timed, record, randn, sets_for, nreps):
              torch.empty(T, HQ, D, device=dev, dtype=half), torch.empty(T, HK, D, device=dev, dtype=half)) for i in range(n)]
     calls = [(lambda b=b: lib.check(L.b2_qk_norm_rope(b[0].data_ptr(), b[1].data_ptr(), gq.data_ptr(), gk.data_ptr(),
                                                        pos.data_ptr(), b[2].data_ptr(), b[3].data_ptr(), T, HQ, HK, D,
-                                                       1e-6, 1e6, F16, s))) for b in bufs]
+                                                       1e-6, 1e6, F16, None, s))) for b in bufs]
     ms = timed(calls, nreps(40))
     record("qk_norm_rope (fused)", f"T={T} {HQ}+{HK} heads x {D} f16", per_set + 4 * T + 512, ms, T)
 
     def unfused(b):
         lib.check(L.b2_rms_norm(b[0].data_ptr(), gq.data_ptr(), b[2].data_ptr(), T * HQ, D, 1e-6, F16, FAST, s))
         lib.check(L.b2_rms_norm(b[1].data_ptr(), gk.data_ptr(), b[3].data_ptr(), T * HK, D, 1e-6, F16, FAST, s))
-        lib.check(L.b2_rope(b[2].data_ptr(), pos.data_ptr(), b[2].data_ptr(), T, HQ, D, 1e6, F16, FAST, s))
-        lib.check(L.b2_rope(b[3].data_ptr(), pos.data_ptr(), b[3].data_ptr(), T, HK, D, 1e6, F16, FAST, s))
+        lib.check(L.b2_rope(b[2].data_ptr(), pos.data_ptr(), b[2].data_ptr(), T, HQ, D, 1e6, F16, FAST, None, s))
+        lib.check(L.b2_rope(b[3].data_ptr(), pos.data_ptr(), b[3].data_ptr(), T, HK, D, 1e6, F16, FAST, None, s))
     ms = timed([(lambda b=b: unfused(b)) for b in bufs], nreps(40))
     record("rms_norm x2 + rope x2 (reference-shaped)", f"T={T} {HQ}+{HK} heads x {D} f16", 2 * per_set + 8 * T + 1024, ms, T,
            note="four launches; bytes counted per launch sequence")
@@ -452,6 +507,19 @@ def _config5(L, lib, dev, s, timed, record, randn, sets_for, sharded, world, ran
                                                                 FAST, sws.data_ptr(), s))) for i, x in enumerate(logits)]
         ms = timed(calls, nreps(40))
         record("softmax_rows", f"{R}x{VOCAB} f32", 2 * per_set, ms, R)
+        # the kernels of the vocabulary-sharded forms with a world of one GPU (the exchange is with itself): what their
+        # local part costs beside the plain kernels above
+        ex = sharded.PeerExchange(max_rows=R)
+        try:
+            stats1 = torch.empty(2, R, dtype=torch.float32, device=dev)
+            ms = timed([(lambda x=x: sharded.sharded_argmax_fused(x, 0, ex, out=ids_out)) for x in logits], nreps(40))
+            record("argmax (exchange fused into the kernel), world of one GPU", f"{R}x{VOCAB} f32", per_set + 4 * R, ms, R)
+            ms = timed([(lambda x=x, i=i: sharded.sharded_softmax_fused(x, ex, out=outs[i % len(outs)], stats=stats1))
+                        for i, x in enumerate(logits)], nreps(40))
+            record("softmax (statistics kernel with the exchange, then apply), world of one GPU", f"{R}x{VOCAB} f32", 3 * per_set, ms, R,
+                   note="two passes over the logits (the second from L2 where it fits): bytes counted as read twice, written once")
+        finally:
+            ex.close()
     else:
         # the yardstick of the sharded forms, in the same run: the whole vocabulary on one GPU (every rank alike, no exchange)
         full = [randn(R, VOCAB, sigma=4.0, dtype=torch.float32) for _ in range(4)]
@@ -571,6 +639,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--reps-scale", type=float, default=1.0)
+    ap.add_argument("--sampler-rows", type=int, default=256, help="rows of the sampler entries (profiler captures use a few)")
     args = ap.parse_args()
     build.build()
     L = lib.load()
@@ -578,7 +647,7 @@ def main():
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         rows = run(L, lib, dev, stream, 1, 0, torch.cuda.synchronize, lambda ms: ms, only=args.only,
-                   reps_scale=args.reps_scale)
+                   reps_scale=args.reps_scale, sampler_rows=args.sampler_rows)
     for e in rows:
         print(json.dumps(e))
 

@@ -360,6 +360,8 @@ class RefCuda:
         for name in ("refcu_time_add_rms_norm", "refcu_time_rms_norm", "refcu_time_binary", "refcu_time_rope_token_positions",
                      "refcu_time_embedding", "refcu_time_softmax", "refcu_time_argmax_last_row", "refcu_time_sample_row"):
             getattr(L, name).restype = C.c_float
+        if hasattr(L, "refcu_time_decode_chain"):      # absent from a library built before this door existed
+            L.refcu_time_decode_chain.restype = C.c_float
 
     @staticmethod
     def _p(t):
@@ -444,6 +446,10 @@ class RefCuda:
     def time_rope_token_positions(self, x, positions_device, tokens, heads, theta, reps):
         return float(self.lib.refcu_time_rope_token_positions(self._p(x), self._p(positions_device), C.c_int64(tokens),
                                                               C.c_int64(heads), C.c_float(theta), C.c_int(reps)))
+
+    def time_decode_chain(self, tokens, eps, theta, graph, reps):
+        """ms per chain of the reference's in-scope operators of one decode layer (see refcu_time_decode_chain)."""
+        return float(self.lib.refcu_time_decode_chain(C.c_int64(tokens), C.c_float(eps), C.c_float(theta), C.c_int(graph), C.c_int(reps)))
 
     def time_embedding(self, table, ids_device, count, hidden, vocab, dtype, reps):
         return float(self.lib.refcu_time_embedding(self._p(table), self._p(ids_device), C.c_int64(count), C.c_int64(hidden),

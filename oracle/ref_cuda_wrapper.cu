@@ -176,6 +176,55 @@ REFCU_API float refcu_time_rope_token_positions(const void* x, const int32_t* po
   });
   return ms;
 }
+// The in-scope operators of one decoder layer of a decode step, in the order the reference's layer launches them
+// (src/qwen3_layer_cuda.cu:285-292,319-325): add + norm, the two per-head norms, the two rotary embeddings, add + norm,
+// SwiGLU, add; Qwen3-0.6B shapes (hidden 1024, 16 + 8 heads of 128, intermediate 3072), fp16, `tokens` rows.  The
+// projections and the attention between them are left out (not on this path), so the operators run back to back.
+// graph != 0: the chain is captured once into a CUDA graph and the replays are timed.  Milliseconds per chain.
+REFCU_API float refcu_time_decode_chain(int64_t tokens, float eps, float theta, int graph, int reps) {
+  float ms = -1;
+  guarded([&] {
+    const DType d = DType::F16;
+    auto zeros = [&](std::vector<int64_t> shape) {
+      Tensor t(d, std::move(shape), DeviceType::CUDA);
+      CUDA_CHECK(cudaMemset(t.data(), 0, t.nbytes()));
+      return t;
+    };
+    Tensor x = zeros({tokens, 1024}), r = zeros({tokens, 1024}), g = zeros({1024}), res = zeros({tokens, 1024}), nrm = zeros({tokens, 1024});
+    Tensor q = zeros({tokens, 16, 128}), k = zeros({tokens, 8, 128}), g128 = zeros({128}), qn = zeros({tokens, 16, 128}),
+           kn = zeros({tokens, 8, 128}), qo = zeros({tokens, 16, 128}), ko = zeros({tokens, 8, 128});
+    Tensor gate = zeros({tokens, 3072}), up = zeros({tokens, 3072}), act = zeros({tokens, 3072}), out = zeros({tokens, 1024});
+    Tensor pos(DType::I32, {tokens}, DeviceType::CUDA);
+    CUDA_CHECK(cudaMemset(pos.data(), 0, size_t(tokens) * 4));
+    cudaStream_t s = cudaStreamPerThread;
+    auto chain = [&] {
+      llm::cuda_add_rms_norm_out(x, r, g, eps, res, nrm, s);
+      llm::cuda_rms_norm_out(q, g128, eps, qn, s);
+      llm::cuda_rms_norm_out(k, g128, eps, kn, s);
+      llm::cuda_rope_token_positions_out(qn, pos, theta, qo, s);
+      llm::cuda_rope_token_positions_out(kn, pos, theta, ko, s);
+      llm::cuda_add_rms_norm_out(res, nrm, g, eps, x, r, s);
+      llm::cuda_swiglu_out(gate, up, act, s);
+      llm::cuda_add_out(x, r, out, s);
+    };
+    if (!graph) {
+      ms = timed(chain, reps);
+    } else {
+      chain();
+      CUDA_CHECK(cudaDeviceSynchronize());
+      cudaGraph_t captured;
+      cudaGraphExec_t exec;
+      CUDA_CHECK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+      chain();
+      CUDA_CHECK(cudaStreamEndCapture(s, &captured));
+      CUDA_CHECK(cudaGraphInstantiate(&exec, captured, 0));
+      ms = timed([&] { CUDA_CHECK(cudaGraphLaunch(exec, s)); }, reps);
+      cudaGraphExecDestroy(exec);
+      cudaGraphDestroy(captured);
+    }
+  });
+  return ms;
+}
 REFCU_API float refcu_time_embedding(const void* table, const int32_t* ids_device, int64_t count, int64_t hidden, int64_t vocab,
                                      int dtype, int reps) {
   float ms = -1;

@@ -35,10 +35,10 @@ def test_validation_happens_before_any_launch(b2):
         b2.b2_add_rms_norm(p, p, p, p, p, 4, 8, 1e-6, lib.F16, lib.FAST, None),  # residual == normalized
         b2.b2_add(p, p, None, 4, lib.F32, None),
         b2.b2_swiglu(p, p, p, -3, lib.F32, lib.FAST, None),
-        b2.b2_rope(p, p, p, 2, 1, 3, 1e4, lib.F32, lib.FAST, None),             # odd head_dim
-        b2.b2_rope(p, p, p, 2, 1, 4, 0.0, lib.F32, lib.FAST, None),             # theta
-        b2.b2_rope_batched(p, p, p, 2, 0, 1, 4, 1e4, lib.F32, lib.FAST, None),  # seq
-        b2.b2_qk_norm_rope(p, None, p, None, p, p, None, 2, 16, 8, 128, 1e-6, 1e6, lib.F16, None),  # k missing
+        b2.b2_rope(p, p, p, 2, 1, 3, 1e4, lib.F32, lib.FAST, None, None),             # odd head_dim
+        b2.b2_rope(p, p, p, 2, 1, 4, 0.0, lib.F32, lib.FAST, None, None),             # theta
+        b2.b2_rope_batched(p, p, p, 2, 0, 1, 4, 1e4, lib.F32, lib.FAST, None, None),  # seq
+        b2.b2_qk_norm_rope(p, None, p, None, p, p, None, 2, 16, 8, 128, 1e-6, 1e6, lib.F16, None, None),  # k missing
         b2.b2_embedding_gather(p, p, p, 4, 8, 0, lib.F16, None, None),          # vocab
         b2.b2_argmax_rows(p, 2, 8, 4, lib.F32, p, p, None),                     # stride < width
         b2.b2_argmax_keys(p, 2, 8, 8, lib.F32, 2 ** 32, p, p, None),            # index does not fit 32 bits

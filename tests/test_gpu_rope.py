@@ -197,3 +197,21 @@ def test_no_bulk_copy_wait_ran_out(b2):
     import ctypes
     n = ctypes.c_uint32(12345)
     assert b2.b2_bulk_copy_timeouts(ctypes.byref(n)) == 0 and n.value == 0
+    assert ops.rope_status(DEV) == 0          # the status word every call above was given says the same
+
+
+def test_status_argument_is_optional_and_left_alone_by_a_healthy_call(b2):
+    from cuda_llm_b200 import lib
+    c = wl.config3(tokens=512)
+    q, k = dev(c["q"]), dev(c["k"])
+    gq, gk, pos = dev(c["gamma_q"]), dev(c["gamma_k"]), dev(c["positions"])
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    s = torch.cuda.current_stream().cuda_stream
+    status = torch.full((1,), 8, dtype=torch.int32, device=DEV)     # an unrelated bit that must survive
+    for st in (None, status.data_ptr()):
+        lib.check(b2.b2_qk_norm_rope(q.data_ptr(), k.data_ptr(), gq.data_ptr(), gk.data_ptr(), pos.data_ptr(), qo.data_ptr(),
+                                     ko.data_ptr(), 512, 16, 8, 128, wl.EPS, wl.THETA, lib.F16, st, s))
+        lib.check(b2.b2_rope(q.data_ptr(), pos.data_ptr(), qo.data_ptr(), 512, 16, 128, wl.THETA, lib.F16, lib.FAST, st, s))
+        lib.check(b2.b2_rope_batched(q.data_ptr(), pos.data_ptr(), qo.data_ptr(), 2, 256, 16, 128, wl.THETA, lib.F16, lib.FAST, st, s))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 8
