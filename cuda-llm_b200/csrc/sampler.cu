@@ -9,7 +9,7 @@
 // What changes is how the order and the sums are produced:
 //   keys     one 64-bit key per token, (order-preserving bits of the score) << 32 | ~index, so one
 //            unsigned sort gives the reference's order including its tie rule
-//   sort     when 0 < top_k <= 2048 only the k largest keys matter: a threshold taken from a sorted sample of
+//   sort     when 0 < top_k <= 2048 only the k largest keys matter: a threshold taken from a sample of
 //            the row, ONE pass over the logits that gathers the few hundred tokens above it, and a one-block
 //            sort of those (checked; a call whose sample misled it is redone by a radix select over all 64
 //            key bits, one more launch that otherwise returns at once); otherwise a bitonic network sorts the whole row (keys in registers, 4096-key tiles,
@@ -28,7 +28,7 @@ namespace b2 {
 namespace {
 
 constexpr int kTile = 4096;          // keys per thread block in the shared-memory sorting steps
-constexpr int kSortThreads = 512;    // 8 keys per thread
+constexpr int kSortThreads = 1024;   // small sorts in shared memory: many warps hide the dependent load-compare-store chain
 constexpr int kChunk = 2048;         // tokens per step of the ordered sums
 constexpr int kSelectThreads = 256;
 
@@ -44,17 +44,40 @@ __device__ __forceinline__ float key_score(unsigned long long key) {
 }
 __device__ __forceinline__ int32_t key_index(unsigned long long key) { return int32_t(0xffffffffu - uint32_t(key)); }
 
+// The rows a kernel of the whole-row sort works on.  list == nullptr: every row, one per block of the grid's row
+// dimension.  Otherwise the first *count entries of list (the rows that the top-p path could not settle), dealt over a
+// row dimension of a few blocks: when the list is empty -- the usual case -- such a launch costs a few idle blocks.
+struct RowSet { const int* list; const int* count; };
+__device__ __forceinline__ bool row_of(const RowSet& rs, int64_t it, int64_t grid_rows, int64_t* row) {
+  if (rs.list == nullptr) { *row = it; return it < grid_rows; }
+  if (it >= int64_t(*rs.count)) return false;
+  *row = rs.list[it];
+  return true;
+}
+constexpr int kListedRowBlocks = 4;   // row dimension of a launch over a row list
+
+__global__ void __launch_bounds__(256) list_rows_kernel(const int* row_flags, int rows, int* list, int* count) {
+  __shared__ int n;
+  if (threadIdx.x == 0) n = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < rows; r += 256)
+    if (row_flags[r] != 0) list[atomicAdd(&n, 1)] = r;
+  __syncthreads();
+  if (threadIdx.x == 0) *count = n;
+}
+
 // keys[r][i] for i < padded: the token's key, or 0 (below every real key) in the padding
 template <typename T>
 __global__ void __launch_bounds__(256)
 sampler_keys_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature,
-                    unsigned long long* keys, const int* only_rows) {
-  const int64_t row = blockIdx.y;
-  if (only_rows != nullptr && only_rows[row] == 0) return;   // this row was settled without the whole-row sort
-  const T* src = logits + row * row_stride;
-  unsigned long long* dst = keys + row * padded;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < padded; i += int64_t(gridDim.x) * blockDim.x)
-    dst[i] = i < width ? sample_key(__fdiv_rn(Elem<T>::load(src + i), temperature), uint32_t(i)) : 0ull;
+                    unsigned long long* keys, const RowSet rs) {
+  int64_t row;
+  for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
+    const T* src = logits + row * row_stride;
+    unsigned long long* dst = keys + row * padded;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < padded; i += int64_t(gridDim.x) * blockDim.x)
+      dst[i] = i < width ? sample_key(__fdiv_rn(Elem<T>::load(src + i), temperature), uint32_t(i)) : 0ull;
+  }
 }
 
 // ---- bitonic network, descending.  Element i and its partner i ^ j are put in descending order when
@@ -67,10 +90,10 @@ __device__ __forceinline__ void compare_exchange(unsigned long long& a, unsigned
 // this sorts the tile from scratch; with k_first == k_last it finishes a merge whose wide steps ran in
 // global memory.
 __global__ void __launch_bounds__(kSortThreads)
-bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t k_first, int64_t k_last, const int* only_rows) {
+bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t k_first, int64_t k_last, const RowSet rs) {
   extern __shared__ unsigned long long tile_keys[];
-  const int64_t row = blockIdx.y;
-  if (only_rows != nullptr && only_rows[row] == 0) return;
+  int64_t row;
+  for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
   unsigned long long* base = keys + row * padded + int64_t(blockIdx.x) * tile;
   const int64_t global0 = int64_t(blockIdx.x) * tile;
   for (int i = threadIdx.x; i < tile; i += kSortThreads) tile_keys[i] = base[i];
@@ -86,20 +109,23 @@ bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t 
     }
   }
   for (int i = threadIdx.x; i < tile; i += kSortThreads) base[i] = tile_keys[i];
+  __syncthreads();   // the tile is reused for the block's next row
+  }
 }
 
 // One step with j >= tile: partners sit in different tiles, so it runs in global memory (the keys of a
 // few hundred rows fit the L2).
 __global__ void __launch_bounds__(256)
-bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const int* only_rows) {
-  const int64_t row = blockIdx.y;
-  if (only_rows != nullptr && only_rows[row] == 0) return;
-  unsigned long long* base = keys + row * padded;
-  for (int64_t p = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; p < padded / 2; p += int64_t(gridDim.x) * blockDim.x) {
-    const int64_t i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
-    unsigned long long a = base[i], b = base[i | j];
-    const bool descending = (i & k) == 0;
-    if ((a < b) == descending) { base[i] = b; base[i | j] = a; }
+bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const RowSet rs) {
+  int64_t row;
+  for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
+    unsigned long long* base = keys + row * padded;
+    for (int64_t p = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; p < padded / 2; p += int64_t(gridDim.x) * blockDim.x) {
+      const int64_t i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+      unsigned long long a = base[i], b = base[i | j];
+      const bool descending = (i & k) == 0;
+      if ((a < b) == descending) { base[i] = b; base[i | j] = a; }
+    }
   }
 }
 
@@ -171,10 +197,11 @@ __device__ __forceinline__ void layout_s_to_b(unsigned long long (&key)[kRegKeys
 // k_first == 2: sorts every 4096-key tile from scratch (phases 2 .. 4096).  k_first == k_last > 4096: the steps
 // j = 2048 .. 1 that finish a merge whose wide steps ran in global memory.
 __global__ void __launch_bounds__(kRegThreads)
-bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last, const int* only_rows) {
+bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last, const RowSet rs) {
   __shared__ unsigned long long tile[kTile];
-  const int64_t row = blockIdx.y, tile_global = int64_t(blockIdx.x) * kTile;
-  if (only_rows != nullptr && only_rows[row] == 0) return;
+  const int64_t tile_global = int64_t(blockIdx.x) * kTile;
+  int64_t row;
+  for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
   unsigned long long* base = keys + row * padded + tile_global;
   const int t = threadIdx.x, lane = t & 31;
   const int64_t first_global = tile_global + int64_t(t) * kRegKeys;   // layout B: global index of register 0
@@ -203,14 +230,16 @@ bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t 
   layout_b_to_s(key, tile, t);
 #pragma unroll
   for (int r = 0; r < kRegKeys; ++r) base[r * kRegThreads + t] = key[r];
+  }
 }
 
 // Two wide steps (j and j/2, both >= the tile) in one pass over global memory: the four elements that the two
 // steps connect are loaded once.
 __global__ void __launch_bounds__(256)
-bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const int* only_rows) {
-  const int64_t row = blockIdx.y, h = j >> 1;
-  if (only_rows != nullptr && only_rows[row] == 0) return;
+bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const RowSet rs) {
+  const int64_t h = j >> 1;
+  int64_t row;
+  for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
   unsigned long long* base = keys + row * padded;
   for (int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < padded / 4; q += int64_t(gridDim.x) * blockDim.x) {
     const int64_t i = ((q & ~(h - 1)) << 2) | (q & (h - 1));   // bits j and j/2 clear
@@ -221,6 +250,7 @@ bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, in
     compare_exchange(a0, a1, descending);
     compare_exchange(a2, a3, descending);
     base[i] = a0; base[i + h] = a1; base[i + j] = a2; base[i + j + h] = a3;
+  }
   }
 }
 
@@ -300,8 +330,8 @@ topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t pa
 }
 
 // ---- small top_k, the usual case: ONE pass over the logits and no key array.
-//   splitter  a thread block per row sorts 2048 evenly spaced logits of the row and takes, as threshold, the
-//             sample whose rank makes "about 6 x top_k, and with near certainty at least top_k" tokens of the
+//   splitter  a thread block per row looks at 8192 evenly spaced logits of the row and takes, as threshold, the
+//             sample whose rank makes "a few times top_k, and with near certainty at least top_k" tokens of the
 //             whole row lie above it, lowered by 2^-12 of its magnitude
 //   gather    the one pass: every token whose logit is at or above the threshold has its exact score computed and
 //             its key appended to the row's candidate list (a few hundred of 150k tokens)
@@ -314,7 +344,7 @@ topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t pa
 // their logit is smaller: scores are logits / temperature, a monotonic map with a relative rounding error of
 // 2^-24.  A NaN logit also sends the call to the exact select (whose key order ranks NaNs as the reference's sort does).
 constexpr int kCandidates = 8192;
-constexpr int kSplitSamples = 2048;
+constexpr int kSplitSamples = 8192;   // evenly spaced logits per row from which the threshold is taken
 
 struct CutState {            // per row
   float threshold;           // candidates are the tokens whose logit is >= this
@@ -338,11 +368,20 @@ __device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& 
   if (aligned16(src)) {
     const int64_t nvec = width / N;
     const uint4* vp = reinterpret_cast<const uint4*>(src);
-    for (int64_t v = first; v < nvec; v += stride) {
-      float e[N];
-      Elem<T>::unpack(ld_stream(vp + v), e);
+    for (int64_t v0 = first; v0 < nvec; v0 += stride * 4) {      // four loads in flight per thread
+      uint4 r[4];
 #pragma unroll
-      for (int q = 0; q < N; ++q) f(e[q], v * N + q);
+      for (int k = 0; k < 4; ++k) if (v0 + k * stride < nvec) r[k] = ld_stream(vp + v0 + k * stride);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * stride;
+        if (v < nvec) {
+          float e[N];
+          Elem<T>::unpack(r[k], e);
+#pragma unroll
+          for (int q = 0; q < N; ++q) f(e[q], v * N + q);
+        }
+      }
     }
     for (int64_t i = nvec * N + first; i < width; i += stride) f(Elem<T>::load(src + i), i);
   } else {
@@ -350,37 +389,98 @@ __device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& 
   }
 }
 
+constexpr int kSplitThreads = 1024;
+constexpr int kSamplesPerThread = kSplitSamples / kSplitThreads;
+// The sample of rank `rank` (0 = largest) is found by a radix select over the samples' 32 ordered bits, eight bits
+// a round, instead of sorting them: per round a 256-bin histogram of the samples that still match the digits
+// found so far (votes of a warp for one bin are added by one lane: most samples share the leading digits), then
+// one warp walks the bins from the top.  Every thread keeps its samples in registers.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kSplitThreads)
 topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int top_k, int safe, CutState* cut,
                      int* overflow, int overflow_stride) {   // the flag of row r is overflow[r * overflow_stride]: stride 0 = one flag per call
-  __shared__ uint32_t sample[kSplitSamples];
+  // top_k == 0: no count to reach; the threshold is to leave as many candidates as fit one kTile-key tile with near
+  // certainty (the top-p path's head)
+  __shared__ unsigned int bins[256];
+  __shared__ uint32_t prefix_found;
+  __shared__ int rank_left;
   const int64_t row = blockIdx.x;
   overflow += row * overflow_stride;
   const T* src = logits + row * row_stride;
-  for (int s = threadIdx.x; s < kSplitSamples; s += 256) {
-    const float x = Elem<T>::load(src + (int64_t(s) * width) / kSplitSamples);   // width > kSplitSamples: distinct tokens
-    sample[s] = x == x ? ordered_bits(x) : 0u;                                     // a NaN never ranks
-  }
-  __syncthreads();
-  for (int k = 2; k <= kSplitSamples; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int p = threadIdx.x; p < kSplitSamples / 2; p += 256) {
-        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
-        const uint32_t a = sample[i], b = sample[i | j];
-        if ((a < b) == ((i & k) == 0)) { sample[i] = b; sample[i | j] = a; }
-      }
-      __syncthreads();
+  // as many samples as there are tokens to take them from two apart, at most kSplitSamples
+  int samples = kSplitSamples;
+  while (samples > kSplitThreads && int64_t(samples) * 2 > width) samples >>= 1;
+  uint32_t mine[kSamplesPerThread];
+#pragma unroll
+  for (int q = 0; q < kSamplesPerThread; ++q) {
+    const int sidx = threadIdx.x + q * kSplitThreads;
+    mine[q] = 0u;
+    if (sidx < samples) {
+      const float x = Elem<T>::load(src + (int64_t(sidx) * width) / samples);
+      mine[q] = x == x ? ordered_bits(x) : 0u;                                   // a NaN never ranks
     }
   }
+  // expected rank of the top_k-th token among the samples, plus four standard deviations and two
+  const float expected = float(top_k) * float(samples) / float(width);
+  int rank = int(ceilf(expected + 4.0f * sqrtf(expected))) + 2;
+  if (top_k == 0u) {
+    // the number of tokens above the sample of rank r is about width * r / samples, with a relative spread of
+    // 1 / sqrt(r): the largest r whose count stays within the tile at five and a half spreads (closed form of
+    // r + 5.5 sqrt(r) <= tile * samples / width)
+    const float budget = float(kTile) * float(samples) / float(width);
+    const float root = 0.5f * (sqrtf(30.25f + 4.0f * budget) - 5.5f);
+    rank = int(root * root) - 1;
+    if (rank < 2) rank = 2;
+  }
+  bool ok = safe != 0 && rank < samples;
+  if (threadIdx.x == 0) { prefix_found = 0u; rank_left = ok ? rank : 0; }
+  const int lane = threadIdx.x & 31;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    if (threadIdx.x < 256) bins[threadIdx.x] = 0u;
+    __syncthreads();
+    const uint32_t prefix = prefix_found;
+    const uint32_t above = shift == 24 ? 0u : 0xffffffffu << (shift + 8);     // the digits already fixed
+#pragma unroll
+    for (int q = 0; q < kSamplesPerThread; ++q) {
+      const bool in = threadIdx.x + q * kSplitThreads < samples && (mine[q] & above) == prefix;
+      const unsigned int digit = in ? (mine[q] >> shift) & 255u : 256u;         // 256: not taking part
+      const unsigned int peers = __match_any_sync(0xffffffffu, digit);
+      if (in && lane == __ffs(peers) - 1) atomicAdd(&bins[digit], unsigned(__popc(peers)));
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l owns bins 255 - 8l .. 248 - 8l (descending); a warp scan finds the bin that holds the rank
+      unsigned int own[8], total = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { own[i] = bins[255 - (lane * 8 + i)]; total += own[i]; }
+      unsigned int before = total;
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const unsigned int up = __shfl_up_sync(0xffffffffu, before, offset);
+        if (lane >= offset) before += up;
+      }
+      before -= total;                                                          // samples in the bins above this lane's
+      const unsigned int want = unsigned(rank_left);
+      const bool here = want >= before && want < before + total;
+      __syncwarp();
+      if (here) {
+        unsigned int seen = before;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (want >= seen && want < seen + own[i]) {
+            prefix_found = prefix | (uint32_t(255 - (lane * 8 + i)) << shift);
+            rank_left = int(want - seen);
+          }
+          seen += own[i];
+        }
+      }
+    }
+    __syncthreads();
+  }
   if (threadIdx.x != 0) return;
-  // expected rank of the top_k-th token among the samples, plus three standard deviations and two
-  const float expected = float(top_k) * float(kSplitSamples) / float(width);
-  int rank = int(ceilf(expected + 3.0f * sqrtf(expected))) + 2;
-  bool ok = safe != 0 && rank < kSplitSamples;
   float threshold = -INFINITY;
   if (ok) {
-    const float at_rank = from_ordered_bits(sample[rank]);
+    const float at_rank = from_ordered_bits(prefix_found);
     const unsigned int exponent = (__float_as_uint(at_rank) >> 23) & 0xffu;
     ok = exponent >= 28u && exponent <= 226u;            // 2^-99 .. 2^99: the division stays exact to rounding
     threshold = at_rank - 0.000244140625f * fabsf(at_rank);   // 2^-12 of the magnitude: 4096 rounding errors of the division
@@ -397,16 +497,35 @@ topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
   const int64_t row = blockIdx.y;
   overflow += row * overflow_stride;
   if (*overflow != 0) return;                      // the row (or the call) is being redone by the exact path anyway
+  // candidates are collected in shared memory and appended to the row's list with ONE global atomic per block
+  // (a few thousand candidates per row would otherwise queue on one address); what does not fit goes out directly
+  constexpr int kLocal = 1024;
+  __shared__ unsigned long long local_keys[kLocal];
+  __shared__ unsigned int local_count, base_slot;
+  if (threadIdx.x == 0) local_count = 0u;
+  __syncthreads();
   const float threshold = cut[row].threshold;
   unsigned long long* out = candidates + row * int64_t(kCandidates);
   bool strange = false;
   for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t i) {
     if (x >= threshold) {
-      const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
-      if (slot < unsigned(kCandidates)) out[slot] = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
+      const unsigned long long key = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
+      const unsigned int mine = atomicAdd(&local_count, 1u);
+      if (mine < unsigned(kLocal)) {
+        local_keys[mine] = key;
+      } else {
+        const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
+        if (slot < unsigned(kCandidates)) out[slot] = key;
+      }
     }
     strange |= x != x;
   });
+  __syncthreads();
+  const unsigned int kept = local_count < unsigned(kLocal) ? local_count : unsigned(kLocal);
+  if (threadIdx.x == 0) base_slot = kept != 0u ? atomicAdd(&cut[row].taken, kept) : 0u;
+  __syncthreads();
+  for (unsigned int i = threadIdx.x; i < kept; i += blockDim.x)
+    if (base_slot + i < unsigned(kCandidates)) out[base_slot + i] = local_keys[i];
   if (strange) atomicExch(const_cast<int*>(overflow), 1);
 }
 
@@ -441,6 +560,23 @@ topk_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const Cu
   for (int i = threadIdx.x; i < top_k; i += kSortThreads) dst[i] = buf[i];
 }
 
+// Running sums of stage[0 .. n) in index order, one thread: sum_j = sum_(j-1) + stage[j], written back in place.
+// The additions form one dependent chain (that is the reference's order); the loads and stores around them do not, so
+// they go eight at a time: a loop that loads, adds and stores one element per turn waits for shared memory every turn.
+// stage must be 16-byte aligned.
+__device__ __forceinline__ float running_sums_in_order(float* stage, int n, float sum) {
+  int j = 0;
+  for (; j + 8 <= n; j += 8) {
+    float4 a = *reinterpret_cast<const float4*>(stage + j), b = *reinterpret_cast<const float4*>(stage + j + 4);
+    sum += a.x; a.x = sum; sum += a.y; a.y = sum; sum += a.z; a.z = sum; sum += a.w; a.w = sum;
+    sum += b.x; b.x = sum; sum += b.y; b.y = sum; sum += b.z; b.z = sum; sum += b.w; b.w = sum;
+    *reinterpret_cast<float4*>(stage + j) = a;
+    *reinterpret_cast<float4*>(stage + j + 4) = b;
+  }
+  for (; j < n; ++j) { sum += stage[j]; stage[j] = sum; }
+  return sum;
+}
+
 // ---- the ordered sums and the pick (reference src/ops_cuda.cu:587-617, same operations in the same order)
 __device__ __forceinline__ unsigned long long sampler_hash(unsigned long long x) {
   x += 0x9e3779b97f4a7c15ULL;
@@ -452,12 +588,12 @@ __device__ __forceinline__ unsigned long long sampler_hash(unsigned long long x)
 __global__ void __launch_bounds__(kSelectThreads)
 sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padded, int top_k, float top_p,
                     unsigned long long seed, const unsigned long long* draw_offsets, float* running, int32_t* out_ids,
-                    const int* only_rows) {
+                    const RowSet rs) {
   __shared__ float stage[kChunk];
   __shared__ float carry;
   __shared__ int found;
-  const int64_t row = blockIdx.x;
-  if (only_rows != nullptr && only_rows[row] == 0) return;
+  int64_t row;
+  for (int64_t it = blockIdx.x; row_of(rs, it, gridDim.x, &row); it += gridDim.x) {
   const unsigned long long* sorted = keys + row * padded;
   float* cum = running + row * padded;
   const int64_t limit = top_k == 0 ? width : (int64_t(top_k) < width ? int64_t(top_k) : width);
@@ -537,6 +673,8 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
   atomicMin(&best, mine);
   __syncthreads();
   if (tid == 0) out_ids[row] = key_index(sorted[best]);
+  __syncthreads();   // the shared variables serve the block's next row
+  }
 }
 
 // ---- top_p < 1 over the whole vocabulary without sorting it.
@@ -557,12 +695,11 @@ sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padde
 //           the only place where the order matters: its terms (tens) are gathered, sorted and added one by one in
 //           fp32.  That yields `total` bit for bit.  The top-p walk and the pick then run over the head exactly as
 //           the reference's single thread does.
-// A row that breaks an assumption (fewer than 64 or more than 8192 head candidates, a NaN, the sum growing by more
+// A row that breaks an assumption (fewer than 64 or more than 4096 head candidates, a NaN, the sum growing by more
 // than one power of two in the tail, a bucket of more than 2048 terms, a prefix that does not end inside the head)
 // raises its flag and is redone by the whole-row sort; those kernels are launched in any case and return at once for
 // the rows whose flag is down.
 constexpr int kTailBuckets = 2048;
-constexpr unsigned int kHeadTarget = 2000;     // the splitter's threshold then leaves about 3000 head candidates of 150k tokens
 constexpr int kMinHead = 64;
 
 struct HeadState {          // per row
@@ -583,6 +720,23 @@ __device__ __forceinline__ void term_increment(float e, int k, unsigned int& r, 
   r = (m + (1u << (d - 1))) >> d;
   tie = (m & ((1u << d) - 1u)) == (1u << (d - 1));
 }
+// the same for two sums at once: units 2^(k-23) and 2^(k-22)
+__device__ __forceinline__ void term_increments(float e, int k, unsigned int& r0, bool& t0, unsigned int& r1, bool& t1) {
+  const uint32_t b = __float_as_uint(e);
+  const uint32_t field = b >> 23;
+  const uint32_t m = field != 0u ? ((b & 0x7fffffu) | 0x800000u) : (b & 0x7fffffu);
+  const int d = k - (field != 0u ? int(field) - 127 : -126);
+  r0 = r1 = 0u;
+  t0 = t1 = false;
+  if (d >= 25 || m == 0u) return;
+  if (d < 1) { r0 = 0xffffffffu; t0 = true; return; }
+  const uint32_t half = 1u << (d - 1);
+  r0 = (m + half) >> d;
+  t0 = (m & (2u * half - 1u)) == half;
+  if (d == 24) return;                                   // under the doubled unit the term is below a quarter: nothing
+  r1 = (m + 2u * half) >> (d + 1);
+  t1 = (m & (4u * half - 1u)) == 2u * half;
+}
 __device__ __forceinline__ int exponent_of(float s) { return int((__float_as_uint(s) >> 23) & 0xffu) - 127; }
 
 __device__ __forceinline__ int tail_bucket(float score, float low_score, float scale) {
@@ -590,107 +744,169 @@ __device__ __forceinline__ int tail_bucket(float score, float low_score, float s
   const int b = t >= float(kTailBuckets - 1) ? kTailBuckets - 1 : int(t);
   return b < 0 ? 0 : b;
 }
-// buckets per unit of score: the tail terms that can still move the sum lie within (k - 26) * ln 2 of the maximum
+// buckets per unit of score: the tail terms that can still move the sum lie within (k - 24) * ln 2 of the maximum
 __device__ __forceinline__ float tail_scale(const HeadState& h) {
-  const float lowest = h.max_score + float(exponent_of(h.sum) - 26) * 0.6931471805599453f;
+  const float lowest = h.max_score + float(exponent_of(h.sum) - 24) * 0.6931471805599453f - 0.01f;
   const float span = h.low_score - lowest;
   return span > 1e-6f ? float(kTailBuckets) / span : 0.0f;
 }
 
-// head: sort the row's candidates (all of them), leave them at the front of the row's key area, and add their
-// exponentials in order, keeping every running sum
-__global__ void __launch_bounds__(kSortThreads)
-topp_head_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
-                 float* running, unsigned int* tails, HeadState* heads, int* row_flags) {
-  extern __shared__ unsigned long long buf[];
-  __shared__ float stage[kChunk];
-  __shared__ float carry;
+// head, step 1: the row's candidates (at most one 4096-key tile of them) move to the front of the row's key area,
+// padded with zeros; the register-tile kernel of the whole-row sort then sorts that one tile per row.
+__global__ void __launch_bounds__(256)
+topp_pack_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
+                 unsigned int* tails, int* row_flags) {
   const int64_t row = blockIdx.x;
-  const int tid = threadIdx.x;
   // the tail pass adds into these: they start at zero
   unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
-  for (int i = tid; i < 3 * kTailBuckets; i += kSortThreads) tail[i] = 0u;
+  for (int i = threadIdx.x; i < 3 * kTailBuckets; i += 256) tail[i] = 0u;
   if (row_flags[row] != 0) return;
   const unsigned int count = cut[row].taken;
-  if (count < unsigned(kMinHead) || count > unsigned(kCandidates)) {
-    if (tid == 0) row_flags[row] = 1;
+  if (count < unsigned(kMinHead) || count > unsigned(kTile)) {
+    if (threadIdx.x == 0) row_flags[row] = 1;
     return;
   }
   const unsigned long long* in = candidates + row * int64_t(kCandidates);
-  int n = 2;
-  while (n < int(count)) n <<= 1;
-  for (int i = tid; i < n; i += kSortThreads) buf[i] = unsigned(i) < count ? in[i] : 0ull;
-  __syncthreads();
-  for (int k = 2; k <= n; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int p = tid; p < n / 2; p += kSortThreads) {
-        const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
-        compare_exchange(buf[i], buf[i | j], (i & k) == 0);
-      }
-      __syncthreads();
-    }
-  }
   unsigned long long* dst = keys + row * padded;
-  for (int i = tid; i < int(count); i += kSortThreads) dst[i] = buf[i];
-  const float maximum = key_score(buf[0]);
+  for (int i = threadIdx.x; i < kTile; i += 256) dst[i] = unsigned(i) < count ? in[i] : 0ull;
+}
+
+// head, step 2 (after the sort): the exponentials of the head in order, added by one thread, every running sum kept
+__global__ void __launch_bounds__(256)
+topp_head_kernel(const unsigned long long* keys, int64_t padded, const CutState* cut, float* running, HeadState* heads,
+                 const int* row_flags) {
+  __shared__ __align__(16) float stage[kChunk];
+  __shared__ float carry;
+  const int64_t row = blockIdx.x;
+  if (row_flags[row] != 0) return;
+  const int tid = threadIdx.x;
+  const int count = int(cut[row].taken);
+  const unsigned long long* sorted = keys + row * padded;
+  const float maximum = key_score(sorted[0]);
   float* cum = running + row * padded;
   if (tid == 0) carry = 0.0f;
   __syncthreads();
-  for (int base = 0; base < int(count); base += kChunk) {
-    const int m = int(count) - base < kChunk ? int(count) - base : kChunk;
-    for (int j = tid; j < m; j += kSortThreads) stage[j] = expf(key_score(buf[base + j]) - maximum);
+  for (int base = 0; base < count; base += kChunk) {
+    const int m = count - base < kChunk ? count - base : kChunk;
+    for (int j = tid; j < m; j += 256) stage[j] = expf(key_score(sorted[base + j]) - maximum);
     __syncthreads();
-    if (tid == 0) {
-      float sum = carry;
-      for (int j = 0; j < m; ++j) { sum += stage[j]; stage[j] = sum; }
-      carry = sum;
-    }
+    if (tid == 0) carry = running_sums_in_order(stage, m, carry);
     __syncthreads();
-    for (int j = tid; j < m; j += kSortThreads) cum[base + j] = stage[j];
+    for (int j = tid; j < m; j += 256) cum[base + j] = stage[j];
     __syncthreads();
   }
-  if (tid == 0) heads[row] = HeadState{carry, maximum, key_score(buf[count - 1]), int(count)};
+  if (tid == 0) heads[row] = HeadState{carry, maximum, key_score(sorted[count - 1]), count};
 }
 
 // tail: increments of every term below the head, per bucket, for the head's power of two and the next one.
-// Per bucket three words: sum of increments under k, under k + 1, and (terms << 2 | tie under k + 1 << 1 | tie under k).
+// Per bucket one 64-bit word (increments under k + 1 << 32 | increments under k) and one word of tie flags
+// (bit 0: a tie under k, bit 1: under k + 1).  A term of more than 4096 units does not belong in a tail (the sums of
+// up to 2^19 of them must stay below 2^32): the row is handed to the whole-row sort.
+constexpr unsigned int kMaxTailIncrement = 4096;   // times at most kMaxToppWidth terms: a bucket's sum fits 32 bits
+constexpr int64_t kMaxToppWidth = int64_t(1) << 19;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, const CutState* cut,
                  const HeadState* heads, unsigned int* tails, int* row_flags) {
-  __shared__ unsigned int local[3 * kTailBuckets];
+  constexpr int N = Elem<T>::kPerVec, kVecs = 16 / N;          // 16 elements per thread and turn
+  constexpr int kQueue = 256 * 16;
+  __shared__ unsigned long long local[kTailBuckets];
+  __shared__ unsigned int local_ties[kTailBuckets];
+  __shared__ float queue[kQueue];
+  __shared__ unsigned int queued;
   const int64_t row = blockIdx.y;
   if (row_flags[row] != 0) return;
-  for (int i = threadIdx.x; i < 3 * kTailBuckets; i += 256) local[i] = 0u;
+  for (int i = threadIdx.x; i < kTailBuckets; i += 256) { local[i] = 0ull; local_ties[i] = 0u; }
+  if (threadIdx.x == 0) queued = 0u;
   __syncthreads();
   const HeadState h = heads[row];
   const float threshold = cut[row].threshold, scale = tail_scale(h);
   const int k = exponent_of(h.sum);
+  // a hair below the score at which the increments vanish (e < 2^(k-24) adds less than half a unit; the margin
+  // covers the roundings of the subtraction and of expf, and the exact test is made on e itself)
+  const float lowest = h.max_score + float(k - 24) * 0.6931471805599453f - 0.01f;
+  // Only a quarter of the tokens lie between that point and the head, scattered over every warp: a warp that took the
+  // slow path (division, exponential, increments, atomics) whenever one lane needs it would take it always.  So a
+  // turn first only SELECTS, with one comparison per token against a cut-off in logit units (a little below
+  // lowest * temperature: the exact test follows), and queues the selected logits; then all threads work the queue.
+  const float cut_logit = lowest * temperature - 1e-5f * fabsf(lowest * temperature) - 1e-30f;
   bool broken = false;
-  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t) {
-    if (x >= threshold) return;                                   // a head token (a NaN would have raised the row's flag)
-    const float score = __fdiv_rn(x, temperature);
-    const float e = expf(score - h.max_score);
-    unsigned int r0, r1;
-    bool t0, t1;
-    term_increment(e, k, r0, t0);
-    term_increment(e, k + 1, r1, t1);
-    if (r0 == 0xffffffffu) { broken = true; return; }
-    if ((r0 | r1) == 0u && !t0 && !t1) return;                    // cannot move the sum under either power of two
-    const int b = tail_bucket(score, h.low_score, scale);
-    if (r0 != 0u) atomicAdd(&local[b], r0);
-    if (r1 != 0u) atomicAdd(&local[kTailBuckets + b], r1);
-    atomicAdd(&local[2 * kTailBuckets + b], 4u);
-    if (t0 || t1) atomicOr(&local[2 * kTailBuckets + b], (t0 ? 1u : 0u) | (t1 ? 2u : 0u));
-  });
-  if (broken) row_flags[row] = 1;
-  __syncthreads();
+  const T* src = logits + row * row_stride;
+  const int lane = threadIdx.x & 31;
+  auto select = [&](float x) {
+    const bool take = x < threshold && x >= cut_logit;
+    const unsigned int votes = __ballot_sync(0xffffffffu, take);
+    if (votes == 0u) return;
+    unsigned int base = 0u;
+    if (lane == 0) base = atomicAdd(&queued, unsigned(__popc(votes)));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (take) queue[base + __popc(votes & ((1u << lane) - 1u))] = x;
+  };
+  auto work_queue = [&]() {
+    __syncthreads();
+    const unsigned int n = queued;
+    for (unsigned int q = threadIdx.x; q < n; q += 256) {
+      const float score = temperature == 1.0f ? queue[q] : __fdiv_rn(queue[q], temperature);
+      if (score < lowest) continue;
+      const float e = expf(score - h.max_score);
+      unsigned int r0, r1;
+      bool t0, t1;
+      term_increments(e, k, r0, t0, r1, t1);
+      if (r0 > kMaxTailIncrement) { broken = true; continue; }
+      if ((r0 | r1) == 0u && !t0 && !t1) continue;                 // cannot move the sum under either power of two
+      const int b = tail_bucket(score, h.low_score, scale);
+      atomicAdd(&local[b], (static_cast<unsigned long long>(r1) << 32) | r0);
+      if (t0 || t1) atomicOr(&local_ties[b], (t0 ? 1u : 0u) | (t1 ? 2u : 0u));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) queued = 0u;
+    __syncthreads();
+  };
+  const int64_t first = int64_t(blockIdx.x) * 256 + threadIdx.x, stride = int64_t(gridDim.x) * 256;
+  if (aligned16(src)) {
+    const int64_t nvec = width / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    // every thread of the block takes the same number of turns (the ballots and barriers need them all)
+    const int64_t turns = (nvec + stride * kVecs - 1) / (stride * kVecs);
+    for (int64_t turn = 0; turn < turns; ++turn) {
+      const int64_t v0 = first + turn * stride * kVecs;
+      uint4 r[kVecs];
+#pragma unroll
+      for (int q = 0; q < kVecs; ++q) if (v0 + q * stride < nvec) r[q] = ld_stream(vp + v0 + q * stride);
+#pragma unroll
+      for (int q = 0; q < kVecs; ++q) {
+        float e[N];
+        const bool in = v0 + q * stride < nvec;
+        if (in) Elem<T>::unpack(r[q], e);
+#pragma unroll
+        for (int z = 0; z < N; ++z) select(in ? e[z] : INFINITY);   // +inf is never selected
+      }
+      work_queue();
+    }
+    const int64_t tail_turns = (width - nvec * N + stride - 1) / stride;
+    for (int64_t turn = 0; turn < tail_turns; ++turn) {
+      const int64_t i = nvec * N + first + turn * stride;
+      select(i < width ? Elem<T>::load(src + i) : INFINITY);
+    }
+  } else {
+    const int64_t turns = (width + stride * 16 - 1) / (stride * 16);
+    for (int64_t turn = 0; turn < turns; ++turn) {
+      for (int q = 0; q < 16; ++q) {
+        const int64_t i = first + (turn * 16 + q) * stride;
+        select(i < width ? Elem<T>::load(src + i) : INFINITY);
+      }
+      work_queue();
+    }
+  }
+  work_queue();
+  if (broken) row_flags[row] = 2;           // (the values only tell the reasons apart for a reader of the flags)
+  // global layout per row: [0, 2 kTailBuckets) the 64-bit sums, [2 kTailBuckets, 3 kTailBuckets) the tie flags
   unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
-  for (int i = threadIdx.x; i < 2 * kTailBuckets; i += 256)
-    if (local[i] != 0u) atomicAdd(&tail[i], local[i]);
-  for (int i = 2 * kTailBuckets + threadIdx.x; i < 3 * kTailBuckets; i += 256) {
-    const unsigned int v = local[i];
-    if (v != 0u) { atomicAdd(&tail[i], v & ~3u); if (v & 3u) atomicOr(&tail[i], v & 3u); }
+  unsigned long long* sums = reinterpret_cast<unsigned long long*>(tail);
+  for (int i = threadIdx.x; i < kTailBuckets; i += 256) {
+    if (local[i] != 0ull) atomicAdd(&sums[i], local[i]);
+    if (local_ties[i] != 0u) atomicOr(&tail[2 * kTailBuckets + i], local_ties[i]);
   }
 }
 
@@ -701,8 +917,12 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
                    const unsigned long long* keys, int64_t padded, const float* running, const unsigned int* tails,
                    const HeadState* heads, float top_p, unsigned long long seed, const unsigned long long* draw_offsets,
                    int32_t* out_ids, int* row_flags) {
-  __shared__ unsigned long long bucket_keys[kTailBuckets];
-  __shared__ float stage[kChunk];
+  constexpr int kGroup = 64, kGroups = kTailBuckets / kGroup;   // the walk first steps over groups of 64 buckets
+  __shared__ __align__(16) unsigned long long bucket_keys[kTailBuckets];
+  __shared__ unsigned long long sums[kTailBuckets];          // (increments under k0 + 1) << 32 | (increments under k0)
+  __shared__ unsigned int ties[kTailBuckets];
+  __shared__ unsigned long long group_sums[kGroups];
+  __shared__ unsigned int group_ties[kGroups];
   __shared__ float carry;
   __shared__ unsigned int walk_m;
   __shared__ int walk_k, walk_bucket, found, give_up;
@@ -711,9 +931,22 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
   if (row_flags[row] != 0) return;
   const int tid = threadIdx.x;
   const HeadState h = heads[row];
-  const unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+  {
+    const unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+    const unsigned long long* tail_sums = reinterpret_cast<const unsigned long long*>(tail);
+    for (int i = tid; i < kTailBuckets; i += kSortThreads) { sums[i] = tail_sums[i]; ties[i] = tail[2 * kTailBuckets + i]; }
+  }
+  __syncthreads();
+  if (tid < kGroups) {
+    unsigned long long total = 0ull;
+    unsigned int any = 0u;
+    for (int i = 0; i < kGroup; ++i) { total += sums[tid * kGroup + i]; any |= ties[tid * kGroup + i]; }
+    group_sums[tid] = total;      // each half stays below 2^32: at most 2^19 terms of at most 4096 units
+    group_ties[tid] = any;
+  }
   const float threshold = cut[row].threshold, scale = tail_scale(h);
   const int k0 = exponent_of(h.sum);
+  const float lowest = h.max_score + float(k0 - 24) * 0.6931471805599453f - 0.01f;   // as in the tail pass
   const T* src = logits + row * row_stride;
   if (tid == 0) {
     walk_m = (__float_as_uint(h.sum) & 0x7fffffu) | 0x800000u;
@@ -726,41 +959,69 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     if (tid == 0) {
       unsigned int m = walk_m;
       int k = walk_k, b = walk_bucket;
-      for (; b < kTailBuckets; ++b) {
-        const unsigned int info = tail[2 * kTailBuckets + b];
-        if (info == 0u) continue;
+      while (b < kTailBuckets) {
         if (k > k0 + 1) { give_up = 1; break; }
-        const unsigned int r = k == k0 ? tail[b] : tail[kTailBuckets + b];
-        const bool tie = (info & (k == k0 ? 1u : 2u)) != 0u;
-        if (tie || static_cast<unsigned long long>(m) + r > (1ull << 24)) break;   // the order inside this bucket matters
-        m += r;
+        const int shift = k == k0 ? 0 : 32;
+        const unsigned int tie_bit = k == k0 ? 1u : 2u;
+        if ((b & (kGroup - 1)) == 0) {        // a whole group at once when nothing in it needs the order
+          const int g = b / kGroup;
+          const unsigned long long r = (group_sums[g] >> shift) & 0xffffffffull;
+          if ((group_ties[g] & tie_bit) == 0u && m + r < (1ull << 24)) { m += unsigned(r); b += kGroup; continue; }
+        }
+        const unsigned long long r = (sums[b] >> shift) & 0xffffffffull;
+        if ((ties[b] & tie_bit) != 0u || m + r > (1ull << 24)) break;   // the order inside this bucket matters
+        m += unsigned(r);
         if (m == (1u << 24)) { m = 1u << 23; ++k; }
+        ++b;
       }
       walk_m = m; walk_k = k; walk_bucket = b;
       gathered = 0u;
     }
     __syncthreads();
-    if (give_up != 0) { if (tid == 0) row_flags[row] = 1; return; }
+    if (give_up != 0) { if (tid == 0) row_flags[row] = 3; return; }
     const int b = walk_bucket;
     if (b >= kTailBuckets) break;
     // gather the terms of bucket b that can move the sum, sort them into the reference's order, add them one by one
-    for (int64_t i = tid; i < width; i += kSortThreads) {
-      const float x = Elem<T>::load(src + i);
-      if (x >= threshold) continue;
-      const float score = __fdiv_rn(x, temperature);
-      if (tail_bucket(score, h.low_score, scale) != b) continue;
+    auto consider = [&](float x, int64_t i) {
+      if (x >= threshold) return;
+      const float score = temperature == 1.0f ? x : __fdiv_rn(x, temperature);
+      if (score < lowest || tail_bucket(score, h.low_score, scale) != b) return;
       const float e = expf(score - h.max_score);
       unsigned int r0, r1;
       bool t0, t1;
-      term_increment(e, k0, r0, t0);
-      term_increment(e, k0 + 1, r1, t1);
-      if ((r0 | r1) == 0u && !t0 && !t1) continue;
+      term_increments(e, k0, r0, t0, r1, t1);
+      if ((r0 | r1) == 0u && !t0 && !t1) return;
       const unsigned int slot = atomicAdd(&gathered, 1u);
       if (slot < unsigned(kTailBuckets)) bucket_keys[slot] = sample_key(score, uint32_t(i));
+    };
+    {
+      constexpr int N = Elem<T>::kPerVec;
+      if (aligned16(src)) {
+        const int64_t nvec = width / N;
+        const uint4* vp = reinterpret_cast<const uint4*>(src);
+        for (int64_t v0 = tid; v0 < nvec; v0 += int64_t(kSortThreads) * 4) {   // four loads in flight per thread
+          uint4 r[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) if (v0 + q * kSortThreads < nvec) r[q] = ld_stream(vp + v0 + q * kSortThreads);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int64_t v = v0 + q * kSortThreads;
+            if (v < nvec) {
+              float e[N];
+              Elem<T>::unpack(r[q], e);
+#pragma unroll
+              for (int z = 0; z < N; ++z) consider(e[z], v * N + z);
+            }
+          }
+        }
+        for (int64_t i = nvec * N + tid; i < width; i += kSortThreads) consider(Elem<T>::load(src + i), i);
+      } else {
+        for (int64_t i = tid; i < width; i += kSortThreads) consider(Elem<T>::load(src + i), i);
+      }
     }
     __syncthreads();
     const unsigned int count = gathered;
-    if (count > unsigned(kTailBuckets)) { if (tid == 0) row_flags[row] = 1; return; }
+    if (count > unsigned(kTailBuckets)) { if (tid == 0) row_flags[row] = 4; return; }
     int n = 2;
     while (n < int(count)) n <<= 1;
     for (int i = int(count) + tid; i < n; i += kSortThreads) bucket_keys[i] = 0ull;
@@ -784,6 +1045,8 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     __syncthreads();
   }
   const float total = __uint_as_float((uint32_t(walk_k + 127) << 23) | (walk_m & 0x7fffffu));
+  float* stage = reinterpret_cast<float*>(bucket_keys);   // the gathered keys are no longer needed: kChunk floats fit their place
+  __syncthreads();
 
   // the reference's top-p walk (src/ops_cuda.cu:596-603) over the head; it must end strictly above the head's lowest score
   const unsigned long long* sorted = keys + row * padded;
@@ -798,17 +1061,30 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     __syncthreads();
     if (tid == 0) {
       float cumulative = carry;
-      for (int j = 0; j < m; ++j) {
+      int at = -1, j = 0;
+      for (; j + 8 <= m && at < 0; j += 8) {        // eight loads in flight; the additions stay in order
+        const float4 a = *reinterpret_cast<const float4*>(stage + j), b4 = *reinterpret_cast<const float4*>(stage + j + 4);
+        const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (at < 0) {
+            cumulative += v[q];
+            if (cumulative >= top_p) at = j + q;
+          }
+        }
+      }
+      for (; j < m && at < 0; ++j) {
         cumulative += stage[j];
-        if (cumulative >= top_p) { found = j; break; }
+        if (cumulative >= top_p) at = j;
       }
       carry = cumulative;
+      found = at;
     }
     __syncthreads();
     if (found >= 0) { prefix = base + found + 1; break; }
   }
   if (prefix < 0 || !(key_score(sorted[prefix - 1]) > h.low_score)) {   // not settled inside the head: the whole-row path decides
-    if (tid == 0) row_flags[row] = 1;
+    if (tid == 0) row_flags[row] = 5;
     return;
   }
   const float prefix_total = cum[prefix - 1];
@@ -840,8 +1116,8 @@ int64_t padded_width(int64_t width) {
 size_t sampler_workspace_bytes(int64_t rows, int64_t width) {
   const int64_t padded = padded_width(width);
   const size_t per_row = size_t(padded) * 12 + size_t(kCandidates) * 8 + size_t(3 * kTailBuckets) * 4 + sizeof(CutState) +
-                         sizeof(HeadState) + sizeof(int);
-  return (size_t(rows) * per_row + 16 + 255) / 256 * 256;
+                         sizeof(HeadState) + 2 * sizeof(int);
+  return (size_t(rows) * per_row + 32 + 255) / 256 * 256;
 }
 
 int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, float temperature,
@@ -865,7 +1141,8 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
   // logits / temperature stays a normal number near a threshold only for a moderate temperature (and a moderate
   // logit there, which the splitter kernel checks)
   const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
-  const int* only_rows = nullptr;   // the rows the whole-row sort below has to do (null: all of them)
+  RowSet todo{nullptr, nullptr};    // the rows the whole-row sort below has to do (no list: all of them)
+  unsigned row_blocks = unsigned(rows);
 
   if (top_k > 0 && top_k <= kMaxSelectK && width > kTile) {
     // only the k largest keys matter: a sampled threshold, one pass over the logits, a small sort: five launches and
@@ -879,11 +1156,11 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     }
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
-      topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      topk_splitter_kernel<float><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
       topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
     } else {
       const __half* x = static_cast<const __half*>(logits);
-      topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      topk_splitter_kernel<__half><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
       topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
     }
     topk_finish_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, top_k, cut, candidates, overflow);
@@ -895,58 +1172,61 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
       topk_exact_kernel<__half><<<unsigned(rows), kExactThreads, 0, s>>>(static_cast<const __half*>(logits), width, row_stride,
                                                                          padded, temperature, top_k, keys, overflow);
   } else {
-    if (top_k == 0 && top_p < 1.0f && width >= 4 * kCandidates) {
+    if (top_k == 0 && top_p < 1.0f && width >= 4 * kCandidates && width <= kMaxToppWidth) {
       // top-p over the whole vocabulary: head sorted, tail summed by buckets; rows that do not fit that scheme raise
       // their flag and are the only ones the whole-row sort below still works on
       if (cudaMemsetAsync(row_flags, 0, size_t(rows) * sizeof(int), s) != cudaSuccess) return launch_status("sample_rows");
-      if (cudaFuncSetAttribute(topp_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCandidates * 8) != cudaSuccess) {
-        cudaGetLastError();
-        set_error("sample_rows: cannot reserve shared memory");
-        return B2_ERR_CUDA;
-      }
       if (dtype == B2_F32) {
         const float* x = static_cast<const float*>(logits);
-        topk_splitter_kernel<float><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, kHeadTarget, safe, cut, row_flags, 1);
+        topk_splitter_kernel<float><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, 0u, safe, cut, row_flags, 1);
         topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        topp_head_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, cut, candidates, running, tails, heads, row_flags);
+        topp_pack_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, candidates, tails, row_flags);
+        bitonic_tile_registers_kernel<<<dim3(1, unsigned(rows)), kRegThreads, 0, s>>>(keys, padded, 2, kTile, RowSet{nullptr, nullptr});
+        topp_head_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, running, heads, row_flags);
         topp_tail_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
         topp_finish_kernel<float><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
                                                                           tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
       } else {
         const __half* x = static_cast<const __half*>(logits);
-        topk_splitter_kernel<__half><<<unsigned(rows), 256, 0, s>>>(x, width, row_stride, kHeadTarget, safe, cut, row_flags, 1);
+        topk_splitter_kernel<__half><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, 0u, safe, cut, row_flags, 1);
         topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        topp_head_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, cut, candidates, running, tails, heads, row_flags);
+        topp_pack_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, candidates, tails, row_flags);
+        bitonic_tile_registers_kernel<<<dim3(1, unsigned(rows)), kRegThreads, 0, s>>>(keys, padded, 2, kTile, RowSet{nullptr, nullptr});
+        topp_head_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, running, heads, row_flags);
         topp_tail_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
         topp_finish_kernel<__half><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
                                                                            tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
       }
-      only_rows = row_flags;
+      // the rows whose flag is up, as a list: the kernels of the whole-row sort walk it
+      int* row_list = overflow + 4;
+      list_rows_kernel<<<1, 256, 0, s>>>(row_flags, int(rows), row_list, overflow + 1);
+      todo = RowSet{row_list, overflow + 1};
+      row_blocks = unsigned(rows < kListedRowBlocks ? rows : kListedRowBlocks);
     }
     // the whole-row sort has little per-block overhead: many small blocks
-    const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), unsigned(rows));
+    const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), row_blocks);
     if (dtype == B2_F32)
       sampler_keys_kernel<float><<<wide_grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
-                                                            temperature, keys, only_rows);
+                                                            temperature, keys, todo);
     else
       sampler_keys_kernel<__half><<<wide_grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
-                                                           temperature, keys, only_rows);
+                                                           temperature, keys, todo);
     const int tile = int(padded < kTile ? padded : kTile);
-    const dim3 tile_grid(unsigned(padded / tile), unsigned(rows));
+    const dim3 tile_grid(unsigned(padded / tile), row_blocks);
     if (tile < kTile) {
-      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile, only_rows);   // the whole row is one small tile
+      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile, todo);   // the whole row is one small tile
     } else {
-      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile, only_rows);
+      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile, todo);
       for (int64_t k = int64_t(kTile) * 2; k <= padded; k <<= 1) {
         int64_t j = k >> 1;
-        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, only_rows);   // steps j and j/2
-        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, only_rows);              // one step left over
-        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k, only_rows);
+        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, todo);   // steps j and j/2
+        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, todo);                   // one step left over
+        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k, todo);
       }
     }
   }
-  sampler_pick_kernel<<<unsigned(rows), kSelectThreads, 0, s>>>(keys, width, padded, top_k, top_p, seed, draw_offsets, running,
-                                                                out_ids, only_rows);
+  sampler_pick_kernel<<<row_blocks, kSelectThreads, 0, s>>>(keys, width, padded, top_k, top_p, seed, draw_offsets, running, out_ids,
+                                                            todo);
   return launch_status("sample_rows");
 }
 
