@@ -57,6 +57,7 @@ __device__ __forceinline__ bool row_of(const RowSet& rs, int64_t it, int64_t gri
 constexpr int kListedRowBlocks = 4;   // row dimension of a launch over a row list
 
 __global__ void __launch_bounds__(256) list_rows_kernel(const int* row_flags, int rows, int* list, int* count) {
+  dependent_launch_prologue();
   __shared__ int n;
   if (threadIdx.x == 0) n = 0;
   __syncthreads();
@@ -71,6 +72,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 sampler_keys_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature,
                     unsigned long long* keys, const RowSet rs) {
+  dependent_launch_prologue();
   int64_t row;
   for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
     const T* src = logits + row * row_stride;
@@ -91,6 +93,7 @@ __device__ __forceinline__ void compare_exchange(unsigned long long& a, unsigned
 // global memory.
 __global__ void __launch_bounds__(kSortThreads)
 bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t k_first, int64_t k_last, const RowSet rs) {
+  dependent_launch_prologue();
   extern __shared__ unsigned long long tile_keys[];
   int64_t row;
   for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
@@ -117,6 +120,7 @@ bitonic_tile_kernel(unsigned long long* keys, int64_t padded, int tile, int64_t 
 // few hundred rows fit the L2).
 __global__ void __launch_bounds__(256)
 bitonic_wide_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const RowSet rs) {
+  dependent_launch_prologue();
   int64_t row;
   for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
     unsigned long long* base = keys + row * padded;
@@ -198,6 +202,7 @@ __device__ __forceinline__ void layout_s_to_b(unsigned long long (&key)[kRegKeys
 // j = 2048 .. 1 that finish a merge whose wide steps ran in global memory.
 __global__ void __launch_bounds__(kRegThreads)
 bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t k_first, int64_t k_last, const RowSet rs) {
+  dependent_launch_prologue();
   __shared__ unsigned long long tile[kTile];
   const int64_t tile_global = int64_t(blockIdx.x) * kTile;
   int64_t row;
@@ -237,6 +242,7 @@ bitonic_tile_registers_kernel(unsigned long long* keys, int64_t padded, int64_t 
 // steps connect are loaded once.
 __global__ void __launch_bounds__(256)
 bitonic_wide_pair_kernel(unsigned long long* keys, int64_t padded, int64_t k, int64_t j, const RowSet rs) {
+  dependent_launch_prologue();
   const int64_t h = j >> 1;
   int64_t row;
   for (int64_t it = blockIdx.y; row_of(rs, it, gridDim.y, &row); it += gridDim.y) {
@@ -268,6 +274,7 @@ template <typename T>
 __global__ void __launch_bounds__(kExactThreads)
 topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t padded, float temperature, int top_k,
                   unsigned long long* keys, const int* only_if) {
+  dependent_launch_prologue();
   __shared__ unsigned int counts[kSelectBins];
   __shared__ unsigned long long survivors[kMaxSelectK];
   __shared__ unsigned long long prefix_s;
@@ -330,7 +337,7 @@ topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t pa
 }
 
 // ---- small top_k, the usual case: ONE pass over the logits and no key array.
-//   splitter  a thread block per row looks at 8192 evenly spaced logits of the row and takes, as threshold, the
+//   splitter  a thread block per row looks at 8192 logits of the row (1024 evenly spaced runs of eight) and takes, as threshold, the
 //             sample whose rank makes "a few times top_k, and with near certainty at least top_k" tokens of the
 //             whole row lie above it, lowered by 2^-12 of its magnitude
 //   gather    the one pass: every token whose logit is at or above the threshold has its exact score computed and
@@ -359,36 +366,6 @@ __device__ __forceinline__ float from_ordered_bits(uint32_t o) {
   return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
 }
 
-// f(value, index) for every element of a row, 16-byte loads when the row allows, blocks of the grid's x dimension
-// striding over the row
-template <typename T, typename F>
-__device__ __forceinline__ void for_each_logit(const T* src, int64_t width, F&& f) {
-  constexpr int N = Elem<T>::kPerVec;
-  const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x, stride = int64_t(gridDim.x) * blockDim.x;
-  if (aligned16(src)) {
-    const int64_t nvec = width / N;
-    const uint4* vp = reinterpret_cast<const uint4*>(src);
-    for (int64_t v0 = first; v0 < nvec; v0 += stride * 4) {      // four loads in flight per thread
-      uint4 r[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) if (v0 + k * stride < nvec) r[k] = ld_stream(vp + v0 + k * stride);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int64_t v = v0 + k * stride;
-        if (v < nvec) {
-          float e[N];
-          Elem<T>::unpack(r[k], e);
-#pragma unroll
-          for (int q = 0; q < N; ++q) f(e[q], v * N + q);
-        }
-      }
-    }
-    for (int64_t i = nvec * N + first; i < width; i += stride) f(Elem<T>::load(src + i), i);
-  } else {
-    for (int64_t i = first; i < width; i += stride) f(Elem<T>::load(src + i), i);
-  }
-}
-
 constexpr int kSplitThreads = 1024;
 constexpr int kSamplesPerThread = kSplitSamples / kSplitThreads;
 // The sample of rank `rank` (0 = largest) is found by a radix select over the samples' 32 ordered bits, eight bits
@@ -401,6 +378,7 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
                      int* overflow, int overflow_stride) {   // the flag of row r is overflow[r * overflow_stride]: stride 0 = one flag per call
   // top_k == 0: no count to reach; the threshold is to leave as many candidates as fit one kTile-key tile with near
   // certainty (the top-p path's head)
+  dependent_launch_prologue();
   __shared__ unsigned int bins[256];
   __shared__ uint32_t prefix_found;
   __shared__ int rank_left;
@@ -416,7 +394,9 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
     const int sidx = threadIdx.x + q * kSplitThreads;
     mine[q] = 0u;
     if (sidx < samples) {
-      const float x = Elem<T>::load(src + (int64_t(sidx) * width) / samples);
+      // runs of eight neighbouring tokens, the runs evenly spaced: one 32-byte sector per run instead of one per
+      // sample (samples every 18 tokens would touch every sector of the row: a whole extra pass over the logits)
+      const float x = Elem<T>::load(src + (int64_t(sidx >> 3) * width) / (samples >> 3) + (sidx & 7));
       mine[q] = x == x ? ordered_bits(x) : 0u;                                   // a NaN never ranks
     }
   }
@@ -491,41 +471,117 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 8)
 topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, CutState* cut,
                    unsigned long long* candidates, const int* overflow, int overflow_stride) {
+  dependent_launch_prologue();
   const int64_t row = blockIdx.y;
   overflow += row * overflow_stride;
   if (*overflow != 0) return;                      // the row (or the call) is being redone by the exact path anyway
-  // candidates are collected in shared memory and appended to the row's list with ONE global atomic per block
-  // (a few thousand candidates per row would otherwise queue on one address); what does not fit goes out directly
-  constexpr int kLocal = 1024;
-  __shared__ unsigned long long local_keys[kLocal];
+  // Candidates are rare (tenths of a percent to two percent of the tokens), so the pass only STAGES them: a turn
+  // reads 16 tokens per thread, counts its candidates, a warp takes room for all of its own with one shared-memory
+  // atomic (per-candidate atomics queue on one address), and each candidate's raw (logit, index) pair goes to the
+  // staging area.  Scores and keys are computed afterwards, densely, and the block appends to the row's list
+  // with ONE global atomic.  What does not fit the staging area goes out directly.
+  constexpr int N = Elem<T>::kPerVec, kVecs = 16 / N, kLocal = 2048;   // 16 tokens per thread and turn
+  __shared__ float2 staged[kLocal];                // (logit, index bits)
   __shared__ unsigned int local_count, base_slot;
   if (threadIdx.x == 0) local_count = 0u;
   __syncthreads();
   const float threshold = cut[row].threshold;
   unsigned long long* out = candidates + row * int64_t(kCandidates);
+  const T* src = logits + row * row_stride;
+  const int lane = threadIdx.x & 31;
   bool strange = false;
-  for_each_logit<T>(logits + row * row_stride, width, [&](float x, int64_t i) {
-    if (x >= threshold) {
-      const unsigned long long key = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
-      const unsigned int mine = atomicAdd(&local_count, 1u);
-      if (mine < unsigned(kLocal)) {
-        local_keys[mine] = key;
-      } else {
-        const unsigned int slot = atomicAdd(&cut[row].taken, 1u);
-        if (slot < unsigned(kCandidates)) out[slot] = key;
+  auto place = [&](float x, int64_t i, unsigned int slot) {
+    if (slot < unsigned(kLocal)) {
+      staged[slot] = make_float2(x, __uint_as_float(uint32_t(i)));
+    } else {
+      const unsigned int direct = atomicAdd(&cut[row].taken, 1u);
+      if (direct < unsigned(kCandidates)) out[direct] = sample_key(__fdiv_rn(x, temperature), uint32_t(i));
+    }
+  };
+  // room for `count` candidates of this lane: returns the lane's first slot (every lane of the warp calls this)
+  auto reserve = [&](unsigned int count) {
+    unsigned int before = count;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const unsigned int up = __shfl_up_sync(0xffffffffu, before, offset);
+      if (lane >= offset) before += up;
+    }
+    const unsigned int total = __shfl_sync(0xffffffffu, before, 31);
+    unsigned int base = 0u;
+    if (total != 0u) {
+      if (lane == 0) base = atomicAdd(&local_count, total);
+      base = __shfl_sync(0xffffffffu, base, 0);
+    }
+    return base + before - count;
+  };
+  const int64_t first = int64_t(blockIdx.x) * 256 + threadIdx.x, stride = int64_t(gridDim.x) * 256;
+  if (aligned16(src)) {
+    const int64_t nvec = width / N;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    const int64_t turns = (nvec + stride * kVecs - 1) / (stride * kVecs);   // the same for every thread: the shuffles need whole warps
+    for (int64_t turn = 0; turn < turns; ++turn) {
+      const int64_t v0 = first + turn * stride * kVecs;
+      uint4 r[kVecs];
+#pragma unroll
+      for (int q = 0; q < kVecs; ++q) r[q] = v0 + q * stride < nvec ? ld_stream(vp + v0 + q * stride) : make_uint4(0u, 0u, 0u, 0u);
+      float e[kVecs][N];
+      unsigned int hits = 0u, count = 0u;
+#pragma unroll
+      for (int q = 0; q < kVecs; ++q) {
+        Elem<T>::unpack(r[q], e[q]);
+        const bool in = v0 + q * stride < nvec;
+#pragma unroll
+        for (int z = 0; z < N; ++z) {
+          const bool hit = in && e[q][z] >= threshold;
+          strange |= in && e[q][z] != e[q][z];
+          if (hit) { hits |= 1u << (q * N + z); ++count; }
+        }
+      }
+      if (__any_sync(0xffffffffu, count != 0u)) {
+        unsigned int slot = reserve(count);
+#pragma unroll
+        for (int q = 0; q < kVecs; ++q) {
+#pragma unroll
+          for (int z = 0; z < N; ++z)
+            if (hits >> (q * N + z) & 1u) place(e[q][z], (v0 + q * stride) * N + z, slot++);
+        }
       }
     }
-    strange |= x != x;
-  });
+    const int64_t rest_turns = (width - nvec * N + stride - 1) / stride;
+    for (int64_t turn = 0; turn < rest_turns; ++turn) {
+      const int64_t i = nvec * N + first + turn * stride;
+      const float x = i < width ? Elem<T>::load(src + i) : -INFINITY;
+      const bool hit = i < width && x >= threshold;
+      strange |= x != x;
+      if (__any_sync(0xffffffffu, hit)) {
+        const unsigned int slot = reserve(hit ? 1u : 0u);
+        if (hit) place(x, i, slot);
+      }
+    }
+  } else {
+    const int64_t turns = (width + stride - 1) / stride;
+    for (int64_t turn = 0; turn < turns; ++turn) {
+      const int64_t i = first + turn * stride;
+      const float x = i < width ? Elem<T>::load(src + i) : -INFINITY;
+      const bool hit = i < width && x >= threshold;
+      strange |= x != x;
+      if (__any_sync(0xffffffffu, hit)) {
+        const unsigned int slot = reserve(hit ? 1u : 0u);
+        if (hit) place(x, i, slot);
+      }
+    }
+  }
   __syncthreads();
   const unsigned int kept = local_count < unsigned(kLocal) ? local_count : unsigned(kLocal);
   if (threadIdx.x == 0) base_slot = kept != 0u ? atomicAdd(&cut[row].taken, kept) : 0u;
   __syncthreads();
-  for (unsigned int i = threadIdx.x; i < kept; i += blockDim.x)
-    if (base_slot + i < unsigned(kCandidates)) out[base_slot + i] = local_keys[i];
+  for (unsigned int i = threadIdx.x; i < kept; i += blockDim.x) {
+    const float2 c = staged[i];
+    if (base_slot + i < unsigned(kCandidates)) out[base_slot + i] = sample_key(__fdiv_rn(c.x, temperature), __float_as_uint(c.y));
+  }
   if (strange) atomicExch(const_cast<int*>(overflow), 1);
 }
 
@@ -534,6 +590,7 @@ topk_gather_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
 __global__ void __launch_bounds__(kSortThreads)
 topk_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const CutState* cut,
                    const unsigned long long* candidates, int* overflow) {
+  dependent_launch_prologue();
   extern __shared__ unsigned long long buf[];
   const int64_t row = blockIdx.x;
   const unsigned int count = cut[row].taken;
@@ -589,6 +646,7 @@ __global__ void __launch_bounds__(kSelectThreads)
 sampler_pick_kernel(const unsigned long long* keys, int64_t width, int64_t padded, int top_k, float top_p,
                     unsigned long long seed, const unsigned long long* draw_offsets, float* running, int32_t* out_ids,
                     const RowSet rs) {
+  dependent_launch_prologue();
   __shared__ float stage[kChunk];
   __shared__ float carry;
   __shared__ int found;
@@ -756,6 +814,7 @@ __device__ __forceinline__ float tail_scale(const HeadState& h) {
 __global__ void __launch_bounds__(256)
 topp_pack_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
                  unsigned int* tails, int* row_flags) {
+  dependent_launch_prologue();
   const int64_t row = blockIdx.x;
   // the tail pass adds into these: they start at zero
   unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
@@ -775,6 +834,7 @@ topp_pack_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, 
 __global__ void __launch_bounds__(256)
 topp_head_kernel(const unsigned long long* keys, int64_t padded, const CutState* cut, float* running, HeadState* heads,
                  const int* row_flags) {
+  dependent_launch_prologue();
   __shared__ __align__(16) float stage[kChunk];
   __shared__ float carry;
   const int64_t row = blockIdx.x;
@@ -809,15 +869,16 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, const CutState* cut,
                  const HeadState* heads, unsigned int* tails, int* row_flags) {
+  dependent_launch_prologue();
   constexpr int N = Elem<T>::kPerVec, kVecs = 16 / N;          // 16 elements per thread and turn
   constexpr int kQueue = 256 * 16;
-  __shared__ unsigned long long local[kTailBuckets];
+  __shared__ unsigned int local0[kTailBuckets], local1[kTailBuckets];   // 32-bit: shared memory adds those natively
   __shared__ unsigned int local_ties[kTailBuckets];
   __shared__ float queue[kQueue];
   __shared__ unsigned int queued;
   const int64_t row = blockIdx.y;
   if (row_flags[row] != 0) return;
-  for (int i = threadIdx.x; i < kTailBuckets; i += 256) { local[i] = 0ull; local_ties[i] = 0u; }
+  for (int i = threadIdx.x; i < kTailBuckets; i += 256) { local0[i] = 0u; local1[i] = 0u; local_ties[i] = 0u; }
   if (threadIdx.x == 0) queued = 0u;
   __syncthreads();
   const HeadState h = heads[row];
@@ -856,7 +917,8 @@ topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float tempe
       if (r0 > kMaxTailIncrement) { broken = true; continue; }
       if ((r0 | r1) == 0u && !t0 && !t1) continue;                 // cannot move the sum under either power of two
       const int b = tail_bucket(score, h.low_score, scale);
-      atomicAdd(&local[b], (static_cast<unsigned long long>(r1) << 32) | r0);
+      if (r0 != 0u) atomicAdd(&local0[b], r0);
+      if (r1 != 0u) atomicAdd(&local1[b], r1);
       if (t0 || t1) atomicOr(&local_ties[b], (t0 ? 1u : 0u) | (t1 ? 2u : 0u));
     }
     __syncthreads();
@@ -905,7 +967,8 @@ topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float tempe
   unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
   unsigned long long* sums = reinterpret_cast<unsigned long long*>(tail);
   for (int i = threadIdx.x; i < kTailBuckets; i += 256) {
-    if (local[i] != 0ull) atomicAdd(&sums[i], local[i]);
+    const unsigned long long both = (static_cast<unsigned long long>(local1[i]) << 32) | local0[i];
+    if (both != 0ull) atomicAdd(&sums[i], both);
     if (local_ties[i] != 0u) atomicOr(&tail[2 * kTailBuckets + i], local_ties[i]);
   }
 }
@@ -917,6 +980,7 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
                    const unsigned long long* keys, int64_t padded, const float* running, const unsigned int* tails,
                    const HeadState* heads, float top_p, unsigned long long seed, const unsigned long long* draw_offsets,
                    int32_t* out_ids, int* row_flags) {
+  dependent_launch_prologue();
   constexpr int kGroup = 64, kGroups = kTailBuckets / kGroup;   // the walk first steps over groups of 64 buckets
   __shared__ __align__(16) unsigned long long bucket_keys[kTailBuckets];
   __shared__ unsigned long long sums[kTailBuckets];          // (increments under k0 + 1) << 32 | (increments under k0)
@@ -982,8 +1046,15 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     const int b = walk_bucket;
     if (b >= kTailBuckets) break;
     // gather the terms of bucket b that can move the sum, sort them into the reference's order, add them one by one
+    // the bucket's range in logit units, a little wide (the exact test follows): most tokens leave after two comparisons
+    const float score_hi = h.low_score - float(b) / scale, score_lo = h.low_score - float(b + 1) / scale;
+    const float slack = 1e-5f * (fabsf(score_hi) + fabsf(score_lo)) + 2.0f / scale * 1e-3f;
+    const float logit_a = (score_hi + slack) * temperature, logit_b = (score_lo - slack) * temperature;
+    const float logit_hi = fmaxf(logit_a, logit_b) + 1e-5f * fabsf(fmaxf(logit_a, logit_b)) + 1e-30f;
+    const float logit_lo = fminf(logit_a, logit_b) - 1e-5f * fabsf(fminf(logit_a, logit_b)) - 1e-30f;
+    const bool last_bucket = b == kTailBuckets - 1;   // it also takes everything below its range
     auto consider = [&](float x, int64_t i) {
-      if (x >= threshold) return;
+      if (x >= threshold || x > logit_hi || (x < logit_lo && !last_bucket)) return;
       const float score = temperature == 1.0f ? x : __fdiv_rn(x, temperature);
       if (score < lowest || tail_bucket(score, h.low_score, scale) != b) return;
       const float e = expf(score - h.max_score);
@@ -999,12 +1070,12 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
       if (aligned16(src)) {
         const int64_t nvec = width / N;
         const uint4* vp = reinterpret_cast<const uint4*>(src);
-        for (int64_t v0 = tid; v0 < nvec; v0 += int64_t(kSortThreads) * 4) {   // four loads in flight per thread
-          uint4 r[4];
+        for (int64_t v0 = tid; v0 < nvec; v0 += int64_t(kSortThreads) * 8) {   // eight loads in flight per thread
+          uint4 r[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) if (v0 + q * kSortThreads < nvec) r[q] = ld_stream(vp + v0 + q * kSortThreads);
+          for (int q = 0; q < 8; ++q) if (v0 + q * kSortThreads < nvec) r[q] = ld_stream(vp + v0 + q * kSortThreads);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 8; ++q) {
             const int64_t v = v0 + q * kSortThreads;
             if (v < nvec) {
               float e[N];
@@ -1133,11 +1204,19 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
   auto* cut = reinterpret_cast<CutState*>(heads + rows);
   int* row_flags = reinterpret_cast<int*>(cut + rows);
   int* overflow = row_flags + rows;
-  // thread blocks per row for a pass over the logits: enough to fill the GPU over all rows and no more
-  int64_t spread64 = (int64_t(sm_count()) * 8 + rows - 1) / rows;
-  if (spread64 > padded / 1024) spread64 = padded / 1024;
-  if (spread64 < 1) spread64 = 1;
-  const dim3 row_grid = dim3(unsigned(spread64), unsigned(rows), 1);
+  // thread blocks per row for a pass over the logits: as many as run at once over all rows (asked of the occupancy
+  // calculator per kernel), so the pass is one wave and no block waits for a slot
+  auto row_grid_of = [&](auto kernel) {
+    int resident = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, 0) != cudaSuccess || resident < 1) {
+      cudaGetLastError();
+      resident = 4;
+    }
+    int64_t spread = int64_t(sm_count()) * resident / rows;
+    if (spread > padded / 1024) spread = padded / 1024;
+    if (spread < 1) spread = 1;
+    return dim3(unsigned(spread), unsigned(rows), 1);
+  };
   // logits / temperature stays a normal number near a threshold only for a moderate temperature (and a moderate
   // logit there, which the splitter kernel checks)
   const int safe = temperature >= 9.5367431640625e-07f && temperature <= 1048576.0f;   // 2^-20 .. 2^20
@@ -1156,20 +1235,20 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
     }
     if (dtype == B2_F32) {
       const float* x = static_cast<const float*>(logits);
-      topk_splitter_kernel<float><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
-      topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
+      launch_kernel(topk_splitter_kernel<float>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      launch_kernel(topk_gather_kernel<float>, dim3(row_grid_of(topk_gather_kernel<float>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, overflow, 0);
     } else {
       const __half* x = static_cast<const __half*>(logits);
-      topk_splitter_kernel<__half><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
-      topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, overflow, 0);
+      launch_kernel(topk_splitter_kernel<__half>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, unsigned(top_k), safe, cut, overflow, 0);
+      launch_kernel(topk_gather_kernel<__half>, dim3(row_grid_of(topk_gather_kernel<__half>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, overflow, 0);
     }
-    topk_finish_kernel<<<unsigned(rows), kSortThreads, kCandidates * 8, s>>>(keys, padded, top_k, cut, candidates, overflow);
+    launch_kernel(topk_finish_kernel, dim3(unsigned(rows)), dim3(kSortThreads), kCandidates * 8, s, keys, padded, top_k, cut, candidates, overflow);
     // ... unless that could not be trusted: then (and only then) the radix select over all 64 key bits redoes every row
     if (dtype == B2_F32)
-      topk_exact_kernel<float><<<unsigned(rows), kExactThreads, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
+      launch_kernel(topk_exact_kernel<float>, dim3(unsigned(rows)), dim3(kExactThreads), 0, s, static_cast<const float*>(logits), width, row_stride, padded,
                                                                         temperature, top_k, keys, overflow);
     else
-      topk_exact_kernel<__half><<<unsigned(rows), kExactThreads, 0, s>>>(static_cast<const __half*>(logits), width, row_stride,
+      launch_kernel(topk_exact_kernel<__half>, dim3(unsigned(rows)), dim3(kExactThreads), 0, s, static_cast<const __half*>(logits), width, row_stride,
                                                                          padded, temperature, top_k, keys, overflow);
   } else {
     if (top_k == 0 && top_p < 1.0f && width >= 4 * kCandidates && width <= kMaxToppWidth) {
@@ -1178,54 +1257,54 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
       if (cudaMemsetAsync(row_flags, 0, size_t(rows) * sizeof(int), s) != cudaSuccess) return launch_status("sample_rows");
       if (dtype == B2_F32) {
         const float* x = static_cast<const float*>(logits);
-        topk_splitter_kernel<float><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, 0u, safe, cut, row_flags, 1);
-        topk_gather_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        topp_pack_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, candidates, tails, row_flags);
-        bitonic_tile_registers_kernel<<<dim3(1, unsigned(rows)), kRegThreads, 0, s>>>(keys, padded, 2, kTile, RowSet{nullptr, nullptr});
-        topp_head_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, running, heads, row_flags);
-        topp_tail_kernel<float><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
-        topp_finish_kernel<float><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
+        launch_kernel(topk_splitter_kernel<float>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, 0u, safe, cut, row_flags, 1);
+        launch_kernel(topk_gather_kernel<float>, dim3(row_grid_of(topk_gather_kernel<float>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, row_flags, 1);
+        launch_kernel(topp_pack_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, candidates, tails, row_flags);
+        launch_kernel(bitonic_tile_registers_kernel, dim3(dim3(1, unsigned(rows))), dim3(kRegThreads), 0, s, keys, padded, 2, kTile, RowSet{nullptr, nullptr});
+        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, running, heads, row_flags);
+        launch_kernel(topp_tail_kernel<float>, dim3(row_grid_of(topp_tail_kernel<float>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, heads, tails, row_flags);
+        launch_kernel(topp_finish_kernel<float>, dim3(unsigned(rows)), dim3(kSortThreads), 0, s, x, width, row_stride, temperature, cut, keys, padded, running,
                                                                           tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
       } else {
         const __half* x = static_cast<const __half*>(logits);
-        topk_splitter_kernel<__half><<<unsigned(rows), kSplitThreads, 0, s>>>(x, width, row_stride, 0u, safe, cut, row_flags, 1);
-        topk_gather_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        topp_pack_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, candidates, tails, row_flags);
-        bitonic_tile_registers_kernel<<<dim3(1, unsigned(rows)), kRegThreads, 0, s>>>(keys, padded, 2, kTile, RowSet{nullptr, nullptr});
-        topp_head_kernel<<<unsigned(rows), 256, 0, s>>>(keys, padded, cut, running, heads, row_flags);
-        topp_tail_kernel<__half><<<row_grid, 256, 0, s>>>(x, width, row_stride, temperature, cut, heads, tails, row_flags);
-        topp_finish_kernel<__half><<<unsigned(rows), kSortThreads, 0, s>>>(x, width, row_stride, temperature, cut, keys, padded, running,
+        launch_kernel(topk_splitter_kernel<__half>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, 0u, safe, cut, row_flags, 1);
+        launch_kernel(topk_gather_kernel<__half>, dim3(row_grid_of(topk_gather_kernel<__half>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, row_flags, 1);
+        launch_kernel(topp_pack_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, candidates, tails, row_flags);
+        launch_kernel(bitonic_tile_registers_kernel, dim3(dim3(1, unsigned(rows))), dim3(kRegThreads), 0, s, keys, padded, 2, kTile, RowSet{nullptr, nullptr});
+        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, running, heads, row_flags);
+        launch_kernel(topp_tail_kernel<__half>, dim3(row_grid_of(topp_tail_kernel<__half>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, heads, tails, row_flags);
+        launch_kernel(topp_finish_kernel<__half>, dim3(unsigned(rows)), dim3(kSortThreads), 0, s, x, width, row_stride, temperature, cut, keys, padded, running,
                                                                            tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
       }
       // the rows whose flag is up, as a list: the kernels of the whole-row sort walk it
       int* row_list = overflow + 4;
-      list_rows_kernel<<<1, 256, 0, s>>>(row_flags, int(rows), row_list, overflow + 1);
+      launch_kernel(list_rows_kernel, dim3(1), dim3(256), 0, s, row_flags, int(rows), row_list, overflow + 1);
       todo = RowSet{row_list, overflow + 1};
       row_blocks = unsigned(rows < kListedRowBlocks ? rows : kListedRowBlocks);
     }
     // the whole-row sort has little per-block overhead: many small blocks
     const dim3 wide_grid(unsigned(padded / 256 < 1 ? 1 : (padded / 256 > 296 ? 296 : padded / 256)), row_blocks);
     if (dtype == B2_F32)
-      sampler_keys_kernel<float><<<wide_grid, 256, 0, s>>>(static_cast<const float*>(logits), width, row_stride, padded,
+      launch_kernel(sampler_keys_kernel<float>, dim3(wide_grid), dim3(256), 0, s, static_cast<const float*>(logits), width, row_stride, padded,
                                                             temperature, keys, todo);
     else
-      sampler_keys_kernel<__half><<<wide_grid, 256, 0, s>>>(static_cast<const __half*>(logits), width, row_stride, padded,
+      launch_kernel(sampler_keys_kernel<__half>, dim3(wide_grid), dim3(256), 0, s, static_cast<const __half*>(logits), width, row_stride, padded,
                                                            temperature, keys, todo);
     const int tile = int(padded < kTile ? padded : kTile);
     const dim3 tile_grid(unsigned(padded / tile), row_blocks);
     if (tile < kTile) {
-      bitonic_tile_kernel<<<tile_grid, kSortThreads, size_t(tile) * 8, s>>>(keys, padded, tile, 2, tile, todo);   // the whole row is one small tile
+      launch_kernel(bitonic_tile_kernel, dim3(tile_grid), dim3(kSortThreads), size_t(tile) * 8, s, keys, padded, tile, 2, tile, todo);   // the whole row is one small tile
     } else {
-      bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, 2, kTile, todo);
+      launch_kernel(bitonic_tile_registers_kernel, dim3(tile_grid), dim3(kRegThreads), 0, s, keys, padded, 2, kTile, todo);
       for (int64_t k = int64_t(kTile) * 2; k <= padded; k <<= 1) {
         int64_t j = k >> 1;
-        for (; j >= 2 * kTile; j >>= 2) bitonic_wide_pair_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, todo);   // steps j and j/2
-        if (j >= kTile) bitonic_wide_kernel<<<wide_grid, 256, 0, s>>>(keys, padded, k, j, todo);                   // one step left over
-        bitonic_tile_registers_kernel<<<tile_grid, kRegThreads, 0, s>>>(keys, padded, k, k, todo);
+        for (; j >= 2 * kTile; j >>= 2) launch_kernel(bitonic_wide_pair_kernel, dim3(wide_grid), dim3(256), 0, s, keys, padded, k, j, todo);   // steps j and j/2
+        if (j >= kTile) launch_kernel(bitonic_wide_kernel, dim3(wide_grid), dim3(256), 0, s, keys, padded, k, j, todo);                   // one step left over
+        launch_kernel(bitonic_tile_registers_kernel, dim3(tile_grid), dim3(kRegThreads), 0, s, keys, padded, k, k, todo);
       }
     }
   }
-  sampler_pick_kernel<<<row_blocks, kSelectThreads, 0, s>>>(keys, width, padded, top_k, top_p, seed, draw_offsets, running, out_ids,
+  launch_kernel(sampler_pick_kernel, dim3(row_blocks), dim3(kSelectThreads), 0, s, keys, width, padded, top_k, top_p, seed, draw_offsets, running, out_ids,
                                                             todo);
   return launch_status("sample_rows");
 }

@@ -134,8 +134,9 @@ __device__ __forceinline__ int32_t winner_index(unsigned long long best) {   // 
 }
 constexpr int32_t kInvalidIndex = -1;   // written for rows whose exchange did not complete in time
 
+// (the register cap keeps the occupancy of the plain kernel: what the rarely run tail needs beyond it spills)
 template <typename T, bool kVec, int kBlock>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, kBlock >= 1024 ? 2 : 8)
 argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_t row_stride, int64_t chunk, int chunks,
                             int64_t index_base, int32_t* out_ids, unsigned long long* keys, unsigned int* tickets,
                             const __grid_constant__ ExchangeArgs xa) {
@@ -689,7 +690,7 @@ softmax_stats_kernel(const T* x, int64_t width, float* row_max, float* row_sum) 
 // row waits (bounded) for the peers' pairs and writes the statistics of the WHOLE row, ready for
 // softmax_apply_kernel.
 template <typename T, bool kVec>
-__global__ void __launch_bounds__(kSoftThreads)
+__global__ void __launch_bounds__(kSoftThreads, 3)   // the tail's registers beyond the cap spill; the row loop's do not
 softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* global_max, float* global_sum,
                               const __grid_constant__ ExchangeArgs xa) {
   constexpr int N = Elem<T>::kPerVec;
