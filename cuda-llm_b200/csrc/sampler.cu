@@ -861,24 +861,25 @@ topp_head_kernel(const unsigned long long* keys, int64_t padded, const CutState*
 // tail: increments of every term below the head, per bucket, for the head's power of two and the next one.
 // Per bucket one 64-bit word (increments under k + 1 << 32 | increments under k) and one word of tie flags
 // (bit 0: a tie under k, bit 1: under k + 1).  A term of more than 4096 units does not belong in a tail (the sums of
-// up to 2^19 of them must stay below 2^32): the row is handed to the whole-row sort.
-constexpr unsigned int kMaxTailIncrement = 4096;   // times at most kMaxToppWidth terms: a bucket's sum fits 32 bits
-constexpr int64_t kMaxToppWidth = int64_t(1) << 19;
+// up to 2^18 of them must stay below 2^32): the row is handed to the whole-row sort.
+constexpr unsigned int kMaxTailIncrement = 4096;   // times at most kMaxToppWidth terms: a bucket's sum fits 30 bits
+constexpr int64_t kMaxToppWidth = int64_t(1) << 18;
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float temperature, const CutState* cut,
                  const HeadState* heads, unsigned int* tails, int* row_flags) {
   dependent_launch_prologue();
   constexpr int N = Elem<T>::kPerVec, kVecs = 16 / N;          // 16 elements per thread and turn
   constexpr int kQueue = 256 * 16;
-  __shared__ unsigned int local0[kTailBuckets], local1[kTailBuckets];   // 32-bit: shared memory adds those natively
-  __shared__ unsigned int local_ties[kTailBuckets];
+  // 32-bit words: shared memory adds those natively.  A thread block's sums stay below 2^29 (at most 2^18 tokens of
+  // at most 2^11 units under the doubled unit), so the two tie flags ride in bits 30 and 31 of local1
+  __shared__ unsigned int local0[kTailBuckets], local1[kTailBuckets];
   __shared__ float queue[kQueue];
   __shared__ unsigned int queued;
   const int64_t row = blockIdx.y;
   if (row_flags[row] != 0) return;
-  for (int i = threadIdx.x; i < kTailBuckets; i += 256) { local0[i] = 0u; local1[i] = 0u; local_ties[i] = 0u; }
+  for (int i = threadIdx.x; i < kTailBuckets; i += 256) { local0[i] = 0u; local1[i] = 0u; }
   if (threadIdx.x == 0) queued = 0u;
   __syncthreads();
   const HeadState h = heads[row];
@@ -919,7 +920,7 @@ topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float tempe
       const int b = tail_bucket(score, h.low_score, scale);
       if (r0 != 0u) atomicAdd(&local0[b], r0);
       if (r1 != 0u) atomicAdd(&local1[b], r1);
-      if (t0 || t1) atomicOr(&local_ties[b], (t0 ? 1u : 0u) | (t1 ? 2u : 0u));
+      if (t0 || t1) atomicOr(&local1[b], (t0 ? 1u << 30 : 0u) | (t1 ? 1u << 31 : 0u));
     }
     __syncthreads();
     if (threadIdx.x == 0) queued = 0u;
@@ -935,14 +936,36 @@ topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float tempe
       const int64_t v0 = first + turn * stride * kVecs;
       uint4 r[kVecs];
 #pragma unroll
-      for (int q = 0; q < kVecs; ++q) if (v0 + q * stride < nvec) r[q] = ld_stream(vp + v0 + q * stride);
+      for (int q = 0; q < kVecs; ++q) r[q] = v0 + q * stride < nvec ? ld_stream(vp + v0 + q * stride) : make_uint4(0u, 0u, 0u, 0u);
+      // count this thread's 16 tokens first; the warp then takes room in the queue with ONE atomic (a ballot and
+      // an atomic per token cost more instructions than the comparison they serve)
+      float e[kVecs][N];
+      unsigned int hits = 0u, count = 0u;
 #pragma unroll
       for (int q = 0; q < kVecs; ++q) {
-        float e[N];
+        Elem<T>::unpack(r[q], e[q]);
         const bool in = v0 + q * stride < nvec;
-        if (in) Elem<T>::unpack(r[q], e);
 #pragma unroll
-        for (int z = 0; z < N; ++z) select(in ? e[z] : INFINITY);   // +inf is never selected
+        for (int z = 0; z < N; ++z)
+          if (in && e[q][z] < threshold && e[q][z] >= cut_logit) { hits |= 1u << (q * N + z); ++count; }
+      }
+      if (__any_sync(0xffffffffu, count != 0u)) {
+        unsigned int before = count;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+          const unsigned int up = __shfl_up_sync(0xffffffffu, before, offset);
+          if (lane >= offset) before += up;
+        }
+        const unsigned int total = __shfl_sync(0xffffffffu, before, 31);
+        unsigned int base = 0u;
+        if (lane == 0) base = atomicAdd(&queued, total);
+        unsigned int slot = __shfl_sync(0xffffffffu, base, 0) + before - count;
+#pragma unroll
+        for (int q = 0; q < kVecs; ++q) {
+#pragma unroll
+          for (int z = 0; z < N; ++z)
+            if (hits >> (q * N + z) & 1u) queue[slot++] = e[q][z];
+        }
       }
       work_queue();
     }
@@ -967,9 +990,10 @@ topp_tail_kernel(const T* logits, int64_t width, int64_t row_stride, float tempe
   unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
   unsigned long long* sums = reinterpret_cast<unsigned long long*>(tail);
   for (int i = threadIdx.x; i < kTailBuckets; i += 256) {
-    const unsigned long long both = (static_cast<unsigned long long>(local1[i]) << 32) | local0[i];
+    const unsigned int ties = local1[i] >> 30;
+    const unsigned long long both = (static_cast<unsigned long long>(local1[i] & 0x3fffffffu) << 32) | local0[i];
     if (both != 0ull) atomicAdd(&sums[i], both);
-    if (local_ties[i] != 0u) atomicOr(&tail[2 * kTailBuckets + i], local_ties[i]);
+    if (ties != 0u) atomicOr(&tail[2 * kTailBuckets + i], ties);
   }
 }
 
@@ -1005,7 +1029,7 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     unsigned long long total = 0ull;
     unsigned int any = 0u;
     for (int i = 0; i < kGroup; ++i) { total += sums[tid * kGroup + i]; any |= ties[tid * kGroup + i]; }
-    group_sums[tid] = total;      // each half stays below 2^32: at most 2^19 terms of at most 4096 units
+    group_sums[tid] = total;      // each half stays below 2^32: at most 2^18 terms of at most 4096 units
     group_ties[tid] = any;
   }
   const float threshold = cut[row].threshold, scale = tail_scale(h);
