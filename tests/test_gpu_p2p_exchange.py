@@ -47,10 +47,10 @@ def stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-@pytest.mark.parametrize("world", [1, 2, 8])
-def test_fused_argmax_ranks_in_turn(b2, port, world):
+# 128 rows over 8 shards: short shards and enough rows to fill the GPU take the one-block-per-row form of the kernel
+@pytest.mark.parametrize("world,rows", [(1, 64), (2, 64), (8, 64), (8, 128), (4, 256)])
+def test_fused_argmax_ranks_in_turn(b2, port, world, rows):
     L = b2
-    rows = 64
     c5 = wl.config5(rows=rows)
     x = c5["logits"]
     x[5, :] = -np.inf                                   # no candidate anywhere: index 0
