@@ -338,6 +338,10 @@ B2_API int b2_select_last_valid_rows(const void* padded, const int32_t* valid_le
  * draw_offsets: device uint64[rows], or NULL for offset 0 on every row.
  * workspace: b2_sampler_workspace_bytes(rows, width) bytes of scratch, no initialisation needed; calls
  * that share it must not overlap on the device.
+ * Three routes, all exact: 0 < top_k <= 2048 makes one pass over the logits (a sampled threshold, checked);
+ * top_k == 0 with top_p < 1 and 32768 <= width <= 262144 sorts only the row's largest ~2800 tokens and adds
+ * the rest of the softmax sum from per-bucket integer increments (rows with a flat distribution, whose top-p
+ * prefix does not end among those tokens, are redone by the third route); everything else sorts the whole row.
  * Replaces CudaSampler::sample_row / sample_last_row / sample_last_token_of_batch, kernels sampler_fill and
  * sampler_select and the library sort between them (include/llm/ops_cuda.h:46-74;
  * src/ops_cuda.cu:575-617,886-971), which handle one row per blocking call. */
