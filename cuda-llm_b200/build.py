@@ -24,6 +24,11 @@ NVCC_FLAGS = [
 ]
 
 
+# sources whose kernels launch other kernels from the device (the sampler's rarely needed whole-row route is launched
+# by the kernel that finds out whether it is needed): relocatable device code, linked against the device runtime
+RDC_SOURCES = {"sampler_fallback.cu"}
+
+
 def _newer(target: str, sources) -> bool:
     if not os.path.exists(target):
         return False
@@ -54,6 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if not force and _newer(obj, [src] + headers):
             return obj, ""
         cmd = [nvcc] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + \
+            (["-rdc=true"] if os.path.basename(src) in RDC_SOURCES else []) + \
             ["-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
@@ -65,7 +71,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         for _, log in results:
             sys.stderr.write(log)
-    proc = subprocess.run([nvcc, "-shared", "-o", LIB] + [obj for obj, _ in results], capture_output=True, text=True)
+    proc = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] +
+                          [obj for obj, _ in results] + ["-lcudadevrt"], capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc (link) failed:\n" + proc.stdout + proc.stderr)
     return LIB

@@ -120,9 +120,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // Kernels of a decode step last a few microseconds, about as long as the gap between two launches: with both
 // instructions at the top of a kernel the gap is spent under the previous kernel.  Without the launch attribute
 // both instructions do nothing.
+// A translation unit whose kernels are launched from the device defines B2_NO_DEPENDENT_LAUNCH: those kernels take
+// no part in this (a grid that early-launched dependents wait on must not need new blocks scheduled to finish,
+// and a grid with child grids does).
 __device__ __forceinline__ void dependent_launch_prologue() {
+#ifndef B2_NO_DEPENDENT_LAUNCH
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
 }
 
 // ---- host-side launch helpers -------------------------------------------------

@@ -157,6 +157,48 @@ def test_draws_follow_the_retained_distribution(b2, port):
     assert np.abs(freq - p).max() < 4 * np.sqrt(0.25 / n)
 
 
+def test_rows_handed_back_by_the_top_p_route_inside_a_graph_and_before_other_kernels(b2, port):
+    """Rows the top-p route cannot settle (flat rows, long ties) are redone by kernels launched from the device.
+    The same call recorded into a CUDA graph and replayed, with another operator of the library queued right
+    behind it (a kernel that may start early under programmatic serialisation), gives the same tokens."""
+    from cuda_llm_b200 import lib
+    L = b2
+    rows, width = 8, wl.VOCAB
+    x = rows_for(width, rows, 4242, np.float32, "ties")          # rows 1 and 2 are flat: they take the whole-row route
+    t = dev(x)
+    cfg = SamplingConfig(1.0, 0, 0.9, 31)
+    offsets = np.arange(rows, dtype=np.int64) * 7 + 1
+    off = dev(offsets)
+    want = [port.sample_row(x[r], cfg.temperature, cfg.top_k, cfg.top_p, cfg.seed, int(offsets[r])) for r in range(rows)]
+    ws = torch.zeros(L.b2_sampler_workspace_bytes(rows, width), dtype=torch.uint8, device=DEV)
+    a = torch.ones(1 << 20, dtype=torch.float16, device=DEV)
+    b = torch.full((1 << 20,), 2.0, dtype=torch.float16, device=DEV)
+    c = torch.zeros(1 << 20, dtype=torch.float16, device=DEV)
+
+    def step(out, stream):
+        lib.check(L.b2_sample_rows(t.data_ptr(), rows, width, width, lib.F32, cfg.temperature, cfg.top_k, cfg.top_p, cfg.seed,
+                                   off.data_ptr(), out.data_ptr(), ws.data_ptr(), stream))
+        lib.check(L.b2_add(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.numel(), lib.F16, stream))
+
+    eager = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        step(eager, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    for r in range(rows):
+        assert int(eager[r]) == want[r][0] or want[r][1] < 1e-5, f"row {r}"
+    assert float(c[12345]) == 3.0
+    replayed = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step(replayed, side.cuda_stream)
+    for _ in range(2):
+        replayed.fill_(-1)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed, eager)
+
+
 def test_c_abi_argument_rules(b2):
     from cuda_llm_b200 import lib
     L = b2
