@@ -101,7 +101,7 @@ topk_exact_kernel(const T* logits, int64_t width, int64_t row_stride, int64_t pa
 }
 
 // ---- small top_k, the usual case: ONE pass over the logits and no key array.
-//   splitter  a thread block per row looks at 8192 logits of the row (1024 evenly spaced runs of eight) and takes, as threshold, the
+//   splitter  a thread block per row looks at 8192 logits of the row (256 evenly spaced runs of 32) and takes, as threshold, the
 //             sample whose rank makes "a few times top_k, and with near certainty at least top_k" tokens of the
 //             whole row lie above it, lowered by 2^-12 of its magnitude
 //   gather    the one pass: every token whose logit is at or above the threshold has its exact score computed and
@@ -158,9 +158,9 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
     const int sidx = threadIdx.x + q * kSplitThreads;
     mine[q] = 0u;
     if (sidx < samples) {
-      // runs of eight neighbouring tokens, the runs evenly spaced: one 32-byte sector per run instead of one per
-      // sample (samples every 18 tokens would touch every sector of the row: a whole extra pass over the logits)
-      const float x = Elem<T>::load(src + (int64_t(sidx >> 3) * width) / (samples >> 3) + (sidx & 7));
+      // runs of 32 neighbouring tokens, the runs evenly spaced: one 128-byte line per run instead of one sector
+      // per sample (samples every 18 tokens would touch every sector of the row: a whole extra pass over the logits)
+      const float x = Elem<T>::load(src + (int64_t(sidx >> 5) * width) / (samples >> 5) + (sidx & 31));
       mine[q] = x == x ? ordered_bits(x) : 0u;                                   // a NaN never ranks
     }
   }
@@ -455,53 +455,67 @@ __device__ __forceinline__ float tail_scale(const HeadState& h) {
   return span > 1e-6f ? float(kTailBuckets) / span : 0.0f;
 }
 
-// head, step 1: the row's candidates (at most one 4096-key tile of them) move to the front of the row's key area,
-// padded with zeros; the register-tile kernel of the whole-row sort then sorts that one tile per row.
-__global__ void __launch_bounds__(256)
-topp_pack_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
-                 unsigned int* tails, int* row_flags) {
+// head: the row's candidates (at most one 4096-key tile of them) are sorted in registers (the network of the whole-row
+// sort's tile kernel), written to the front of the row's key area for the finish kernel, and their exponentials
+// are added in order by one thread, every running sum kept.  One kernel: the keys go from the candidate list
+// through registers and shared memory to the sums without a round trip through global memory in between.
+__global__ void __launch_bounds__(kRegThreads)
+topp_head_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
+                 unsigned int* tails, float* running, HeadState* heads, int* row_flags) {
   dependent_launch_prologue();
-  const int64_t row = blockIdx.x;
-  // the tail pass adds into these: they start at zero
-  unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
-  for (int i = threadIdx.x; i < 3 * kTailBuckets; i += 256) tail[i] = 0u;
-  if (row_flags[row] != 0) return;
-  const unsigned int count = cut[row].taken;
-  if (count < unsigned(kMinHead) || count > unsigned(kTile)) {
-    if (threadIdx.x == 0) row_flags[row] = 1;
-    return;
-  }
-  const unsigned long long* in = candidates + row * int64_t(kCandidates);
-  unsigned long long* dst = keys + row * padded;
-  for (int i = threadIdx.x; i < kTile; i += 256) dst[i] = unsigned(i) < count ? in[i] : 0ull;
-}
-
-// head, step 2 (after the sort): the exponentials of the head in order, added by one thread, every running sum kept
-__global__ void __launch_bounds__(256)
-topp_head_kernel(const unsigned long long* keys, int64_t padded, const CutState* cut, float* running, HeadState* heads,
-                 const int* row_flags) {
-  dependent_launch_prologue();
+  __shared__ unsigned long long tile[kTile];
   __shared__ __align__(16) float stage[kChunk];
   __shared__ float carry;
   const int64_t row = blockIdx.x;
+  const int t = threadIdx.x, lane = t & 31;
+  // the tail pass adds into these: they start at zero
+  unsigned int* tail = tails + row * int64_t(3 * kTailBuckets);
+  for (int i = t; i < 3 * kTailBuckets; i += kRegThreads) tail[i] = 0u;
   if (row_flags[row] != 0) return;
-  const int tid = threadIdx.x;
-  const int count = int(cut[row].taken);
-  const unsigned long long* sorted = keys + row * padded;
-  const float maximum = key_score(sorted[0]);
-  float* cum = running + row * padded;
-  if (tid == 0) carry = 0.0f;
+  const unsigned int taken = cut[row].taken;
+  if (taken < unsigned(kMinHead) || taken > unsigned(kTile)) {
+    if (t == 0) row_flags[row] = 1;
+    return;
+  }
+  const int count = int(taken);
+  const unsigned long long* in = candidates + row * int64_t(kCandidates);
+  unsigned long long key[kRegKeys];
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) key[r] = r * kRegThreads + t < count ? in[r * kRegThreads + t] : 0ull;   // layout S
+  const int64_t first_global = int64_t(t) * kRegKeys;
+  layout_s_to_b(key, tile, t);
+  for (int64_t k = 2; k <= kTile; k <<= 1) {
+    const int top = int(k >> 1);
+    if (top >= 512) {
+      layout_b_to_s(key, tile, t);
+      steps_in_registers_s(key, 0, t, k, top);
+      layout_s_to_b(key, tile, t);
+    }
+    if (top >= 16) steps_by_shuffle_b(key, first_global, k, top < 256 ? top : 256, lane);
+    steps_in_registers_b(key, first_global, k, top < 8 ? top : 8);
+  }
+  layout_b_to_s(key, tile, t);
+  __syncthreads();                                   // the transposes are done with the tile
+  unsigned long long* dst = keys + row * padded;
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) {
+    tile[r * kRegThreads + t] = key[r];              // in order, for the sums below
+    dst[r * kRegThreads + t] = key[r];               // and for the finish kernel
+  }
+  if (t == 0) carry = 0.0f;
   __syncthreads();
+  const float maximum = key_score(tile[0]);
+  float* cum = running + row * padded;
   for (int base = 0; base < count; base += kChunk) {
     const int m = count - base < kChunk ? count - base : kChunk;
-    for (int j = tid; j < m; j += 256) stage[j] = expf(key_score(sorted[base + j]) - maximum);
+    for (int j = t; j < m; j += kRegThreads) stage[j] = expf(key_score(tile[base + j]) - maximum);
     __syncthreads();
-    if (tid == 0) carry = running_sums_in_order(stage, m, carry);
+    if (t == 0) carry = running_sums_in_order(stage, m, carry);
     __syncthreads();
-    for (int j = tid; j < m; j += 256) cum[base + j] = stage[j];
+    for (int j = t; j < m; j += kRegThreads) cum[base + j] = stage[j];
     __syncthreads();
   }
-  if (tid == 0) heads[row] = HeadState{carry, maximum, key_score(sorted[count - 1]), count};
+  if (t == 0) heads[row] = HeadState{carry, maximum, key_score(tile[count - 1]), count};
 }
 
 // tail: increments of every term below the head, per bucket, for the head's power of two and the next one.
@@ -928,9 +942,7 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
         const float* x = static_cast<const float*>(logits);
         launch_kernel(topk_splitter_kernel<float>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, 0u, safe, cut, row_flags, 1);
         launch_kernel(topk_gather_kernel<float>, dim3(row_grid_of(topk_gather_kernel<float>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        launch_kernel(topp_pack_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, candidates, tails, row_flags);
-        launch_kernel(bitonic_tile_registers_kernel, dim3(dim3(1, unsigned(rows))), dim3(kRegThreads), 0, s, keys, padded, 2, kTile, RowSet{nullptr, nullptr});
-        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, running, heads, row_flags);
+        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(kRegThreads), 0, s, keys, padded, cut, candidates, tails, running, heads, row_flags);
         launch_kernel(topp_tail_kernel<float>, dim3(row_grid_of(topp_tail_kernel<float>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, heads, tails, row_flags);
         launch_kernel(topp_finish_kernel<float>, dim3(unsigned(rows)), dim3(kSortThreads), 0, s, x, width, row_stride, temperature, cut, keys, padded, running,
                                                                           tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
@@ -938,9 +950,7 @@ int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t 
         const __half* x = static_cast<const __half*>(logits);
         launch_kernel(topk_splitter_kernel<__half>, dim3(unsigned(rows)), dim3(kSplitThreads), 0, s, x, width, row_stride, 0u, safe, cut, row_flags, 1);
         launch_kernel(topk_gather_kernel<__half>, dim3(row_grid_of(topk_gather_kernel<__half>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, candidates, row_flags, 1);
-        launch_kernel(topp_pack_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, candidates, tails, row_flags);
-        launch_kernel(bitonic_tile_registers_kernel, dim3(dim3(1, unsigned(rows))), dim3(kRegThreads), 0, s, keys, padded, 2, kTile, RowSet{nullptr, nullptr});
-        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(256), 0, s, keys, padded, cut, running, heads, row_flags);
+        launch_kernel(topp_head_kernel, dim3(unsigned(rows)), dim3(kRegThreads), 0, s, keys, padded, cut, candidates, tails, running, heads, row_flags);
         launch_kernel(topp_tail_kernel<__half>, dim3(row_grid_of(topp_tail_kernel<__half>)), dim3(256), 0, s, x, width, row_stride, temperature, cut, heads, tails, row_flags);
         launch_kernel(topp_finish_kernel<__half>, dim3(unsigned(rows)), dim3(kSortThreads), 0, s, x, width, row_stride, temperature, cut, keys, padded, running,
                                                                            tails, heads, top_p, seed, draw_offsets, out_ids, row_flags);
