@@ -96,8 +96,9 @@ __device__ __forceinline__ void exchange_send(const ExchangeArgs& xa, uint32_t e
 
 // Called by the thread that has stored a row's partial into this GPU's OWN slot: true for exactly one thread
 // per call, the one that finished the last row.
+// No fence orders the slot store before this count: the tail does not trust the count for the data, it polls its
+// own slots like the peers' until each carries the call's epoch.
 __device__ __forceinline__ bool exchange_row_done(const ExchangeArgs& xa, int64_t rows) {
-  __threadfence();
   return atomicAdd(exchange_done(xa.buf[xa.rank]), 1u) == uint32_t(rows - 1);
 }
 
@@ -109,12 +110,12 @@ __device__ __forceinline__ void exchange_trace_start(const ExchangeArgs& xa) {
 // is called for rows handed out thread by thread; partial_of(g), g a compile-time-unrolled or runtime index below
 // `world`, returns GPU g's partial of that row; `complete` is false when some GPU's partial had not arrived when the
 // time ran out (the row's result must then be marked invalid, and the partials of the missing GPUs are undefined).
+// `epoch` is the call's epoch as every thread block of the call read it (exchange_call_epoch at kernel start).
 template <typename Combine>
-__device__ __forceinline__ void exchange_tail(const ExchangeArgs& xa, int64_t rows, Combine&& combine) {
+__device__ __forceinline__ void exchange_tail(const ExchangeArgs& xa, int64_t rows, uint32_t epoch, Combine&& combine) {
   unsigned char* own = xa.buf[xa.rank];
   const int tid = threadIdx.x, threads = blockDim.x;
-  __threadfence();   // the other thread blocks' own-slot stores (ordered before their tickets) are visible here
-  const uint32_t epoch = *exchange_epoch(own) + 1u, parity = epoch & 1u;
+  const uint32_t parity = epoch & 1u;
   const unsigned long long start = global_timer_ns();
   if (xa.trace != nullptr) {
     if (tid == 0) xa.trace[1] = start;

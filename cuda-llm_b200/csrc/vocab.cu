@@ -143,9 +143,13 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
   __shared__ float warp_v[kBlock / kWarpSize];
   __shared__ int warp_i[kBlock / kWarpSize];
   __shared__ unsigned long long row_key;
-  __shared__ uint32_t call_epoch;   // read by thread 0 BEFORE it takes the row's ticket: the last row's tail rewrites the stored epoch
+  __shared__ uint32_t call_epoch;
   __shared__ int state;   // 0: this row is not finished yet, 1: finished (send its key), 2: and it was the last row
   exchange_trace_start(xa);
+  // the call's epoch, fetched under the scan of the row (the stored value changes only at the very end of a call,
+  // when every thread block has long read it)
+  uint32_t epoch = 0u;
+  if (threadIdx.x == 0) epoch = exchange_call_epoch(xa);
   const int64_t row = blockIdx.x / chunks;
   const int c = int(blockIdx.x - row * chunks);
   const int64_t lo = int64_t(c) * chunk;
@@ -180,22 +184,22 @@ argmax_rows_exchange_kernel(const T* logits, int64_t rows, int64_t width, int64_
         tickets[row] = 0u;
       }
     }
-    int st = 0;
-    if (row_finished) {
-      const uint32_t epoch = exchange_call_epoch(xa);
-      row_key = key;
-      call_epoch = epoch;
-      exchange_send(xa, epoch, xa.rank, row, key);
-      st = exchange_row_done(xa, rows) ? 2 : 1;
-    }
-    state = st;
+    row_key = key;
+    call_epoch = epoch;
+    state = row_finished ? 1 : 0;
   }
   __syncthreads();
   if (state == 0) return;
-  // threads 1 .. world-1: one peer each
+  // the row's key leaves for the peers first (threads 1 .. world-1: one peer each) while thread 0 stores this GPU's
+  // own slot and counts the row
   if (threadIdx.x > 0 && threadIdx.x < xa.world) exchange_send(xa, call_epoch, (xa.rank + threadIdx.x) % xa.world, row, row_key);
+  if (threadIdx.x == 0) {
+    exchange_send(xa, epoch, xa.rank, row, row_key);
+    if (exchange_row_done(xa, rows)) state = 2;
+  }
+  __syncthreads();
   if (state != 2) return;
-  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
+  exchange_tail(xa, rows, call_epoch, [&](int64_t r, bool complete, auto partial_of) {
     unsigned long long best = 0ull;
 #pragma unroll
     for (int g = 0; g < kMaxWorld; ++g)
@@ -215,7 +219,7 @@ argmax_keys_exchange_kernel(const int64_t* keys, int64_t rows, int32_t* out_ids,
     for (int g = 0; g < xa.world; ++g) exchange_send(xa, epoch, (xa.rank + g) % xa.world, r, key);
   }
   __syncthreads();   // nobody rewrites the stored epoch (end of the tail) before every thread has read it
-  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
+  exchange_tail(xa, rows, epoch, [&](int64_t r, bool complete, auto partial_of) {
     unsigned long long best = 0ull;
 #pragma unroll
     for (int g = 0; g < kMaxWorld; ++g)
@@ -698,6 +702,7 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
   __shared__ int run_tail;
   __shared__ uint32_t call_epoch;
   exchange_trace_start(xa);
+  if (threadIdx.x == 0) call_epoch = exchange_call_epoch(xa);   // fetched under the scan of the row; published by the barriers of the reductions below
   const int64_t row = blockIdx.x;
   const T* src = x + row * width;
   const int64_t step = blockDim.x;
@@ -728,16 +733,15 @@ softmax_stats_exchange_kernel(const T* x, int64_t rows, int64_t width, float* gl
   // every thread holds the row's (max, sum): thread 0 stores this GPU's own slot and takes the ticket, threads
   // 1 .. world-1 send the pair to one peer each
   const unsigned long long pair = (static_cast<unsigned long long>(__float_as_uint(s)) << 32) | __float_as_uint(big);
+  // (block_max / block_sum above end with barriers: call_epoch is visible to every thread)
+  if (threadIdx.x > 0 && threadIdx.x < xa.world) exchange_send(xa, call_epoch, (xa.rank + threadIdx.x) % xa.world, row, pair);
   if (threadIdx.x == 0) {
-    const uint32_t epoch = exchange_call_epoch(xa);   // before the ticket: the last row's tail rewrites the stored epoch
-    call_epoch = epoch;
-    exchange_send(xa, epoch, xa.rank, row, pair);
+    exchange_send(xa, call_epoch, xa.rank, row, pair);
     run_tail = exchange_row_done(xa, rows) ? 1 : 0;
   }
   __syncthreads();
-  if (threadIdx.x > 0 && threadIdx.x < xa.world) exchange_send(xa, call_epoch, (xa.rank + threadIdx.x) % xa.world, row, pair);
   if (!run_tail) return;
-  exchange_tail(xa, rows, [&](int64_t r, bool complete, auto partial_of) {
+  exchange_tail(xa, rows, call_epoch, [&](int64_t r, bool complete, auto partial_of) {
     float top = -INFINITY;
 #pragma unroll
     for (int g = 0; g < kMaxWorld; ++g)
