@@ -401,8 +401,8 @@ topk_finish_kernel(unsigned long long* keys, int64_t padded, int top_k, const Cu
 //           the reference's single thread does.
 // A row that breaks an assumption (fewer than 64 or more than 4096 head candidates, a NaN, the sum growing by more
 // than one power of two in the tail, a bucket of more than 2048 terms, a prefix that does not end inside the head)
-// raises its flag and is redone by the whole-row sort; those kernels are launched in any case and return at once for
-// the rows whose flag is down.
+// raises its flag and is redone by the whole-row sort, over exactly those rows: launched from the device by the
+// kernel that lists them, and only when there are any (sampler_fallback.cu).
 constexpr int kTailBuckets = 2048;
 constexpr int kMinHead = 64;
 
