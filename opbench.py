@@ -134,7 +134,7 @@ def run(L, lib, dev, stream, world, rank, barrier, max_over_ranks, quick=False, 
             record("device copy (library kernel, yardstick only)", label, 2 * nbytes, ms)
             del bufs
     if world == 1 and (want("sampler") or want("kvmove")):
-        _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows)
+        _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows, stream)
     if world == 1 and want("decode_chain"):
         _decode_chain(L, lib, dev, stream, timed, table)
     if world == 1 and want("lm_head"):
@@ -269,7 +269,7 @@ def _lm_head_other_hidden_sizes(L, lib, dev, s, timed, record, randn, nreps):
         del table
 
 
-def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows=256):
+def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows=256, stream=None):
     """The callers either side of the path: sampling over the LM-head logits, paged-KV row writes, last-valid-row gather."""
     F16, F32 = lib.F16, lib.F32
     if want("sampler"):
@@ -279,12 +279,35 @@ def _next_rows(L, lib, dev, s, timed, record, randn, want, nreps, sampler_rows=2
         offs = torch.arange(R, dtype=torch.int64, device=dev)
         ws = torch.empty(L.b2_sampler_workspace_bytes(R, VOCAB), dtype=torch.uint8, device=dev)
         for label, temp, top_k, top_p in (("top_k=50 top_p=0.95 (sampled threshold, one pass)", 0.8, 50, 0.95),
-                                          ("top_k=0 top_p=0.9 (whole-vocabulary sort)", 1.0, 0, 0.9)):
+                                          ("top_k=0 top_p=0.9 (top-p over the whole vocabulary, head sorted, tail summed)", 1.0, 0, 0.9)):
             calls = [(lambda x=x: lib.check(L.b2_sample_rows(x.data_ptr(), R, VOCAB, VOCAB, F32, temp, top_k, top_p, 7,
                                                              offs.data_ptr(), ids.data_ptr(), ws.data_ptr(), s))) for x in logits]
             ms = timed(calls, nreps(6), warm=2)
             record(f"sample_rows {label}", f"{R}x{VOCAB} f32", R * VOCAB * 4 + 12 * R, ms, R,
                    note="bytes = the logits read once; launches and the ordered fp32 sums set the time, not HBM")
+        if stream is not None and R >= 2:
+            # the same batch as two half-batches on two streams (each call has its own workspace): the kernels that
+            # are one thread block per row and latency-bound (threshold search, head, finish) of one half run under
+            # the passes over the logits of the other
+            halves = ((0, R // 2), (R // 2, R))
+            sides = [torch.cuda.Stream(device=dev) for _ in halves]
+            wss = [torch.empty(L.b2_sampler_workspace_bytes(hi - lo, VOCAB), dtype=torch.uint8, device=dev) for lo, hi in halves]
+
+            def split_call(x, temp, top_k, top_p):
+                fork = torch.cuda.Event()
+                fork.record(stream)
+                for h, (lo, hi) in enumerate(halves):
+                    sides[h].wait_event(fork)
+                    lib.check(L.b2_sample_rows(x[lo:hi].data_ptr(), hi - lo, VOCAB, VOCAB, F32, temp, top_k, top_p, 7,
+                                               offs[lo:hi].data_ptr(), ids[lo:hi].data_ptr(), wss[h].data_ptr(), sides[h].cuda_stream))
+                    done = torch.cuda.Event()
+                    done.record(sides[h])
+                    stream.wait_event(done)
+            for label, temp, top_k, top_p in (("top_k=50 top_p=0.95", 0.8, 50, 0.95), ("top_k=0 top_p=0.9", 1.0, 0, 0.9)):
+                ms = timed([(lambda x=x: split_call(x, temp, top_k, top_p)) for x in logits], nreps(6), warm=2)
+                record(f"sample_rows {label}, the batch as two half-batches on two streams", f"{R}x{VOCAB} f32", R * VOCAB * 4 + 12 * R,
+                       ms, R, note="two calls, one workspace each; fork and join by events on the caller's stream")
+            del wss
         del logits, ws
     if want("kvmove"):
         half = torch.float16
