@@ -403,6 +403,16 @@ int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_
                             reinterpret_cast<const unsigned long long*>(draw_offsets), out_ids, workspace, as_stream(stream));
 }
 
+int b2_ordered_sums(const float* terms, int64_t rows, int64_t n, float* sums, b2_stream stream) {
+  const char* op = "b2_ordered_sums";
+  B2_REQUIRE(rows >= 0 && n >= 0, op, "negative size");
+  B2_REQUIRE(n <= B2_ORDERED_SUMS_MAX, op, "at most B2_ORDERED_SUMS_MAX terms per row");
+  B2_REQUIRE(rows <= 0x7fffffffll, op, "too many rows");
+  if (rows == 0 || n == 0) return B2_OK;
+  B2_REQUIRE(terms != nullptr && sums != nullptr, op, "null pointer");
+  return launch_ordered_sums(terms, rows, n, sums, as_stream(stream));
+}
+
 size_t b2_p2p_exchange_bytes(int world, int64_t max_rows) {
   return world >= 1 && world <= B2_P2P_MAX_WORLD && max_rows > 0 && max_rows < (1 << 24) ? exchange_bytes(world, max_rows) : 0;
 }

@@ -69,6 +69,7 @@ size_t sampler_workspace_bytes(int64_t rows, int64_t width);
 int launch_sample_rows(const void* logits, int64_t rows, int64_t width, int64_t row_stride, int dtype, float temperature,
                        int top_k, float top_p, unsigned long long seed, const unsigned long long* draw_offsets,
                        int32_t* out_ids, void* workspace, cudaStream_t s);
+int launch_ordered_sums(const float* terms, int64_t rows, int64_t n, float* sums, cudaStream_t s);
 // sampler_fallback.cu: lists the rows whose flag is up and, from the device and only if there are any, launches the
 // whole-row route over them
 int launch_sampler_rows_fallback(const int* row_flags, int64_t rows, int* list, int* count, const void* logits, int dtype,

@@ -455,16 +455,182 @@ __device__ __forceinline__ float tail_scale(const HeadState& h) {
   return span > 1e-6f ? float(kTailBuckets) / span : 0.0f;
 }
 
+// ---- fp32 running sums in index order, by the whole thread block.
+// vals[0 .. n) holds non-negative terms in descending order; on return vals[i] = fl(... fl(fl(vals[0] + vals[1]) +
+// vals[2]) ... + vals[i]), bit for bit what one thread adding them in order computes -- the reference's order -- and
+// *total the last of them.  The same observation as for the tail: while the sum S = M * 2^(k-23) stays inside one
+// power of two, adding a term moves M by round(term / 2^(k-23)), whatever M is, except when the quotient falls on a
+// half (then the parity of M decides: a tie) -- so inside one power of two the sums are a prefix sum of integers,
+// corrected at the few ties, which one thread walks in order.  The first terms (large against the sum: ties are
+// the rule there) and every term that carries the sum into the next power of two are added in fp32 by one thread.
+// kThreads * kPer >= n; every thread of the block calls this.  More than kMaxTies ties inside one power of two: the
+// rest is added serially (always correct, never seen on real rows).
+constexpr int kSerialFirst = 64, kMaxTies = 64;
+constexpr unsigned int kIncrementCap = 1u << 26;   // sums of increments saturate here: beyond 2^24 they only say "crossed"
+__device__ __forceinline__ unsigned int add_capped(unsigned int a, unsigned int b) {
+  const unsigned int c = a + b;                    // both <= the cap: no wrap
+  return c < kIncrementCap ? c : kIncrementCap;
+}
+struct TieRecord { int index; unsigned int before, increment; };
+
+template <int kThreads, int kPer>
+__device__ void ordered_sums_block(float* vals, int n, float* total) {
+  constexpr int kWarps = kThreads / 32;
+  __shared__ unsigned int warp_sums[kWarps];
+  __shared__ float seg_sum;
+  __shared__ int seg_start, tie_count, event_count, cross, serial_rest;
+  __shared__ TieRecord ties[kMaxTies];
+  __shared__ int events[kMaxTies];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  if (t == 0) {
+    float s = 0.0f;
+    const int first = n < kSerialFirst ? n : kSerialFirst;
+    for (int i = 0; i < first; ++i) { s += vals[i]; vals[i] = s; }
+    seg_sum = s;
+    seg_start = first;
+    serial_rest = (s > 0.0f && s <= 3.0e38f) ? 0 : 1;   // nothing to decompose in a zero, infinite or NaN sum
+    if (serial_rest != 0) {
+      for (int i = first; i < n; ++i) { s += vals[i]; vals[i] = s; }
+      seg_sum = s;
+      seg_start = n;
+    }
+  }
+  __syncthreads();
+  for (;;) {
+    const int i0 = seg_start;
+    if (i0 >= n) break;
+    const float S = seg_sum;
+    const unsigned int M = (__float_as_uint(S) & 0x7fffffu) | 0x800000u;
+    const int k = exponent_of(S);
+    if (t == 0) { tie_count = 0; event_count = 0; cross = n; }
+    // this thread's terms: kPer consecutive ones
+    unsigned int inc[kPer], tie_mask = 0u, mine = 0u;
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+      const int j = t * kPer + q;
+      inc[q] = 0u;
+      if (j >= i0 && j < n) {
+        bool tie;
+        term_increment(vals[j], k, inc[q], tie);
+        if (inc[q] > kIncrementCap) inc[q] = kIncrementCap;
+        if (tie) tie_mask |= 1u << q;
+      }
+      mine = add_capped(mine, inc[q]);
+    }
+    // exclusive scan of the threads' sums over the block
+    unsigned int scan = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const unsigned int up = __shfl_up_sync(0xffffffffu, scan, offset);
+      if (lane >= offset) scan = add_capped(scan, up);
+    }
+    if (lane == 31) warp_sums[warp] = scan;
+    __syncthreads();                                  // also: tie_count, event_count, cross are reset
+    unsigned int before = scan - mine;                // exclusive within the warp (no cap was hit unless scan is at the cap: then "crossed" anyway)
+    if (scan >= kIncrementCap) before = kIncrementCap;
+    for (int w = 0; w < warp; ++w) before = add_capped(before, warp_sums[w]);
+    unsigned int pref[kPer];                          // increments up to and including the term
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+      if (tie_mask >> q & 1u) {
+        const int slot = atomicAdd(&tie_count, 1);
+        if (slot < kMaxTies) ties[slot] = TieRecord{t * kPer + q, before, inc[q]};
+      }
+      before = add_capped(before, inc[q]);
+      pref[q] = before;
+    }
+    __syncthreads();
+    if (t == 0) {
+      const int count = tie_count;
+      if (count > kMaxTies) {
+        serial_rest = 1;
+      } else {
+        for (int a = 1; a < count; ++a) {             // by index: the order in which the sum meets them
+          const TieRecord x = ties[a];
+          int b = a - 1;
+          for (; b >= 0 && ties[b].index > x.index; --b) ties[b + 1] = ties[b];
+          ties[b + 1] = x;
+        }
+        unsigned int corrected = 0u;
+        int found = 0;
+        for (int a = 0; a < count; ++a) {
+          const unsigned int m_before = M + ties[a].before - corrected, q = ties[a].increment - 1u;
+          if (m_before + q >= (1u << 24)) break;      // at or beyond the next power of two: the serial step below takes over
+          if (((m_before + q) & 1u) == 0u) { ++corrected; events[found++] = ties[a].index; }   // half-way rounds to the even side: down
+        }
+        event_count = found;
+      }
+    }
+    __syncthreads();
+    if (serial_rest != 0) {
+      if (t == 0) {
+        float s = S;
+        for (int i = i0; i < n; ++i) { s += vals[i]; vals[i] = s; }
+        seg_sum = s;
+        seg_start = n;
+      }
+      __syncthreads();
+      break;
+    }
+    const int found = event_count;
+    unsigned int sums[kPer];
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+      const int j = t * kPer + q;
+      unsigned int corrected = 0u;
+      for (int a = 0; a < found; ++a) corrected += events[a] <= j ? 1u : 0u;
+      sums[q] = add_capped(M, pref[q]) - corrected;
+      if (j >= i0 && j < n && sums[q] >= (1u << 24)) { atomicMin(&cross, j); break; }   // later ones are larger still
+    }
+    __syncthreads();
+    const int c = cross;
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+      const int j = t * kPer + q;
+      if (j >= i0 && j < c) vals[j] = __uint_as_float((uint32_t(k + 127) << 23) | (sums[q] & 0x7fffffu));
+    }
+    __syncthreads();
+    if (t == 0) {
+      const float last = c > i0 ? vals[c - 1] : S;
+      if (c < n) {
+        const float s = last + vals[c];             // the term that reaches the next power of two: one fp32 addition
+        vals[c] = s;
+        seg_sum = s;
+        seg_start = c + 1;
+      } else {
+        seg_sum = last;
+        seg_start = n;
+      }
+    }
+    __syncthreads();
+  }
+  if (t == 0) *total = seg_sum;
+  __syncthreads();
+}
+
+// The running sums alone, one row of at most kTile terms per thread block (b2_ordered_sums).
+__global__ void __launch_bounds__(kRegThreads)
+ordered_sums_kernel(const float* terms, int64_t n, float* sums) {
+  dependent_launch_prologue();
+  __shared__ __align__(16) float vals[kTile];
+  __shared__ float total;
+  const float* src = terms + int64_t(blockIdx.x) * n;
+  for (int j = threadIdx.x; j < kTile; j += kRegThreads) vals[j] = j < n ? src[j] : 0.0f;
+  __syncthreads();
+  ordered_sums_block<kRegThreads, kRegKeys>(vals, int(n), &total);
+  float* dst = sums + int64_t(blockIdx.x) * n;
+  for (int j = threadIdx.x; j < n; j += kRegThreads) dst[j] = vals[j];
+}
+
 // head: the row's candidates (at most one 4096-key tile of them) are sorted in registers (the network of the whole-row
 // sort's tile kernel), written to the front of the row's key area for the finish kernel, and their exponentials
-// are added in order by one thread, every running sum kept.  One kernel: the keys go from the candidate list
+// are summed in the reference's order (ordered_sums_block above), every running sum kept.  One kernel: the keys go from the candidate list
 // through registers and shared memory to the sums without a round trip through global memory in between.
 __global__ void __launch_bounds__(kRegThreads)
 topp_head_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, const unsigned long long* candidates,
                  unsigned int* tails, float* running, HeadState* heads, int* row_flags) {
   dependent_launch_prologue();
   __shared__ unsigned long long tile[kTile];
-  __shared__ __align__(16) float stage[kChunk];
   __shared__ float carry;
   const int64_t row = blockIdx.x;
   const int t = threadIdx.x, lane = t & 31;
@@ -498,24 +664,26 @@ topp_head_kernel(unsigned long long* keys, int64_t padded, const CutState* cut, 
   __syncthreads();                                   // the transposes are done with the tile
   unsigned long long* dst = keys + row * padded;
 #pragma unroll
-  for (int r = 0; r < kRegKeys; ++r) {
-    tile[r * kRegThreads + t] = key[r];              // in order, for the sums below
-    dst[r * kRegThreads + t] = key[r];               // and for the finish kernel
-  }
-  if (t == 0) carry = 0.0f;
+  for (int r = 0; r < kRegKeys; ++r) dst[r * kRegThreads + t] = key[r];   // in order (layout S), for the finish kernel
+  // the exponentials, in order, in the shared memory the sort no longer needs; then their running sums by the block
+  __shared__ float bounds[2];                        // score of the first and of the last head token
+  float* vals = reinterpret_cast<float*>(tile);
+  if (t == 0) bounds[0] = key_score(key[0]);
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r)
+    if (r * kRegThreads + t == count - 1) bounds[1] = key_score(key[r]);
   __syncthreads();
-  const float maximum = key_score(tile[0]);
-  float* cum = running + row * padded;
-  for (int base = 0; base < count; base += kChunk) {
-    const int m = count - base < kChunk ? count - base : kChunk;
-    for (int j = t; j < m; j += kRegThreads) stage[j] = expf(key_score(tile[base + j]) - maximum);
-    __syncthreads();
-    if (t == 0) carry = running_sums_in_order(stage, m, carry);
-    __syncthreads();
-    for (int j = t; j < m; j += kRegThreads) cum[base + j] = stage[j];
-    __syncthreads();
+  const float maximum = bounds[0];
+#pragma unroll
+  for (int r = 0; r < kRegKeys; ++r) {
+    const int j = r * kRegThreads + t;
+    vals[j] = j < count ? expf(key_score(key[r]) - maximum) : 0.0f;
   }
-  if (t == 0) heads[row] = HeadState{carry, maximum, key_score(tile[count - 1]), count};
+  __syncthreads();
+  ordered_sums_block<kRegThreads, kRegKeys>(vals, count, &carry);
+  float* cum = running + row * padded;
+  for (int j = t; j < count; j += kRegThreads) cum[j] = vals[j];
+  if (t == 0) heads[row] = HeadState{carry, maximum, bounds[1], count};
 }
 
 // tail: increments of every term below the head, per bucket, for the head's power of two and the next one.
@@ -868,6 +1036,12 @@ int64_t padded_width(int64_t width) {
 
 // per row: padded keys (8 B each), padded running sums (4 B each), the candidates of the top-k / top-p paths, the
 // tail buckets of the top-p path and three small records; one flag for the whole call
+int launch_ordered_sums(const float* terms, int64_t rows, int64_t n, float* sums, cudaStream_t s) {
+  if (rows == 0 || n == 0) return B2_OK;
+  launch_kernel(ordered_sums_kernel, dim3(unsigned(rows)), dim3(kRegThreads), 0, s, terms, n, sums);
+  return launch_status("ordered_sums");
+}
+
 size_t sampler_workspace_bytes(int64_t rows, int64_t width) {
   const int64_t padded = padded_width(width);
   const size_t per_row = size_t(padded) * 12 + size_t(kCandidates) * 8 + size_t(3 * kTailBuckets) * 4 + sizeof(CutState) +

@@ -86,6 +86,7 @@ _SIGNATURES = {
     "b2_qk_norm_rope_paged": (_i, [_p] * 10 + [_i64, _i64, _i64, _i64, _f, _f, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "b2_select_last_valid_rows": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p, _p]),
     "b2_sampler_workspace_bytes": (_sz, [_i64, _i64]),
+    "b2_ordered_sums": (_i, [_p, _i64, _i64, _p, _p]),
     "b2_sample_rows": (_i, [_p, _i64, _i64, _i64, _i, _f, C.c_int32, _f, C.c_uint64, _p, _p, _p, _p]),
     "b2_p2p_exchange_bytes": (_sz, [_i, _i64]),
     "b2_p2p_exchange_init": (_i, [_p, _i, _i64, _p]),

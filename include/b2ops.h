@@ -351,6 +351,15 @@ B2_API int b2_sample_rows(const void* logits, int64_t rows, int64_t width, int64
                           float temperature, int32_t top_k, float top_p, uint64_t seed, const uint64_t* draw_offsets,
                           int32_t* out_ids, void* workspace, b2_stream stream);
 
+/* sums[r, i] = fl(... fl(fl(terms[r, 0] + terms[r, 1]) + terms[r, 2]) ... + terms[r, i]): the fp32 running sums of
+ * each row's terms added one after the other in index order -- what the single thread of the reference's
+ * sampler_select computes (src/ops_cuda.cu:587-603), bit for bit -- by a whole thread block: inside one power
+ * of two of the sum the additions are a prefix sum of integer increments, corrected at the ties.
+ * terms: device fp32 [rows, n], non-negative, each row in descending order (the order the sampler meets them);
+ * n <= B2_ORDERED_SUMS_MAX.  sums may alias terms. */
+#define B2_ORDERED_SUMS_MAX 4096
+B2_API int b2_ordered_sums(const float* terms, int64_t rows, int64_t n, float* sums, b2_stream stream);
+
 /* ---- vocabulary-sharded reductions with the exchange fused into the kernel ------ */
 
 /* One process per GPU, all GPUs on one NVLink node.  Instead of reduce kernel -> collective
