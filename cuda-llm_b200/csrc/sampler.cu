@@ -968,44 +968,24 @@ topp_finish_kernel(const T* logits, int64_t width, int64_t row_stride, float tem
     __syncthreads();
   }
   const float total = __uint_as_float((uint32_t(walk_k + 127) << 23) | (walk_m & 0x7fffffu));
-  float* stage = reinterpret_cast<float*>(bucket_keys);   // the gathered keys are no longer needed: kChunk floats fit their place
+  float* stage = reinterpret_cast<float*>(bucket_keys);   // the gathered keys are no longer needed: kTile floats fit their place
   __syncthreads();
 
   // the reference's top-p walk (src/ops_cuda.cu:596-603) over the head; it must end strictly above the head's lowest score
   const unsigned long long* sorted = keys + row * padded;
   const float* cum = running + row * padded;
   const int limit = h.count;
-  if (tid == 0) { carry = 0.0f; found = -1; }
+  // the masses in order, their running sums by the whole block (ordered_sums_block: the serial walk's additions, bit
+  // for bit), then the first index at which the running mass reaches top_p
+  for (int j = tid; j < kTile; j += kSortThreads)
+    stage[j] = j < limit ? __fdiv_rn(expf(key_score(sorted[j]) - h.max_score), total) : 0.0f;
+  if (tid == 0) found = limit;
   __syncthreads();
-  int prefix = -1;
-  for (int base = 0; base < limit; base += kChunk) {
-    const int m = limit - base < kChunk ? limit - base : kChunk;
-    for (int j = tid; j < m; j += kSortThreads) stage[j] = __fdiv_rn(expf(key_score(sorted[base + j]) - h.max_score), total);
-    __syncthreads();
-    if (tid == 0) {
-      float cumulative = carry;
-      int at = -1, j = 0;
-      for (; j + 8 <= m && at < 0; j += 8) {        // eight loads in flight; the additions stay in order
-        const float4 a = *reinterpret_cast<const float4*>(stage + j), b4 = *reinterpret_cast<const float4*>(stage + j + 4);
-        const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          if (at < 0) {
-            cumulative += v[q];
-            if (cumulative >= top_p) at = j + q;
-          }
-        }
-      }
-      for (; j < m && at < 0; ++j) {
-        cumulative += stage[j];
-        if (cumulative >= top_p) at = j;
-      }
-      carry = cumulative;
-      found = at;
-    }
-    __syncthreads();
-    if (found >= 0) { prefix = base + found + 1; break; }
-  }
+  ordered_sums_block<kSortThreads, kTile / kSortThreads>(stage, limit, &carry);
+  for (int j = tid; j < limit; j += kSortThreads)
+    if (stage[j] >= top_p) { atomicMin(&found, j); break; }   // the sums never decrease: a thread's first hit is its lowest
+  __syncthreads();
+  const int prefix = found < limit ? found + 1 : -1;
   if (prefix < 0 || !(key_score(sorted[prefix - 1]) > h.low_score)) {   // not settled inside the head: the whole-row path decides
     if (tid == 0) row_flags[row] = 5;
     return;
