@@ -132,10 +132,11 @@ __device__ __forceinline__ float from_ordered_bits(uint32_t o) {
 
 constexpr int kSplitThreads = 1024;
 constexpr int kSamplesPerThread = kSplitSamples / kSplitThreads;
-// The sample of rank `rank` (0 = largest) is found by a radix select over the samples' 32 ordered bits, eight bits
-// a round, instead of sorting them: per round a 256-bin histogram of the samples that still match the digits
-// found so far (votes of a warp for one bin are added by one lane: most samples share the leading digits), then
-// one warp walks the bins from the top.  Every thread keeps its samples in registers.
+constexpr int kSplitLowestBit = 12;   // the threshold is lowered by 2^-12 of its magnitude anyway: the low bits stay zero (a lower bound)
+// The sample of rank `rank` (0 = largest) is found without sorting the samples: its 32 ordered bits are decided one
+// at a time from the top by counting the samples at or above a candidate (the lowest twelve bits are left zero:
+// that only lowers the threshold a little further).  Every thread keeps its samples in registers.  (A radix select with 256-bin histograms took three times as long: most samples share their leading
+// digits, and matching a warp's votes per bin costs more than the eight comparisons of a count.)
 template <typename T>
 __global__ void __launch_bounds__(kSplitThreads)
 topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigned int top_k, int safe, CutState* cut,
@@ -143,26 +144,25 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
   // top_k == 0: no count to reach; the threshold is to leave as many candidates as fit one kTile-key tile with near
   // certainty (the top-p path's head)
   dependent_launch_prologue();
-  __shared__ unsigned int bins[256];
-  __shared__ uint32_t prefix_found;
-  __shared__ int rank_left;
+  __shared__ unsigned int counts[2][kSplitThreads / 32];
   const int64_t row = blockIdx.x;
   overflow += row * overflow_stride;
   const T* src = logits + row * row_stride;
   // as many samples as there are tokens to take them from two apart, at most kSplitSamples
   int samples = kSplitSamples;
   while (samples > kSplitThreads && int64_t(samples) * 2 > width) samples >>= 1;
+  const int run_shift = 31 - __clz(samples >> 5);    // log2 of the number of 32-token runs
   uint32_t mine[kSamplesPerThread];
 #pragma unroll
   for (int q = 0; q < kSamplesPerThread; ++q) {
     const int sidx = threadIdx.x + q * kSplitThreads;
-    mine[q] = 0u;
-    if (sidx < samples) {
-      // runs of 32 neighbouring tokens, the runs evenly spaced: one 128-byte line per run instead of one sector
-      // per sample (samples every 18 tokens would touch every sector of the row: a whole extra pass over the logits)
-      const float x = Elem<T>::load(src + (int64_t(sidx >> 5) * width) / (samples >> 5) + (sidx & 31));
-      mine[q] = x == x ? ordered_bits(x) : 0u;                                   // a NaN never ranks
-    }
+    const bool present = sidx < samples;
+    const int at = present ? sidx : 0;                 // every load is issued (none sits behind a branch): all in flight at once
+    // runs of 32 neighbouring tokens, the runs evenly spaced: one 128-byte line per run instead of one sector
+    // per sample (samples every 18 tokens would touch every sector of the row: a whole extra pass over the logits);
+    // the number of runs is a power of two: a shift, not a 64-bit division per sample
+    const float x = Elem<T>::load(src + ((int64_t(at >> 5) * width) >> run_shift) + (at & 31));
+    mine[q] = present && x == x ? ordered_bits(x) : 0u;                          // a NaN never ranks
   }
   // expected rank of the top_k-th token among the samples, plus four standard deviations and two
   const float expected = float(top_k) * float(samples) / float(width);
@@ -177,49 +177,23 @@ topk_splitter_kernel(const T* logits, int64_t width, int64_t row_stride, unsigne
     if (rank < 2) rank = 2;
   }
   bool ok = safe != 0 && rank < samples;
-  if (threadIdx.x == 0) { prefix_found = 0u; rank_left = ok ? rank : 0; }
-  const int lane = threadIdx.x & 31;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    if (threadIdx.x < 256) bins[threadIdx.x] = 0u;
+  // the key with exactly `need` samples at or above it, bit by bit from the top: a candidate keeps its bit when
+  // at least `need` samples are at or above it (32 counts of 8 comparisons per thread, one barrier each)
+  const unsigned int need = unsigned(ok ? rank : 0) + 1u;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t prefix_found = 0u;
+  for (int bit = 31; bit >= kSplitLowestBit; --bit) {
+    const uint32_t candidate = prefix_found | (1u << bit);
+    unsigned int above = 0u;
+#pragma unroll
+    for (int q = 0; q < kSamplesPerThread; ++q) above += mine[q] >= candidate ? 1u : 0u;   // absent samples and NaNs are 0: never counted
+    above = __reduce_add_sync(0xffffffffu, above);
+    // one slot per warp (32 warps adding to one address would queue), two sets of slots in turn: a warp can be
+    // one barrier ahead of the slowest reader, never two
+    if (lane == 0) counts[bit & 1][warp] = above;
     __syncthreads();
-    const uint32_t prefix = prefix_found;
-    const uint32_t above = shift == 24 ? 0u : 0xffffffffu << (shift + 8);     // the digits already fixed
-#pragma unroll
-    for (int q = 0; q < kSamplesPerThread; ++q) {
-      const bool in = threadIdx.x + q * kSplitThreads < samples && (mine[q] & above) == prefix;
-      const unsigned int digit = in ? (mine[q] >> shift) & 255u : 256u;         // 256: not taking part
-      const unsigned int peers = __match_any_sync(0xffffffffu, digit);
-      if (in && lane == __ffs(peers) - 1) atomicAdd(&bins[digit], unsigned(__popc(peers)));
-    }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      // lane l owns bins 255 - 8l .. 248 - 8l (descending); a warp scan finds the bin that holds the rank
-      unsigned int own[8], total = 0u;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { own[i] = bins[255 - (lane * 8 + i)]; total += own[i]; }
-      unsigned int before = total;
-#pragma unroll
-      for (int offset = 1; offset < 32; offset <<= 1) {
-        const unsigned int up = __shfl_up_sync(0xffffffffu, before, offset);
-        if (lane >= offset) before += up;
-      }
-      before -= total;                                                          // samples in the bins above this lane's
-      const unsigned int want = unsigned(rank_left);
-      const bool here = want >= before && want < before + total;
-      __syncwarp();
-      if (here) {
-        unsigned int seen = before;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (want >= seen && want < seen + own[i]) {
-            prefix_found = prefix | (uint32_t(255 - (lane * 8 + i)) << shift);
-            rank_left = int(want - seen);
-          }
-          seen += own[i];
-        }
-      }
-    }
-    __syncthreads();
+    const unsigned int all = __reduce_add_sync(0xffffffffu, lane < kSplitThreads / 32 ? counts[bit & 1][lane] : 0u);
+    if (all >= need) prefix_found = candidate;                // every thread takes the same decision
   }
   if (threadIdx.x != 0) return;
   float threshold = -INFINITY;
